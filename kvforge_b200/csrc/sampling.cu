@@ -1,0 +1,285 @@
+// Token sampling on the device: greedy, temperature, top-k and top-p, one CTA per row.
+//
+// Meaning of the options (as in umarhassan-cloud/kvforge, src/tokenvault/sampling.py:40-66):
+// temperature 0 picks the argmax of the logits; otherwise logits are divided by the
+// temperature; top-k keeps the k largest; top-p keeps, in descending order, the entries
+// whose mass *before* them is below top_p (so the top entry always stays); the token is
+// drawn from the softmax of what is kept.
+//
+// How: no sort.  The k-th largest value and the top-p cut are found by a radix descent over
+// the order-preserving integer image of the floats (4 levels of 8 bits), by count for
+// top-k and by probability mass for top-p.  Masses are exp(x - max) in 2^-40 fixed point
+// summed as 64-bit integers, so every sum is exact and independent of the order of
+// addition: the same row, options and random key always give the same token.  Values tied
+// with the k-th largest all stay.  The draw is the inverse CDF in index order with a
+// uniform integer in [0, total mass).
+#include "common.cuh"
+
+using namespace kvf;
+
+namespace {
+
+constexpr int THREADS = 512;
+constexpr int NWARPS = THREADS / 32;
+constexpr float FIX_ONE = 1099511627776.0f;  // 2^40
+
+__device__ __forceinline__ unsigned ordered_key(float v) {
+  const unsigned b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long t = __shfl_xor_sync(0xffffffffu, v, o);
+    v = t > v ? t : v;
+  }
+  return v;
+}
+
+struct Shared {
+  unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass)
+  unsigned long long red[NWARPS];
+  unsigned long long bcast[3];
+  float fred[32];
+};
+
+// One level of the radix descent.  Among entries with key >= lo_key whose bits above
+// `shift + 8` equal `prefix`, histogram (count or mass) by the digit at `shift`, then walk
+// digits from 255 down until the running total reaches `remaining`.  Returns the digit and
+// updates `remaining` to what is still wanted inside that digit.
+template <bool BY_MASS>
+__device__ int radix_level(Shared& sh, const float* row, int V, float temp, float mx, unsigned lo_key,
+                           unsigned prefix, int shift, unsigned long long& remaining) {
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < NWARPS * 256; i += THREADS) (&sh.hist[0][0])[i] = 0ull;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += THREADS) {
+    const float x = row[i] / temp;
+    const unsigned key = ordered_key(x);
+    if (key < lo_key) continue;
+    if (shift < 24 && (key >> (shift + 8)) != prefix) continue;
+    const unsigned digit = (key >> shift) & 255u;
+    const unsigned long long w = BY_MASS ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 1ull;
+    atomicAdd(&sh.hist[warp][digit], w);
+  }
+  __syncthreads();
+  // fold the per-warp histograms: thread t < 256 owns digit t
+  if (threadIdx.x < 256) {
+    unsigned long long s = 0;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) s += sh.hist[w][threadIdx.x];
+    sh.hist[0][threadIdx.x] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long cum = 0;
+    int chosen = 0;
+    unsigned long long rem = remaining;
+    bool found = false;
+    for (int dgt = 255; dgt >= 0; --dgt) {
+      const unsigned long long c = sh.hist[0][dgt];
+      if (cum + c >= remaining) {
+        chosen = dgt;
+        rem = remaining - cum;
+        found = true;
+        break;
+      }
+      cum += c;
+    }
+    if (!found) {  // fewer than wanted exist under this prefix: take everything
+      chosen = 0;
+      rem = 0;
+    }
+    sh.bcast[0] = (unsigned long long)chosen;
+    sh.bcast[1] = rem;
+  }
+  __syncthreads();
+  remaining = sh.bcast[1];
+  const int chosen = (int)sh.bcast[0];
+  __syncthreads();
+  return chosen;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temps,
+              const int* __restrict__ top_ks, const float* __restrict__ top_ps,
+              const unsigned long long* __restrict__ rand_keys, int* __restrict__ out_tokens,
+              float* __restrict__ probs_out) {
+  __shared__ Shared sh;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  float* prow = probs_out ? probs_out + (size_t)r * V : nullptr;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float T = temps ? temps[r] : 0.f;
+
+  if (T == 0.f) {
+    // ---- greedy: highest logit, lowest index among equals
+    unsigned long long best = 0;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+      const unsigned long long c = ((unsigned long long)ordered_key(row[i]) << 32) | (0xFFFFFFFFu - (unsigned)i);
+      best = c > best ? c : best;
+    }
+    best = warp_max_u64(best);
+    if (lane == 0) sh.red[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long v = lane < NWARPS ? sh.red[lane] : 0ull;
+      v = warp_max_u64(v);
+      if (lane == 0) sh.bcast[0] = v;
+    }
+    __syncthreads();
+    const int tok = (int)(0xFFFFFFFFu - (unsigned)(sh.bcast[0] & 0xFFFFFFFFull));
+    if (threadIdx.x == 0) out_tokens[r] = tok;
+    if (prow)
+      for (int i = threadIdx.x; i < V; i += THREADS) prow[i] = (i == tok) ? 1.f : 0.f;
+    return;
+  }
+
+  // ---- maximum of the scaled row
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += THREADS) mx = fmaxf(mx, row[i] / T);
+  mx = block_max(mx, sh.fred);
+  __syncthreads();
+
+  unsigned lo_key = 0u;  // entries with key >= lo_key are kept
+  const int k = top_ks ? top_ks[r] : 0;
+  if (k > 0 && k < V) {
+    unsigned prefix = 0u;
+    unsigned long long remaining = (unsigned long long)k;
+    for (int level = 0; level < 4; ++level) {
+      const int shift = 24 - 8 * level;
+      const int dgt = radix_level<false>(sh, row, V, T, mx, 0u, prefix, shift, remaining);
+      prefix = (prefix << 8) | (unsigned)dgt;
+    }
+    lo_key = prefix;  // the k-th largest key
+  }
+
+  const float top_p = top_ps ? top_ps[r] : 1.f;
+  if (top_p < 1.f) {
+    // mass of what top-k kept
+    unsigned long long z = 0;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+      const float x = row[i] / T;
+      if (ordered_key(x) >= lo_key) z += __float2ull_rz(expf(x - mx) * FIX_ONE);
+    }
+    z = warp_sum_u64(z);
+    if (lane == 0) sh.red[warp] = z;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long s = 0;
+      for (int w = 0; w < NWARPS; ++w) s += sh.red[w];
+      unsigned long long tgt = (unsigned long long)ceil((double)top_p * (double)s);
+      if (tgt < 1ull) tgt = 1ull;
+      if (tgt > s) tgt = s;
+      sh.bcast[0] = tgt;
+    }
+    __syncthreads();
+    unsigned long long remaining = sh.bcast[0];
+    __syncthreads();
+    unsigned prefix = 0u;
+    for (int level = 0; level < 4; ++level) {
+      const int shift = 24 - 8 * level;
+      const int dgt = radix_level<true>(sh, row, V, T, mx, lo_key, prefix, shift, remaining);
+      prefix = (prefix << 8) | (unsigned)dgt;
+    }
+    lo_key = prefix > lo_key ? prefix : lo_key;
+  }
+
+  // ---- draw: warp w owns the contiguous index range [w*seg, (w+1)*seg)
+  const int seg = (((V + NWARPS - 1) / NWARPS) + 31) / 32 * 32;
+  const int s_begin = warp * seg, s_end = min(V, s_begin + seg);
+  unsigned long long part = 0;
+  for (int i = s_begin + lane; i < s_end; i += 32) {
+    const float x = row[i] / T;
+    if (ordered_key(x) >= lo_key) part += __float2ull_rz(expf(x - mx) * FIX_ONE);
+  }
+  part = warp_sum_u64(part);
+  if (lane == 0) sh.red[warp] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long total = 0;
+    for (int w = 0; w < NWARPS; ++w) total += sh.red[w];
+    const unsigned long long rnd = splitmix64(rand_keys ? rand_keys[r] : 0ull);
+    unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
+    int w_sel = NWARPS - 1;
+    unsigned long long before = 0;
+    for (int w = 0; w < NWARPS; ++w) {
+      if (target < before + sh.red[w]) {
+        w_sel = w;
+        break;
+      }
+      before += sh.red[w];
+    }
+    sh.bcast[0] = target - before;
+    sh.bcast[1] = total;
+    sh.bcast[2] = (unsigned long long)w_sel;
+  }
+  __syncthreads();
+  const int w_sel = (int)sh.bcast[2];
+  unsigned long long rem = sh.bcast[0];
+  const unsigned long long total = sh.bcast[1];
+  if (warp == w_sel) {
+    int tok = -1;
+    int last_kept = -1;
+    for (int base = s_begin; base < s_end && tok < 0; base += 32) {
+      const int i = base + lane;
+      unsigned long long w = 0;
+      if (i < s_end) {
+        const float x = row[i] / T;
+        if (ordered_key(x) >= lo_key) w = __float2ull_rz(expf(x - mx) * FIX_ONE);
+      }
+      unsigned long long incl = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const unsigned hit = __ballot_sync(0xffffffffu, w > 0 && incl > rem);
+      const unsigned kept = __ballot_sync(0xffffffffu, w > 0);
+      if (kept) last_kept = base + 31 - __clz(kept);
+      if (hit) {
+        tok = base + __ffs(hit) - 1;
+      } else {
+        rem -= __shfl_sync(0xffffffffu, incl, 31);
+      }
+    }
+    if (tok < 0) tok = last_kept >= 0 ? last_kept : 0;
+    if (lane == 0) out_tokens[r] = tok;
+  }
+  if (prow) {
+    const float inv = 1.f / (float)total;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+      const float x = row[i] / T;
+      const unsigned long long w = ordered_key(x) >= lo_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
+      prow[i] = (float)w * inv;
+    }
+  }
+}
+
+}  // namespace
+
+// logits: [R, V] float with row stride ld.  temps/top_ks/top_ps/rand_keys: [R] (null temps =
+// all greedy).  out_tokens: [R] int.  probs_out: optional [R, V] float, the distribution
+// each token was drawn from (for tests).
+KVF_API int kvf_sample_f32(const float* logits, long long ld, int R, int V, const float* temps,
+                           const int* top_ks, const float* top_ps, const unsigned long long* rand_keys,
+                           int* out_tokens, float* probs_out, cudaStream_t st) {
+  if (R <= 0) return 0;
+  if (V <= 0) return (int)cudaErrorInvalidValue;
+  sample_kernel<<<R, THREADS, 0, st>>>(logits, ld, V, temps, top_ks, top_ps, rand_keys, out_tokens, probs_out);
+  return KVF_LAUNCH_STATUS();
+}

@@ -1,0 +1,85 @@
+"""Device-side run state shared by the parts: storage type, persistent activation
+buffers, the device error flag, and the step's batch description (``StepContext``)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+class Runtime:
+    """Owns the activation buffers.  A buffer is asked for by name and width and is kept for
+    the life of the runtime, so that the same addresses are used every step (a captured
+    CUDA graph can be replayed) and no step allocates."""
+
+    def __init__(self, device: str | torch.device, dtype: torch.dtype, max_tokens: int, max_seqs: int, max_model_len: int = 0) -> None:
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("kvforge_b200 runs on a CUDA device only (there is no CPU path)")
+        self.dtype = dtype
+        self.max_tokens = int(max_tokens)
+        self.max_seqs = int(max_seqs)
+        self.max_model_len = int(max_model_len)
+        self._buffers: dict[tuple, torch.Tensor] = {}
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.capturing = False
+
+    def buf(self, name: str, rows: int, cols: int, dtype: torch.dtype | None = None, cap: int | None = None) -> torch.Tensor:
+        """A ``[rows, cols]`` view of the persistent buffer ``name`` (contents undefined).
+        It is made for ``cap`` rows (default: the token budget of a step) and grows if more
+        are asked for."""
+        dtype = dtype or self.dtype
+        key = (name, cols, dtype)
+        t = self._buffers.get(key)
+        if t is None or t.shape[0] < rows:
+            if self.capturing:
+                raise RuntimeError(f"buffer {name} would have to grow during graph capture")
+            cap = max(rows, self.max_tokens if cap is None else cap)
+            t = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            self._buffers[key] = t
+        return t[:rows]
+
+    def check_error_flag(self) -> None:
+        flag = int(self.err.item())
+        if flag:
+            self.err.zero_()
+            what = []
+            if flag & 1:
+                what.append("a token id outside the vocabulary")
+            if flag & 2:
+                what.append("a cache slot outside the pool")
+            raise RuntimeError("device-side check failed: " + ", ".join(what or [f"flag {flag}"]))
+
+
+@dataclass
+class StepContext:
+    """One step's batch as the parts see it.  All device arrays are int32."""
+
+    rt: Runtime
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor  # [N]
+    positions: torch.Tensor  # [N] absolute position of each token
+    query_start_loc: torch.Tensor  # [B+1]
+    context_lens: torch.Tensor  # [B] tokens in the cache after this step's writes
+    state_slots: torch.Tensor  # [B] slot of each request's fixed-size state
+    logit_rows: torch.Tensor  # [R] flat token rows whose logits are wanted
+    num_logit_rows: int
+    block_tables: list[torch.Tensor]  # per cache group: [B, W]
+    slot_mappings: list[torch.Tensor]  # per cache group: [N]
+    max_query_len: int
+    max_context_len: int
+    block_size: int
+    # Host copies, for parts that walk sequences on the host (test parts do).
+    h_query_start_loc: np.ndarray | None = None
+    h_context_lens: np.ndarray | None = None
+    h_state_slots: np.ndarray | None = None
+    # Upper bound on any context (fixes grid sizes of captured decode steps).
+    context_bound: int = 0
+    extras: dict = field(default_factory=dict)
+
+    @property
+    def all_single_query(self) -> bool:
+        return self.max_query_len == 1

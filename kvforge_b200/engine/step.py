@@ -1,0 +1,299 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+Same contract as umarhassan-cloud/kvforge's ``prepare_inputs`` + ``ModelRunner.execute``
+(src/tokenvault/batching/continuous.py:44-117): items are whole prompts, portions of prompts
+at any start position, or single decoded tokens, mixed freely; all of them run as one flat
+batch; only the tokens given are computed, everything before them comes from the cache;
+pages for the new positions must have been reserved by the caller.
+
+Different in how: all index arrays are int32 and are packed on the host into one pinned
+buffer that goes to the device in a single copy; the device copy lives at fixed addresses.
+A step of single tokens only is, per batch-size bucket, captured once as a CUDA graph and
+replayed (the arrays it reads are then laid out for the bucket's full width, so the
+addresses inside the graph stay valid).
+"""
+
+from __future__ import annotations
+
+from collections.abc import Sequence
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache.block_manager import BlockManager
+from ..cache.state_slots import StateSlotPool
+from .runtime import Runtime, StepContext
+
+
+@dataclass
+class BatchItem:
+    """``logits``: ``"last"``, ``"all"``, ``"none"`` (continuous.py:24-32) or a list of places
+    among ``token_ids`` whose logits are wanted."""
+
+    seq_id: str
+    token_ids: Sequence[int]
+    start_pos: int
+    logits: str | Sequence[int] = "last"
+
+    def wanted(self) -> list[int]:
+        n = len(self.token_ids)
+        if isinstance(self.logits, str):
+            if self.logits == "last":
+                return [n - 1]
+            if self.logits == "all":
+                return list(range(n))
+            if self.logits == "none":
+                return []
+            raise ValueError(f"logits mode {self.logits!r}")
+        out = [int(i) for i in self.logits]
+        for i in out:
+            if not 0 <= i < n:
+                raise ValueError(f"wanted place {i} is outside the {n} tokens of {self.seq_id}")
+        return out
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+@dataclass
+class _Layout:
+    """Offsets (in int32 elements) of the arrays of a step inside the metadata buffer."""
+
+    n_cap: int
+    b_cap: int
+    width: int
+    n_groups: int
+    r_cap: int
+    off: dict[str, int] = field(default_factory=dict)
+    total: int = 0
+
+    def __post_init__(self) -> None:
+        o = 0
+        for name, size in (
+            ("token_ids", self.n_cap),
+            ("positions", self.n_cap),
+            ("logit_rows", self.r_cap),
+            ("qsl", self.b_cap + 1),
+            ("ctx", self.b_cap),
+            ("state_slots", self.b_cap),
+            ("slots", self.n_groups * self.n_cap),
+            ("tables", self.n_groups * self.b_cap * self.width),
+        ):
+            self.off[name] = o
+            o += _align(size)
+        self.total = o
+
+
+class ModelRunner:
+    """Owns the device metadata buffer and runs ``model.forward`` on batches."""
+
+    def __init__(
+        self,
+        model,
+        rt: Runtime,
+        block_manager: BlockManager,
+        state_slots: StateSlotPool | None,
+        max_model_len: int,
+        cuda_graphs: bool = False,
+        graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64, 128, 256),
+    ) -> None:
+        self.model = model
+        self.rt = rt
+        self.block_manager = block_manager
+        self.state_slots = state_slots
+        self.block_size = block_manager.block_size
+        self.max_model_len = int(max_model_len)
+        self.max_width = max(1, -(-self.max_model_len // self.block_size))
+        self.n_groups = block_manager.num_groups
+        self.cuda_graphs = bool(cuda_graphs)
+        self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
+        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._cap = 0
+        self._host: torch.Tensor | None = None
+        self._dev: torch.Tensor | None = None
+        self._copy_done: torch.cuda.Event | None = None
+        # made once for the widest step there can be, so its address never changes
+        self._ensure(self._layout(rt.max_tokens, rt.max_seqs, self.max_width, rt.max_tokens).total)
+        self.num_forward_passes = 0  # continuous.py:105-106
+        self.num_tokens_processed = 0
+
+    # ------------------------------------------------------------------ buffers
+    def _layout(self, n_cap: int, b_cap: int, width: int, r_cap: int) -> _Layout:
+        return _Layout(n_cap, b_cap, max(1, width), self.n_groups, max(1, r_cap))
+
+    def _ensure(self, total: int) -> None:
+        if total <= self._cap:
+            return
+        if self._graphs:
+            raise RuntimeError("the metadata buffer would have to move after graphs were captured")
+        self._cap = int(total) + 64
+        self._host = torch.empty(self._cap, dtype=torch.int32, pin_memory=True)
+        self._dev = torch.empty(self._cap, dtype=torch.int32, device=self.rt.device)
+
+    # ------------------------------------------------------------------ batch building
+    def _upload(self, total: int) -> None:
+        """The one host-to-device copy of a step."""
+        self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        if self._copy_done is None:
+            self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+
+    def _fill(self, items: Sequence[BatchItem], lay: _Layout) -> tuple[int, int, int, int, int]:
+        """Write the arrays of ``items`` into the host buffer under layout ``lay``."""
+        if self._copy_done is not None:
+            self._copy_done.synchronize()  # the last step's copy has left the host buffer
+        host = self._host.numpy()
+        bm, bs = self.block_manager, self.block_size
+        o = lay.off
+        n = 0
+        rows: list[int] = []
+        max_q = max_ctx = 0
+        qsl = host[o["qsl"] : o["qsl"] + lay.b_cap + 1]
+        ctx = host[o["ctx"] : o["ctx"] + lay.b_cap]
+        sslots = host[o["state_slots"] : o["state_slots"] + lay.b_cap]
+        qsl[0] = 0
+        for b, item in enumerate(items):
+            k = len(item.token_ids)
+            if k == 0:
+                raise ValueError(f"request {item.seq_id} brings no tokens")
+            end = item.start_pos + k
+            if end > self.max_model_len:
+                raise ValueError(f"request {item.seq_id} would reach {end} tokens, beyond max_model_len {self.max_model_len}")
+            host[o["token_ids"] + n : o["token_ids"] + n + k] = item.token_ids
+            host[o["positions"] + n : o["positions"] + n + k] = np.arange(item.start_pos, end, dtype=np.int32)
+            for g in range(self.n_groups):
+                base = o["slots"] + g * lay.n_cap + n
+                host[base : base + k] = bm.slots(item.seq_id, item.start_pos, end, g)
+                table = bm.get_block_table(item.seq_id, g)
+                used = -(-end // bs)  # only the pages that cover the live context (continuous.py:67)
+                tb = o["tables"] + (g * lay.b_cap + b) * lay.width
+                host[tb : tb + used] = table[:used]  # entries past the context are never read
+            rows.extend(n + i for i in item.wanted())
+            n += k
+            qsl[b + 1] = n
+            ctx[b] = end
+            sslots[b] = self.state_slots.slot(item.seq_id) if (self.state_slots and self.state_slots.has(item.seq_id)) else 0
+            max_q = max(max_q, k)
+            max_ctx = max(max_ctx, end)
+        nb = len(items)
+        # padding sequences of a captured bucket: no queries, no context
+        for b in range(nb, lay.b_cap):
+            qsl[b + 1] = n
+            ctx[b] = 0
+            sslots[b] = 0
+        if len(rows) > lay.r_cap:
+            raise RuntimeError("more logit rows than the layout holds")
+        host[o["logit_rows"] : o["logit_rows"] + len(rows)] = rows
+        return n, nb, len(rows), max_q, max_ctx
+
+    def _context(self, lay: _Layout, n: int, nb: int, r: int, max_q: int, max_ctx: int, bound: int) -> StepContext:
+        dev, host, o = self._dev, self._host.numpy(), lay.off
+        view = lambda name, size: dev[o[name] : o[name] + size]  # noqa: E731
+        tables, slots = [], []
+        for g in range(self.n_groups):
+            tb = o["tables"] + g * lay.b_cap * lay.width
+            tables.append(dev[tb : tb + nb * lay.width].view(nb, lay.width))
+            sb = o["slots"] + g * lay.n_cap
+            slots.append(dev[sb : sb + n])
+        return StepContext(
+            rt=self.rt,
+            num_tokens=n,
+            num_seqs=nb,
+            token_ids=view("token_ids", n),
+            positions=view("positions", n),
+            query_start_loc=view("qsl", nb + 1),
+            context_lens=view("ctx", nb),
+            state_slots=view("state_slots", nb),
+            logit_rows=view("logit_rows", max(r, 1)),
+            num_logit_rows=r,
+            block_tables=tables,
+            slot_mappings=slots,
+            max_query_len=max_q,
+            max_context_len=max_ctx,
+            block_size=self.block_size,
+            h_query_start_loc=host[o["qsl"] : o["qsl"] + nb + 1].copy(),
+            h_context_lens=host[o["ctx"] : o["ctx"] + nb].copy(),
+            h_state_slots=host[o["state_slots"] : o["state_slots"] + nb].copy(),
+            context_bound=bound,
+        )
+
+    # ------------------------------------------------------------------ running
+    @torch.inference_mode()
+    def step(self, items: Sequence[BatchItem]) -> torch.Tensor:
+        """Run one batch.  Returns float logits ``[R, vocab]`` on the device, rows ordered by
+        item, then by the item's wanted places.  The tensor is a view of a buffer that the
+        next step overwrites."""
+        if not items:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        if self.state_slots is not None:
+            fresh = self.state_slots.take_fresh()
+            if fresh and self._pool is not None:
+                self._pool.clear_state_slots(fresh)
+        single = all(len(it.token_ids) == 1 and it.wanted() == [0] for it in items)
+        if self.cuda_graphs and single and len(items) <= self.graph_buckets[-1]:
+            return self._step_graph(items)
+        n_tok = sum(len(it.token_ids) for it in items)
+        if n_tok > self.rt.max_tokens or len(items) > self.rt.max_seqs:
+            raise ValueError(
+                f"a step of {n_tok} tokens in {len(items)} requests exceeds the runner's limits "
+                f"({self.rt.max_tokens} tokens, {self.rt.max_seqs} requests)"
+            )
+        n_rows = sum(len(it.wanted()) for it in items)
+        width = max(-(-(it.start_pos + len(it.token_ids)) // self.block_size) for it in items)
+        lay = self._layout(n_tok, len(items), width, n_rows)
+        self._ensure(lay.total)
+        n, nb, r, max_q, max_ctx = self._fill(items, lay)
+        self._upload(lay.total)
+        ctx = self._context(lay, n, nb, r, max_q, max_ctx, bound=0)
+        logits = self.model.forward(ctx)
+        self.num_forward_passes += 1
+        self.num_tokens_processed += n
+        return logits[:r]
+
+    _pool = None
+
+    def attach_pool(self, pool) -> None:
+        self._pool = pool
+        self.model.attach_cache(pool.caches)
+
+    def _step_graph(self, items: Sequence[BatchItem]) -> torch.Tensor:
+        nb = len(items)
+        bucket = next(b for b in self.graph_buckets if b >= nb)
+        lay = self._layout(bucket, bucket, self.max_width, bucket)
+        self._ensure(lay.total)
+        # padding tokens of the bucket: token 0 at position 0, written to no slot
+        if self._copy_done is not None:
+            self._copy_done.synchronize()
+        host, o = self._host.numpy(), lay.off
+        host[o["token_ids"] : o["token_ids"] + bucket] = 0
+        host[o["positions"] : o["positions"] + bucket] = 0
+        host[o["logit_rows"] : o["logit_rows"] + bucket] = 0
+        for g in range(self.n_groups):
+            host[o["slots"] + g * bucket : o["slots"] + (g + 1) * bucket] = -1
+        n, _, r, max_q, max_ctx = self._fill(items, lay)
+        self._upload(lay.total)
+        entry = self._graphs.get(bucket)
+        if entry is None:
+            entry = self._capture(bucket, lay)
+        graph, logits = entry
+        graph.replay()
+        self.num_forward_passes += 1
+        self.num_tokens_processed += n
+        return logits[:r]
+
+    def _capture(self, bucket: int, lay: _Layout):
+        ctx = self._context(lay, bucket, bucket, bucket, 1, self.max_model_len, bound=self.max_model_len)
+        # one eager run first: sizes every buffer and loads every kernel outside the capture
+        self.model.forward(ctx)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        self.rt.capturing = True
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+        finally:
+            self.rt.capturing = False
+        self._graphs[bucket] = (graph, logits)
+        return self._graphs[bucket]

@@ -1,0 +1,394 @@
+"""Python faces of the CUDA launchers in ``csrc/`` (loaded through ``native``).
+
+Every function checks device, dtype, layout and size, then launches on torch's current
+stream.  A launcher's non-zero return raises with the kernel's name.  Nothing here has a
+CPU path: a tensor that is not on a CUDA device is an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import native
+
+_SUF = {torch.float32: "f32", torch.bfloat16: "bf16"}
+
+# p = pointer, i = int, l = long long, f = float
+_SIGNATURES = {
+    "kvf_embed_{s}": "pppiiipp",
+    "kvf_add_rmsnorm_{s}": "pppppiifp",
+    "kvf_add_residual_{s}": "pplp",
+    "kvf_rope_cache_{s}": "ppppppiiiiiilpp",
+    "kvf_silu_mul_{s}": "pplip",
+    "kvf_cast_from_float_{s}": "pplp",
+    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiippp",
+    "kvf_gemm_nt_f32": "pppiiiiiip",
+    "kvf_sample_f32": "pliippppppp",
+}
+_CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
+
+_bound: dict[tuple[str, str], object] = {}
+
+
+def _fn(name: str, lib: str = "core", signature: str | None = None):
+    key = (lib, name)
+    f = _bound.get(key)
+    if f is None:
+        cdll = native.load(lib)
+        try:
+            f = getattr(cdll, name)
+        except AttributeError as e:  # pragma: no cover - a build that lacks a symbol
+            raise RuntimeError(f"native library '{lib}' lacks {name}") from e
+        sig = signature
+        if sig is None:
+            for pat, s in _SIGNATURES.items():
+                if pat.format(s="f32") == name or pat.format(s="bf16") == name:
+                    sig = s
+                    break
+        if sig is None:
+            raise RuntimeError(f"no signature known for {name}")
+        f.argtypes = [_CTYPES[c] for c in sig]
+        f.restype = ctypes.c_int
+        _bound[key] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"CUDA launcher {name} failed with cudaError {rc}")
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype | None, what: str, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor (this engine has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{what} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    try:
+        return _SUF[dtype]
+    except KeyError:
+        raise TypeError(f"storage type {dtype} is not supported (float32 or bfloat16)") from None
+
+
+# ------------------------------------------------------------------ elementwise
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torch.Tensor | None = None) -> None:
+    """``resid[n, :] = float(table[ids[n], :])``; ``ids`` int32 ``[N]``, ``resid`` float ``[N, H]``."""
+    s = _suffix(table.dtype)
+    _need(table, None, "table")
+    _need(ids, torch.int32, "ids")
+    _need(resid, torch.float32, "resid")
+    n, h = resid.shape
+    if table.shape[1] != h or ids.numel() < n:
+        raise ValueError("embed: shapes do not agree")
+    name = f"kvf_embed_{s}"
+    _check(_fn(name)(_ptr(table), _ptr(ids), _ptr(resid), n, h, table.shape[0], _ptr(err), _stream()), name)
+
+
+def add_rmsnorm(
+    resid: torch.Tensor,
+    delta: torch.Tensor | None,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    eps: float,
+    rows: torch.Tensor | None = None,
+) -> None:
+    """``v = resid (+ delta)``; ``out = T(v * rsqrt(mean(v^2) + eps) * weight)``.
+
+    Without ``rows`` the sum is written back into ``resid``.  With ``rows`` (int32 ``[R]``)
+    row ``r`` of ``out`` comes from row ``rows[r]`` and ``resid`` is left as it is.
+    """
+    s = _suffix(out.dtype)
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "norm weight")
+    _need(out, None, "out")
+    h = resid.shape[-1]
+    n_rows = out.shape[0]
+    if out.shape[-1] != h or weight.numel() != h:
+        raise ValueError("add_rmsnorm: widths do not agree")
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+        if delta.shape[-1] != h:
+            raise ValueError("add_rmsnorm: delta width")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        if rows.numel() < n_rows:
+            raise ValueError("add_rmsnorm: fewer row indices than output rows")
+    elif resid.shape[0] < n_rows:
+        raise ValueError("add_rmsnorm: fewer residual rows than output rows")
+    name = f"kvf_add_rmsnorm_{s}"
+    _check(
+        _fn(name)(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_rows, h, float(eps), _stream()),
+        name,
+    )
+
+
+def add_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
+    """``resid += float(delta)`` over the first ``delta.numel()`` elements."""
+    s = _suffix(delta.dtype)
+    _need(resid, torch.float32, "resid")
+    _need(delta, None, "delta")
+    if delta.numel() > resid.numel():
+        raise ValueError("add_residual: delta is larger than resid")
+    name = f"kvf_add_residual_{s}"
+    _check(_fn(name)(_ptr(resid), _ptr(delta), delta.numel(), _stream()), name)
+
+
+def rope_cache_write(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor,
+    slots: torch.Tensor | None,
+    kcache: torch.Tensor | None,
+    vcache: torch.Tensor | None,
+    nh: int,
+    nkv: int,
+    d: int,
+    block_size: int,
+    err: torch.Tensor | None = None,
+) -> None:
+    """Rotate q (in place) and k of ``qkv [N, (nh+2nkv)*d]``; write k and v to their slots.
+
+    ``inv_freq`` float ``[rot/2]`` fixes how many leading dims turn (``rot <= d``).
+    ``kcache/vcache``: ``[num_blocks, nkv, block_size, d]``.  ``slots=None`` rotates q only.
+    """
+    s = _suffix(qkv.dtype)
+    _need(qkv, None, "qkv")
+    _need(positions, torch.int32, "positions")
+    _need(inv_freq, torch.float32, "inv_freq")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise ValueError("rope_cache_write: qkv width")
+    rot = 2 * inv_freq.numel()
+    if rot > d:
+        raise ValueError("rope_cache_write: more frequencies than head_dim/2")
+    num_slots = 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots")
+        _need(kcache, qkv.dtype, "kcache")
+        _need(vcache, qkv.dtype, "vcache")
+        if tuple(kcache.shape[1:]) != (nkv, block_size, d) or kcache.shape != vcache.shape:
+            raise ValueError("rope_cache_write: cache shape must be [num_blocks, nkv, block_size, d]")
+        num_slots = kcache.shape[0] * block_size
+    name = f"kvf_rope_cache_{s}"
+    _check(
+        _fn(name)(
+            _ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(kcache), _ptr(vcache),
+            n, nh, nkv, d, rot, block_size, num_slots, _ptr(err), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]`` computed in float."""
+    s = _suffix(gate_up.dtype)
+    _need(gate_up, None, "gate_up")
+    _need(out, gate_up.dtype, "out")
+    n, i2 = gate_up.shape
+    if out.shape[0] != n or out.shape[1] * 2 != i2:
+        raise ValueError("silu_mul: shapes do not agree")
+    name = f"kvf_silu_mul_{s}"
+    _check(_fn(name)(_ptr(gate_up), _ptr(out), n, out.shape[1], _stream()), name)
+
+
+def cast_from_float(src: torch.Tensor, out: torch.Tensor) -> None:
+    s = _suffix(out.dtype)
+    _need(src, torch.float32, "src")
+    _need(out, None, "out")
+    if src.numel() != out.numel():
+        raise ValueError("cast_from_float: sizes differ")
+    name = f"kvf_cast_from_float_{s}"
+    _check(_fn(name)(_ptr(src), _ptr(out), src.numel(), _stream()), name)
+
+
+# ------------------------------------------------------------------ attention
+
+ATTN_SPLIT_SIZE = 256  # keys per range of the decode form; ranges start at multiples of it
+
+
+def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int) -> tuple[tuple[int, ...], tuple[int, ...]]:
+    """Shapes of the float scratch the decode form needs for contexts up to ``max_context``."""
+    splits = max(1, -(-max_context // ATTN_SPLIT_SIZE))
+    return (max_seqs, nh, splits, d), (max_seqs, nh, splits, 2)
+
+
+def check_head_dim(d: int) -> None:
+    if d <= 0 or d % 16 != 0 or d > 256:
+        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 16, at most 256")
+
+
+def paged_attention_generic(
+    q: torch.Tensor,
+    out: torch.Tensor,
+    kcache: torch.Tensor,
+    vcache: torch.Tensor,
+    block_tables: torch.Tensor,
+    qsl: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    num_seqs: int,
+    max_q_len: int,
+    nh: int,
+    nkv: int,
+    d: int,
+    scale: float,
+    window: int = 0,
+    q_stride: int | None = None,
+    scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+    max_context: int | None = None,
+) -> None:
+    """Paged GQA attention of a flat batch (see ``csrc/attention_generic.cu`` for the contract).
+
+    ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
+    ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form
+    runs: key ranges in parallel, then a merge; ``max_context`` bounds the contexts.
+    """
+    s = _suffix(q.dtype)
+    check_head_dim(d)
+    _need(q, None, "q")
+    _need(out, q.dtype, "out")
+    _need(kcache, q.dtype, "kcache")
+    _need(vcache, q.dtype, "vcache")
+    _need(block_tables, torch.int32, "block_tables")
+    _need(qsl, torch.int32, "query_start_loc")
+    _need(ctx_lens, torch.int32, "context_lens")
+    if kcache.dim() != 4 or kcache.shape[1] != nkv or kcache.shape[3] != d or kcache.shape != vcache.shape:
+        raise ValueError("paged_attention: cache shape must be [num_blocks, nkv, block_size, d]")
+    block_size = kcache.shape[2]
+    if q_stride is None:
+        q_stride = q.shape[-1]
+    bt_stride = block_tables.shape[-1] if block_tables.dim() == 2 else block_tables.numel() // max(1, num_seqs)
+    split, max_splits, pa, pm = 0, 0, None, None
+    if scratch is not None:
+        pa, pm = scratch
+        _need(pa, torch.float32, "scratch acc")
+        _need(pm, torch.float32, "scratch ml")
+        if max_q_len != 1:
+            raise ValueError("the decode form needs one query per sequence")
+        split = ATTN_SPLIT_SIZE
+        max_splits = pa.shape[2]
+        if pa.shape[0] < num_seqs or pa.shape[1] != nh or pa.shape[3] != d:
+            raise ValueError("paged_attention: scratch shape does not fit")
+        if max_context is None or -(-max_context // split) > max_splits:
+            raise ValueError("paged_attention: scratch is too small for the longest context")
+    name = f"kvf_paged_attention_generic_{s}"
+    _check(
+        _fn(name)(
+            _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
+            num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
+            int(window), split, max_splits, _ptr(pa), _ptr(pm), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+# ------------------------------------------------------------------ matrix products
+
+
+def gemm_nt_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M, N] = a[M, K] @ w[N, K]^T`` on the FP32 pipes (no tensor cores).  Row strides
+    may exceed the widths (views of wider buffers)."""
+    for t, what in ((a, "a"), (w, "w"), (out, "out")):
+        _need(t, torch.float32, what, contiguous=False)
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"gemm_nt_f32: {what} must be 2-D with unit inner stride")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n):
+        raise ValueError("gemm_nt_f32: shapes do not agree")
+    name = "kvf_gemm_nt_f32"
+    _check(
+        _fn(name)(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), w.stride(0), out.stride(0), _stream()),
+        name,
+    )
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = x @ w^T`` for ``x [M, K]``, ``w [N, K]``.
+
+    float32: the engine's own FFMA kernel (true 32-bit).  bfloat16 inputs: cuBLAS through
+    ``torch.mm`` with 32-bit accumulation, the library product that umarhassan-cloud/kvforge
+    itself uses (``nn.Linear``, src/tokenvault/model.py:70-73); ``out`` may be bfloat16 or
+    float32.
+    """
+    if x.dtype == torch.float32:
+        gemm_nt_f32(x, w, out)
+        return
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(w, torch.bfloat16, "w", contiguous=False)
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        raise TypeError("linear: out must be bfloat16 or float32")
+
+
+# ------------------------------------------------------------------ sampling
+
+
+def sample(
+    logits: torch.Tensor,
+    out_tokens: torch.Tensor,
+    temps: torch.Tensor | None = None,
+    top_ks: torch.Tensor | None = None,
+    top_ps: torch.Tensor | None = None,
+    rand_keys: torch.Tensor | None = None,
+    probs_out: torch.Tensor | None = None,
+) -> None:
+    """One token per row of float ``logits [R, V]``.  ``temps=None`` is greedy for all rows.
+    ``rand_keys`` int64 ``[R]``: the draw of a row depends on its key alone."""
+    _need(logits, torch.float32, "logits", contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("sample: logits must be [R, V] with unit inner stride")
+    r, v = logits.shape
+    _need(out_tokens, torch.int32, "out_tokens")
+    if out_tokens.numel() < r:
+        raise ValueError("sample: out_tokens is too short")
+    for t, dt, what in (
+        (temps, torch.float32, "temps"),
+        (top_ks, torch.int32, "top_ks"),
+        (top_ps, torch.float32, "top_ps"),
+        (rand_keys, torch.int64, "rand_keys"),
+    ):
+        if t is not None:
+            _need(t, dt, what)
+            if t.numel() < r:
+                raise ValueError(f"sample: {what} is too short")
+    if probs_out is not None:
+        _need(probs_out, torch.float32, "probs_out")
+        if tuple(probs_out.shape) != (r, v):
+            raise ValueError("sample: probs_out shape")
+    name = "kvf_sample_f32"
+    _check(
+        _fn(name)(
+            _ptr(logits), logits.stride(0), r, v, _ptr(temps), _ptr(top_ks), _ptr(top_ps), _ptr(rand_keys),
+            _ptr(out_tokens), _ptr(probs_out), _stream(),
+        ),
+        name,
+    )  # fmt: skip
+
+
+def splitmix64(z: int) -> int:
+    """The host twin of the device generator (``csrc/sampling.cu``): the 64-bit value whose
+    high-multiply with the total mass picks the token."""
+    m = (1 << 64) - 1
+    z = (z + 0x9E3779B97F4A7C15) & m
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+    return z ^ (z >> 31)

@@ -1,0 +1,16 @@
+"""The parts a model is put together from.  Importing the package registers the built-in
+ones (rotary encoding, RMSNorm, paged attention, gated feed-forward, pre-norm block)."""
+
+from . import attention, block, mlp, norm, rope  # noqa: F401  (registration)
+from .base import (  # noqa: F401
+    CacheNeed,
+    LayerCache,
+    PartSpec,
+    WeightDecl,
+    register_block,
+    register_feed_forward,
+    register_mixer,
+    register_norm,
+    register_position_encoding,
+)
+from .model import DecoderModel, LayerCall, LayerSpec, ModelSpec  # noqa: F401

@@ -1,0 +1,115 @@
+"""Grouped-query attention over the paged cache (the mixer of the Llama decoder).
+
+What it computes is umarhassan-cloud/kvforge's ``Attention.forward``
+(src/tokenvault/model.py:77-92): bias-free q/k/v projections, rotation of q and k, the step's
+k and v written to their slots *before* attention reads the cache, causal attention over
+the block table (src/tokenvault/cache/paged_attention.py:66-91), output projection.
+The three input projections are one product here (their weights are stacked at load).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from .base import CacheNeed, Mixer, PartSpec, WeightDecl, build_part, register_mixer
+
+
+@register_mixer("paged_attention")
+class PagedAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``; optional
+    ``position`` (a position-encoding ``PartSpec`` or ``None``), ``window`` (keys a query
+    sees, itself included; ``None`` = all) and ``scale`` (default ``1/sqrt(head_dim)``)."""
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.nh = int(params["num_heads"])
+        self.nkv = int(params["num_kv_heads"])
+        self.d = int(params["head_dim"])
+        if self.nkv <= 0 or self.nh % self.nkv:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        ops.check_head_dim(self.d)
+        self.window = params.get("window")
+        if self.window is not None and int(self.window) <= 0:
+            raise ValueError("window must be positive")
+        self.scale = float(params.get("scale") or 1.0 / math.sqrt(self.d))  # model.py:74
+        pos = params.get("position")
+        if isinstance(pos, dict):
+            pos = PartSpec(pos["kind"], pos.get("params", {}))
+        self.position_spec: PartSpec | None = pos
+        self.position = None  # shared instance, set by the model before bind
+        self.q_dim = self.nh * self.d
+        self.qkv_dim = (self.nh + 2 * self.nkv) * self.d
+
+    @classmethod
+    def weight_decls(cls, params):
+        h, nh, nkv, d = (int(params[k]) for k in ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
+        return {
+            "q_proj.weight": WeightDecl((nh * d, h)),
+            "k_proj.weight": WeightDecl((nkv * d, h)),
+            "v_proj.weight": WeightDecl((nkv * d, h)),
+            "o_proj.weight": WeightDecl((h, nh * d)),
+        }
+
+    def cache_need(self) -> CacheNeed:
+        if self.window is None:
+            return CacheNeed("full", self.nkv, self.d, None)
+        return CacheNeed("window", self.nkv, self.d, int(self.window))
+
+    def bind(self, weights, rt):
+        super().bind(weights, rt)
+        self.w_qkv = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0).contiguous()
+        self.w_o = weights["o_proj.weight"].contiguous()
+        if self.position_spec is not None and self.position is None:
+            self.position = build_part("position", self.position_spec)
+            self.position.bind({}, rt)
+        if self.position is not None:
+            self.inv_freq = self.position.table()
+        else:
+            self.inv_freq = torch.empty(0, dtype=torch.float32, device=rt.device)
+
+    def _scratch(self, ctx):
+        rt = self.rt
+        bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
+        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound)
+        acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32).view(sa)
+        ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32).view(sm)
+        return (acc, ml), bound
+
+    def forward(self, ctx, x: torch.Tensor, cache) -> torch.Tensor:
+        rt = self.rt
+        n = x.shape[0]
+        if cache is None:
+            raise RuntimeError("paged_attention needs a cache")
+        if cache.writable:
+            qkv = rt.buf("attn.qkv", n, self.qkv_dim)
+            ops.linear(x, self.w_qkv, qkv)
+            ops.rope_cache_write(
+                qkv, ctx.positions, self.inv_freq, ctx.slot_mappings[cache.group], cache.k, cache.v,
+                self.nh, self.nkv, self.d, ctx.block_size, rt.err,
+            )  # fmt: skip
+            q, q_stride = qkv, self.qkv_dim
+        else:
+            # reads another call's keys and values: only the queries are needed
+            q = rt.buf("attn.q", n, self.q_dim)
+            ops.linear(x, self.w_qkv[: self.q_dim], q)
+            ops.rope_cache_write(q, ctx.positions, self.inv_freq, None, None, None, self.nh, 0, self.d, ctx.block_size)
+            q_stride = self.q_dim
+        out = rt.buf("attn.out", n, self.q_dim)
+        self.attend(ctx, q, q_stride, out, cache)
+        y = rt.buf("attn.proj", n, self.hidden)
+        ops.linear(out, self.w_o, y)
+        return y
+
+    def attend(self, ctx, q, q_stride, out, cache) -> None:
+        scratch, bound = (None, None)
+        if ctx.all_single_query:
+            scratch, bound = self._scratch(ctx)
+        ops.paged_attention_generic(
+            q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens,
+            ctx.num_seqs, ctx.max_query_len, self.nh, self.nkv, self.d, self.scale,
+            window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound,
+        )  # fmt: skip
