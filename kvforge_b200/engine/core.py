@@ -53,6 +53,7 @@ class EngineCore:
         max_num_batched_tokens: int = 2048,
         max_model_len: int = 2048,
         cuda_graphs: bool = False,
+        lazy_buffers: bool = False,
     ) -> None:
         if not torch.cuda.is_available():
             raise RuntimeError("kvforge_b200 needs a CUDA device: there is no CPU path")
@@ -62,7 +63,7 @@ class EngineCore:
         self.max_model_len = int(max_model_len)
         cache = cache or CacheConfig()
         self.model = DecoderModel(spec)
-        self.rt = Runtime(self.device, self.dtype, max_num_batched_tokens, max_num_seqs, self.max_model_len)
+        self.rt = Runtime(self.device, self.dtype, max_num_batched_tokens, max_num_seqs, self.max_model_len, lazy=lazy_buffers)
         expected = self.model.expected_weights()
         if model_dir is not None:
             weights = load_weights(model_dir, expected, self.dtype, self.device, spec.ignore_suffixes)

@@ -14,7 +14,7 @@ class Runtime:
     the life of the runtime, so that the same addresses are used every step (a captured
     CUDA graph can be replayed) and no step allocates."""
 
-    def __init__(self, device: str | torch.device, dtype: torch.dtype, max_tokens: int, max_seqs: int, max_model_len: int = 0) -> None:
+    def __init__(self, device: str | torch.device, dtype: torch.dtype, max_tokens: int, max_seqs: int, max_model_len: int = 0, lazy: bool = False) -> None:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("kvforge_b200 runs on a CUDA device only (there is no CPU path)")
@@ -22,6 +22,8 @@ class Runtime:
         self.max_tokens = int(max_tokens)
         self.max_seqs = int(max_seqs)
         self.max_model_len = int(max_model_len)
+        # lazy: a buffer is made for the rows asked for (rounded up), not for the whole token budget
+        self.lazy = bool(lazy)
         self._buffers: dict[tuple, torch.Tensor] = {}
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.capturing = False
@@ -36,7 +38,10 @@ class Runtime:
         if t is None or t.shape[0] < rows:
             if self.capturing:
                 raise RuntimeError(f"buffer {name} would have to grow during graph capture")
-            cap = max(rows, self.max_tokens if cap is None else cap)
+            if self.lazy:
+                cap = 1 << max(4, (max(rows, 1) - 1).bit_length())
+            else:
+                cap = max(rows, self.max_tokens if cap is None else cap)
             t = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self._buffers[key] = t
         return t[:rows]

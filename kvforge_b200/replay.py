@@ -1,0 +1,118 @@
+"""Trace replay: feeds given token ids through a model step by step and writes logits.
+
+It samples nothing and has no forward pass, cache or loader of its own: it drives
+``EngineCore`` (the model, step function, page allocator and kernels that generation uses).
+The nearest thing in umarhassan-cloud/kvforge is the test that drives ``ModelRunner.execute``
+with explicit batch items (tests/test_paged_attention.py:93-113).
+
+Input, one JSON object a line on standard input::
+
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
+
+``entries``: for each request its next tokens and the places among them whose logits are
+wanted.  All entries of a step run as one batch.  ``end``: requests that are finished after
+the step; their pages are given back.  A step with wanted places writes
+``<out>/<step>.f32``: little-endian float32 ``[wanted, vocab]`` in the order of the entries
+and of ``want``.  After every step ``done <step>`` is printed and flushed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+PAGE = 16  # tokens per page of the replay engine
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(prog="trace_run", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
+    ap.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
+    ap.add_argument("--max-live", type=int, default=16, help="most requests live at a time")
+    return ap.parse_args(argv)
+
+
+class TraceRunner:
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, max_live: int = 16) -> None:
+        from .config.engine_config import CacheConfig
+        from .engine.core import EngineCore
+
+        num_blocks = max(1, -(-int(max_tokens) // PAGE))
+        budget = num_blocks * PAGE
+        self.core = EngineCore.from_model_dir(
+            model_dir,
+            dtype=dtype,
+            cache=CacheConfig(block_size=PAGE, num_blocks=num_blocks, watermark=0.0),
+            max_num_seqs=max_live,
+            max_num_batched_tokens=budget,
+            max_model_len=budget,
+            cuda_graphs=False,
+            lazy_buffers=True,
+        )
+        self.lengths: dict[str, int] = {}
+
+    def step(self, record: dict):
+        """Runs one step; returns the float logits ``[wanted, vocab]`` on the host, or ``None``."""
+        from .engine.step import BatchItem
+
+        core = self.core
+        bm, slots = core.block_manager, core.state_slots
+        vocab = core.spec.vocab_size
+        items = []
+        for e in record.get("entries", []):
+            rid, tokens = str(e["id"]), [int(t) for t in e["tokens"]]
+            if not tokens:
+                continue
+            if any(t < 0 or t >= vocab for t in tokens):
+                raise ValueError(f"step {record.get('step')}: request {rid} has a token id outside the vocabulary of {vocab}")
+            start = self.lengths.get(rid, 0)
+            total = start + len(tokens)
+            if rid not in self.lengths:
+                bm.allocate(rid, total, len(tokens))
+                slots.allocate(rid)
+            else:
+                bm.append_slots(rid, total, start)
+            self.lengths[rid] = total
+            items.append(BatchItem(rid, tokens, start, [int(i) for i in e.get("want", [])]))
+        logits = core.runner.step(items) if items else None
+        host = None
+        if logits is not None and logits.shape[0] > 0:
+            host = logits.cpu()
+        elif logits is not None:
+            import torch
+
+            torch.cuda.current_stream().synchronize()
+        if items:
+            core.rt.check_error_flag()
+        for rid in record.get("end", []):
+            rid = str(rid)
+            bm.free(rid)
+            slots.free(rid)
+            self.lengths.pop(rid, None)
+        return host
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    out = Path(args.out)
+    out.mkdir(parents=True, exist_ok=True)
+    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.max_live)
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        record = json.loads(line)
+        step = record["step"]
+        logits = runner.step(record)
+        if logits is not None:
+            logits.numpy().astype("<f4", copy=False).tofile(out / f"{step}.f32")
+        print(f"done {step}", flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

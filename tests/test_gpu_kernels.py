@@ -1,0 +1,330 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's
+tiny models use: widths and vocabularies that are no power of two, odd head counts, every
+head size in steps of 16, pages of several sizes."""
+
+from __future__ import annotations
+
+import math
+import random
+
+import pytest
+import torch
+
+from plain_llama import apply_rope, causal_attention, plain_inv_freq, processed_probs, rms_norm, rope_cos_sin
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from kvforge_b200 import ops as o
+
+    return o
+
+
+def dev(t, dtype=None):
+    return t.to(device="cuda", dtype=dtype or t.dtype).contiguous()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(ops, dtype):
+    table = torch.randn(37, 100).to(dtype)
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32)
+    out = torch.empty(5, 100, device="cuda")
+    ops.embed(dev(table), dev(ids), out)
+    assert torch.equal(out.cpu(), table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("h", [24, 100, 1000, 5120])
+def test_add_rmsnorm(ops, dtype, h):
+    n = 7
+    resid = torch.randn(n, h) * 3
+    delta = (torch.randn(n, h)).to(dtype)
+    w = torch.rand(h) + 0.5
+    r = dev(resid)
+    out = torch.empty(n, h, device="cuda", dtype=dtype)
+    ops.add_rmsnorm(r, dev(delta), dev(w), out, 1e-5)
+    summed = resid + delta.float()
+    assert torch.allclose(r.cpu(), summed, atol=1e-6)
+    ref = rms_norm(summed, w, 1e-5)
+    assert torch.allclose(out.float().cpu(), ref, rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+    # gathered rows (a row twice), with a pending sum that must not be written back
+    rows = torch.tensor([6, 0, 6], dtype=torch.int32)
+    r2 = dev(resid)
+    out2 = torch.empty(3, h, device="cuda", dtype=dtype)
+    ops.add_rmsnorm(r2, dev(delta), dev(w), out2, 1e-5, rows=dev(rows))
+    assert torch.equal(r2.cpu(), resid)
+    assert torch.allclose(out2.float().cpu(), ref[rows.long()], rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+    # no pending sum
+    ops.add_rmsnorm(r2, None, dev(w), out, 1e-6)
+    assert torch.allclose(out.float().cpu(), rms_norm(resid, w, 1e-6), rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    gu = (torch.randn(5, 2 * 93) * 3).to(dtype)
+    out = torch.empty(5, 93, device="cuda", dtype=dtype)
+    ops.silu_mul(dev(gu), out)
+    g, u = gu[:, :93].float(), gu[:, 93:].float()
+    ref = torch.nn.functional.silu(g) * u
+    assert torch.allclose(out.float().cpu(), ref, rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 100, 33), (7, 64, 64), (130, 203, 80), (65, 3, 1000)])
+def test_gemm_f32_is_true_float32(ops, m, n, k):
+    a, w = torch.randn(m, k), torch.randn(n, k)
+    out = torch.empty(m, n, device="cuda")
+    ops.gemm_nt_f32(dev(a), dev(w), out)
+    ref = (a.double() @ w.double().t())
+    # float32 accumulation error grows like sqrt(k) * 2^-24; tf32 or bfloat16 inputs would be ~1e-3
+    assert float((out.cpu().double() - ref).abs().max()) < 2e-6 * math.sqrt(k) * float(ref.abs().max())
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch(ops):
+    a, w = torch.randn(200, 96), torch.randn(150, 96)
+    full = torch.empty(200, 150, device="cuda")
+    ops.gemm_nt_f32(dev(a), dev(w), full)
+    one = torch.empty(1, 150, device="cuda")
+    ops.gemm_nt_f32(dev(a[137:138]), dev(w), one)
+    assert torch.equal(one[0], full[137])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot,bs", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 24, 4), (5, 5, 128, 128, 32)])
+def test_rope_and_cache_write(ops, dtype, nh, nkv, d, rot, bs):
+    n, nb = 11, 9
+    qkv = torch.randn(n, (nh + 2 * nkv) * d).to(dtype)
+    positions = torch.tensor([0, 1, 2, 63, 64, 65, 1000, 4095, 4096, 7, 8], dtype=torch.int32)
+    inv = plain_inv_freq(rot, 500000.0)
+    slots = torch.tensor(random.Random(1).sample(range(nb * bs), n), dtype=torch.int32)
+    kc = torch.zeros(nb, nkv, bs, d, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    x = dev(qkv)
+    ops.rope_cache_write(x, dev(positions), dev(inv), dev(slots), kc, vc, nh, nkv, d, bs)
+    cos, sin = rope_cos_sin(positions, inv)
+
+    def rotated(t):  # [n, heads, d]; only the first `rot` dims turn
+        return torch.cat([apply_rope(t[..., :rot], cos, sin), t[..., rot:]], dim=-1)
+
+    q = qkv[:, : nh * d].view(n, nh, d)
+    k = qkv[:, nh * d : (nh + nkv) * d].view(n, nkv, d)
+    v = qkv[:, (nh + nkv) * d :].view(n, nkv, d)
+    t = tol(dtype) * 8
+    assert torch.allclose(x[:, : nh * d].float().cpu().view(n, nh, d), rotated(q).float(), rtol=t, atol=t)
+    kc_flat = kc.float().cpu().permute(0, 2, 1, 3).reshape(nb * bs, nkv, d)
+    vc_flat = vc.float().cpu().permute(0, 2, 1, 3).reshape(nb * bs, nkv, d)
+    assert torch.allclose(kc_flat[slots.long()], rotated(k).float(), rtol=t, atol=t)
+    assert torch.equal(vc_flat[slots.long()], v.float())
+    untouched = torch.ones(nb * bs, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert (kc_flat[untouched] == 0).all() and (vc_flat[untouched] == 0).all()
+
+
+# ------------------------------------------------------------------ attention
+
+
+def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5):
+    """Scatter per-sequence [ctx, nkv, d] keys/values into shuffled pages; stale pages hold junk."""
+    rng = random.Random(seed)
+    need = [-(-k.shape[0] // bs) for k, _ in kv_per_seq]
+    nb = sum(need) + extra_blocks
+    order = list(range(nb))
+    rng.shuffle(order)
+    kc = torch.full((nb, nkv, bs, d), 1e4).to(dtype)  # junk that would show if it were read
+    vc = torch.full((nb, nkv, bs, d), -1e4).to(dtype)
+    width = max(need)
+    tables = torch.zeros(len(kv_per_seq), width, dtype=torch.int32)
+    for s, (k, v) in enumerate(kv_per_seq):
+        for j in range(need[s]):
+            blk = order.pop()
+            tables[s, j] = blk
+            part = slice(j * bs, min((j + 1) * bs, k.shape[0]))
+            m = part.stop - part.start
+            kc[blk, :, :m] = k[part].transpose(0, 1).to(dtype)
+            vc[blk, :, :m] = v[part].transpose(0, 1).to(dtype)
+    return kc, vc, tables
+
+
+def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None):
+    g = torch.Generator().manual_seed(seed)
+    kv = [(torch.randn(c, nkv, d, generator=g).to(dtype), torch.randn(c, nkv, d, generator=g).to(dtype)) for c in ctx_lens]
+    qs = [torch.randn(ql, nh, d, generator=g).to(dtype) for ql in q_lens]
+    if craft:
+        craft(kv, qs)
+    kc, vc, tables = paged(kv, nkv, d, bs, dtype, seed)
+    q = torch.cat(qs, 0).reshape(-1, nh * d)
+    qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    out = torch.full((q.shape[0], nh * d), float("nan"), device="cuda", dtype=dtype)
+    scale = 1.0 / math.sqrt(d)
+    scratch, bound = None, None
+    if decode_form:
+        bound = max(ctx_lens)
+        sa, sm = ops.attention_scratch_shapes(len(ctx_lens), nh, d, bound)
+        scratch = (torch.full(sa, float("nan"), device="cuda"), torch.full(sm, float("nan"), device="cuda"))
+    ops.paged_attention_generic(
+        dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
+        len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
+    )  # fmt: skip
+    refs = []
+    for (k, v), qq, c, ql in zip(kv, qs, ctx_lens, q_lens):
+        full_q = torch.zeros(c, nh, d, dtype=dtype)
+        full_q[c - ql :] = qq
+        refs.append(causal_attention(full_q.float(), k.float(), v.float(), scale, window or None)[c - ql :])
+    ref = torch.cat(refs, 0).reshape(-1, nh * d)
+    return out.float().cpu(), ref, kv
+
+
+SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 4), (8, 2, 64, 16), (5, 5, 80, 32), (32, 1, 128, 16), (2, 2, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,bs", SHAPES)
+@pytest.mark.parametrize(
+    "ctx_lens,q_lens",
+    [([7, 13, 1, 20], [1, 1, 1, 1]), ([9, 16], [9, 16]), ([12, 30, 5], [4, 7, 5]), ([17, 3, 25, 130], [1, 3, 5, 67])],
+)
+def test_paged_attention_generic(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens):
+    out, ref, _ = run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens)
+    t = 1e-5 if dtype == torch.float32 else 2e-2
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out, ref, rtol=t, atol=t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,bs", [(4, 2, 16, 16), (6, 3, 48, 4), (8, 2, 64, 16), (24, 1, 32, 8)])
+def test_paged_attention_decode_form(ops, dtype, nh, nkv, d, bs):
+    ctx = [700, 1, 256, 257, 33]
+    out, ref, _ = run_attention(ops, dtype, nh, nkv, d, bs, ctx, [1] * 5, decode_form=True)
+    t = 1e-5 if dtype == torch.float32 else 2e-2
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out, ref, rtol=t, atol=t)
+
+
+@pytest.mark.parametrize("decode_form", [False, True])
+def test_attention_finds_a_far_key_among_hundreds(ops, decode_form):
+    """Random scores are near uniform and would hide a key that is skipped: one far key is
+    made to take all the weight, at a page's first and last place and across a range edge."""
+    for far in (0, 15, 16, 255, 256, 511, 640):
+
+        def craft(kv, qs, far=far):
+            k, v = kv[0]
+            k.mul_(0.01)
+            k[far, :, 0] = 40.0
+            qs[0][-1, :, 0] = 40.0
+
+        out, ref, kv = run_attention(ops, torch.float32, 4, 2, 32, 16, [700], [1], decode_form=decode_form, craft=craft)
+        v_far = kv[0][1][far].float().repeat_interleave(2, dim=0).reshape(-1)
+        assert torch.allclose(out[-1], v_far, atol=1e-3), far
+        assert torch.allclose(out, ref, atol=1e-5), far
+
+
+@pytest.mark.parametrize("decode_form", [False, True])
+@pytest.mark.parametrize("window", [1, 5, 32, 33, 100])
+def test_attention_window_edge(ops, window, decode_form):
+    """The key just inside the window is seen, the one just outside is not."""
+    ctx = 300
+    for offset, seen in ((window - 1, True), (window, False)):
+        far = ctx - 1 - offset
+
+        def craft(kv, qs, far=far):
+            k, v = kv[0]
+            k.mul_(0.01)
+            k[far, :, 0] = 40.0
+            qs[0][-1, :, 0] = 40.0
+
+        q_lens = [1] if decode_form else [9]
+        out, ref, kv = run_attention(ops, torch.float32, 2, 1, 16, 8, [ctx], q_lens, window=window, decode_form=decode_form, craft=craft)
+        assert torch.allclose(out, ref, atol=1e-5), (window, offset)
+        v_far = kv[0][1][far].float().repeat(2, 1).reshape(-1)
+        assert torch.allclose(out[-1], v_far, atol=1e-3) == seen, (window, offset)
+
+
+def test_attention_rows_do_not_depend_on_the_cut(ops):
+    """A query's output is bit-identical whether it comes alone, in a portion, or in the whole prompt."""
+    nh, nkv, d, bs, ctx = 6, 3, 48, 4, 97
+    whole, _, _ = run_attention(ops, torch.float32, nh, nkv, d, bs, [ctx], [ctx], seed=4)
+    # same seed -> same keys and values; the queries are drawn after them, so rebuild the tail from `whole`'s inputs
+    g = torch.Generator().manual_seed(4)
+    k = torch.randn(ctx, nkv, d, generator=g)
+    v = torch.randn(ctx, nkv, d, generator=g)
+    q = torch.randn(ctx, nh, d, generator=g)
+    for ql in (1, 2, 30):
+        kc, vc, tables = paged([(k, v)], nkv, d, bs, torch.float32, seed=ql)
+        out = torch.empty(ql, nh * d, device="cuda")
+        ops.paged_attention_generic(
+            dev(q[ctx - ql :].reshape(ql, -1)), out, dev(kc), dev(vc), dev(tables), dev(torch.tensor([0, ql], dtype=torch.int32)),
+            dev(torch.tensor([ctx], dtype=torch.int32)), 1, ql, nh, nkv, d, 1.0 / math.sqrt(d),
+        )  # fmt: skip
+        assert torch.equal(out.cpu(), whole[ctx - ql :]), ql
+
+
+def test_head_dim_is_checked(ops):
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.check_head_dim(40)
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.check_head_dim(512)
+
+
+# ------------------------------------------------------------------ sampling
+
+
+def test_greedy_is_argmax_with_lowest_index_on_ties(ops):
+    logits = torch.randn(6, 1003)
+    logits[2, 77] = logits[2, 500] = 9.0
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), out)
+    want = logits.argmax(-1)
+    want[2] = 77
+    assert out.cpu().tolist() == want.tolist()
+
+
+@pytest.mark.parametrize("v", [5, 320, 1003, 128256])
+def test_sampling_distribution_matches_the_formula(ops, v):
+    g = torch.Generator().manual_seed(v)
+    logits = torch.randn(8, v, generator=g) * 3
+    cases = [(1.0, 0, 1.0), (0.8, 0, 1.0), (1.0, 3, 1.0), (1.0, 0, 0.9), (0.7, 50, 0.5), (2.0, 1, 1.0), (0.0, 0, 1.0), (1.3, 0, 0.01)]
+    temps = torch.tensor([c[0] for c in cases])
+    ks = torch.tensor([c[1] for c in cases], dtype=torch.int32)
+    ps = torch.tensor([c[2] for c in cases])
+    keys = torch.arange(8, dtype=torch.int64) + 12345
+    out = torch.empty(8, dtype=torch.int32, device="cuda")
+    probs = torch.empty(8, v, device="cuda")
+    ops.sample(dev(logits), out, dev(temps), dev(ks), dev(ps), dev(keys), probs)
+    probs = probs.cpu()
+    for i, (t, k, p) in enumerate(cases):
+        ref = processed_probs(logits[i], t, k, p)
+        # masses are 2^-40 fixed point relative to the largest: what is kept and not vanishingly
+        # small must be kept, and nothing that the formula removes may be kept
+        assert not ((probs[i] > 0) & (ref == 0)).any(), i
+        assert not ((probs[i] == 0) & (ref > 1e-11)).any(), (i, int((probs[i] > 0).sum()), int((ref > 0).sum()))
+        assert torch.allclose(probs[i], ref, atol=2e-6, rtol=1e-4), i
+        # the draw is the inverse CDF in index order at u = splitmix64(key) / 2^64
+        u = ops.splitmix64(int(keys[i])) / 2.0**64
+        cdf = ref.double().cumsum(0)
+        want = int(torch.searchsorted(cdf, torch.tensor(u * float(cdf[-1]), dtype=torch.float64), right=True))
+        tok = int(out[i])
+        assert ref[tok] > 0
+        if tok != want:  # only a draw that lands within rounding of a CDF step may differ
+            lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+            assert min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (i, tok, want)
+
+
+def test_sampling_is_reproducible_and_follows_the_distribution(ops):
+    logits = torch.tensor([[2.0, 1.0, 0.5, -1.0, 0.0]]).repeat(4000, 1)
+    temps = torch.full((4000,), 0.8)
+    keys = torch.arange(4000, dtype=torch.int64) * 7919
+    out1 = torch.empty(4000, dtype=torch.int32, device="cuda")
+    out2 = torch.empty(4000, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), out1, dev(temps), None, None, dev(keys))
+    ops.sample(dev(logits), out2, dev(temps), None, None, dev(keys))
+    assert torch.equal(out1, out2)
+    freq = torch.bincount(out1.cpu().long(), minlength=5).double() / 4000
+    ref = torch.softmax(logits[0].double() / 0.8, -1)
+    assert float((freq - ref).abs().max()) < 0.03
