@@ -266,8 +266,10 @@ def processed_probs(
 ) -> torch.Tensor:
     """src/tokenvault/sampling.py:40-66 for one row: the distribution a token is drawn from.
     Temperature 0 gives the one-hot of the argmax; top-k keeps ranks ``< k``; top-p keeps the
-    entries whose mass *before* them in descending order is ``< top_p``."""
-    logits = logits.float()
+    entries whose mass *before* them in descending order is ``< top_p``.  A float64 input is
+    kept in float64 (the running sum over a large vocabulary is then free of rounding)."""
+    if logits.dtype != torch.float64:
+        logits = logits.float()
     if temperature == 0.0:
         out = torch.zeros_like(logits)
         out[logits.argmax()] = 1.0

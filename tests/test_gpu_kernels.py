@@ -299,12 +299,14 @@ def test_sampling_distribution_matches_the_formula(ops, v):
     ops.sample(dev(logits), out, dev(temps), dev(ks), dev(ps), dev(keys), probs)
     probs = probs.cpu()
     for i, (t, k, p) in enumerate(cases):
-        ref = processed_probs(logits[i], t, k, p)
-        # masses are 2^-40 fixed point relative to the largest: what is kept and not vanishingly
-        # small must be kept, and nothing that the formula removes may be kept
-        assert not ((probs[i] > 0) & (ref == 0)).any(), i
-        assert not ((probs[i] == 0) & (ref > 1e-11)).any(), (i, int((probs[i] > 0).sum()), int((ref > 0).sum()))
-        assert torch.allclose(probs[i], ref, atol=2e-6, rtol=1e-4), i
+        # The formula in float64: over 128k entries a float32 running sum moves the top-p cut
+        # by a few entries.  What may differ from exact arithmetic: entries whose mass is
+        # below the 2^-40 fixed point, and entries that sit exactly on the cut.
+        ref = processed_probs(logits[i].double(), t, k, p)
+        differ = (probs[i] > 0) != (ref > 0)
+        assert float(ref[differ].sum()) + float(probs[i][differ].sum()) < 1e-5, (i, int(differ.sum()))
+        assert torch.allclose(probs[i].double()[~differ], ref[~differ], atol=2e-6, rtol=1e-4), i
+        ref = ref.float()
         # the draw is the inverse CDF in index order at u = splitmix64(key) / 2^64
         u = ops.splitmix64(int(keys[i])) / 2.0**64
         cdf = ref.double().cumsum(0)

@@ -1,0 +1,321 @@
+"""Each part alone against the plain function it stands for; a model whose execution list
+names a layer twice and lets a layer read another's cache; attention with a window; and a
+toy mixer with state of its own, defined here, registered, built and stepped without any
+change to the framework's files."""
+
+from __future__ import annotations
+
+import json
+import math
+
+import pytest
+import torch
+
+import traces
+from helpers import TINY, make_model_dir, random_tokens, rel_err
+from plain_llama import PlainLlama, causal_attention, apply_rope, linear, plain_inv_freq, rms_norm, rope_cos_sin, swiglu
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 1e-5 if dtype == torch.float32 else 2.5e-2
+
+
+def runtime(dtype, max_tokens=256):
+    from kvforge_b200.engine.runtime import Runtime
+
+    return Runtime("cuda", dtype, max_tokens, 8, 512)
+
+
+def context(rt, seq_lens, starts, block_size, tables, slots):
+    """A StepContext for hand-made batches: sequence i brings seq_lens[i] tokens from starts[i]."""
+    from kvforge_b200.engine.runtime import StepContext
+    import numpy as np
+
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    positions = [p for n, s in zip(seq_lens, starts) for p in range(s, s + n)]
+    qsl = [0]
+    for n in seq_lens:
+        qsl.append(qsl[-1] + n)
+    ctx_lens = [s + n for n, s in zip(seq_lens, starts)]
+    return StepContext(
+        rt=rt, num_tokens=sum(seq_lens), num_seqs=len(seq_lens), token_ids=i32([0] * sum(seq_lens)), positions=i32(positions),
+        query_start_loc=i32(qsl), context_lens=i32(ctx_lens), state_slots=i32(list(range(len(seq_lens)))), logit_rows=i32([0]),
+        num_logit_rows=0, block_tables=[i32(tables)], slot_mappings=[i32(slots)], max_query_len=max(seq_lens),
+        max_context_len=max(ctx_lens), block_size=block_size, h_query_start_loc=np.array(qsl), h_context_lens=np.array(ctx_lens),
+        h_state_slots=np.arange(len(seq_lens)),
+    )  # fmt: skip
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_part(dtype):
+    from kvforge_b200.parts.base import PartSpec, build_part
+
+    rt = runtime(dtype)
+    part = build_part("norm", PartSpec("rmsnorm", {"dim": 100, "eps": 3e-6}), "x.")
+    w = torch.rand(100) + 0.5
+    part.bind({"weight": w.cuda()}, rt)
+    resid, delta = torch.randn(9, 100), torch.randn(9, 100).to(dtype)
+    r = resid.cuda()
+    out = part.forward(None, r, delta.cuda())
+    assert torch.allclose(out.float().cpu(), rms_norm(resid + delta.float(), w, 3e-6), atol=tol(dtype), rtol=tol(dtype))
+    assert torch.allclose(r.cpu(), resid + delta.float(), atol=1e-6)
+
+
+def test_rotary_part_table():
+    from kvforge_b200.parts.base import PartSpec, build_part
+    from plain_llama import llama3_scaled_inv_freq
+
+    rt = runtime(torch.float32)
+    scaling = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+    part = build_part("position", PartSpec("rotary", {"head_dim": 32, "theta": 500000.0, "scaling": scaling}))
+    part.bind({}, rt)
+    want = llama3_scaled_inv_freq(plain_inv_freq(32, 500000.0), 8.0, 1.0, 4.0, 64)
+    assert torch.allclose(part.table().cpu(), want, rtol=1e-6)
+    assert not torch.allclose(part.table().cpu(), plain_inv_freq(32, 500000.0), rtol=1e-3)
+    plain_part = build_part("position", PartSpec("rotary", {"head_dim": 16, "theta": 10000.0}))
+    plain_part.bind({}, rt)
+    assert torch.equal(plain_part.table().cpu(), plain_inv_freq(16, 10000.0))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gated_mlp_part(dtype):
+    from kvforge_b200.parts.base import PartSpec, build_part
+
+    rt = runtime(dtype)
+    h, i = 80, 112
+    part = build_part("ffn", PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": i, "activation": "silu"}), "m.")
+    wg, wu, wd = (torch.randn(i, h) * 0.2).to(dtype), (torch.randn(i, h) * 0.2).to(dtype), (torch.randn(h, i) * 0.2).to(dtype)
+    part.bind({"gate_proj.weight": wg.cuda(), "up_proj.weight": wu.cuda(), "down_proj.weight": wd.cuda()}, rt)
+    x = torch.randn(13, h).to(dtype)
+    out = part.forward(None, x.cuda())
+    ref = swiglu(x.float(), wg.float(), wu.float(), wd.float())
+    assert rel_err(out.float().cpu(), ref) < tol(dtype)
+    with pytest.raises(ValueError):
+        build_part("ffn", PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": i, "activation": "gelu"}))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 7])
+def test_paged_attention_part(dtype, window):
+    """Whole prompt in one step, then a portion and single tokens on top of the cache."""
+    from kvforge_b200.parts.base import LayerCache, PartSpec, build_part
+
+    rt = runtime(dtype)
+    h, nh, nkv, d, bs = 80, 6, 3, 48, 4
+    pos = PartSpec("rotary", {"head_dim": d, "theta": 25000.0})
+    part = build_part("mixer", PartSpec("paged_attention", {"hidden_size": h, "num_heads": nh, "num_kv_heads": nkv, "head_dim": d, "position": pos, "window": window}), "a.")
+    w = {n: (torch.randn(o, i) * 0.15).to(dtype) for n, (o, i) in {"q_proj.weight": (nh * d, h), "k_proj.weight": (nkv * d, h), "v_proj.weight": (nkv * d, h), "o_proj.weight": (h, nh * d)}.items()}
+    part.bind({k: v.cuda() for k, v in w.items()}, rt)
+    t = 30
+    x = torch.randn(t, h).to(dtype)
+    # plain: the formulas of the attention layer on the whole sequence
+    cos, sin = rope_cos_sin(torch.arange(t), plain_inv_freq(d, 25000.0))
+    xf = x.float()
+    q = apply_rope(linear(xf, w["q_proj.weight"].float()).view(t, nh, d), cos, sin)
+    k = apply_rope(linear(xf, w["k_proj.weight"].float()).view(t, nkv, d), cos, sin)
+    v = linear(xf, w["v_proj.weight"].float()).view(t, nkv, d)
+    ref = linear(causal_attention(q, k, v, 1 / math.sqrt(d), window).reshape(t, -1), w["o_proj.weight"].float())
+    nb = 12
+    table = [7, 2, 9, 0, 11, 4, 5, 1]
+    slots = [table[p // bs] * bs + p % bs for p in range(t)]
+    cache = LayerCache(torch.zeros(nb, nkv, bs, d, device="cuda", dtype=dtype), torch.zeros(nb, nkv, bs, d, device="cuda", dtype=dtype), 0)
+    cuts = [(0, 17), (17, 26), (26, 27), (27, 28), (28, 30)]
+    got = []
+    for a, b in cuts:
+        ctx = context(rt, [b - a], [a], bs, [table], slots[a:b])
+        got.append(part.forward(ctx, x[a:b].cuda(), cache).float().cpu().clone())
+    assert rel_err(torch.cat(got), ref) < tol(dtype)
+    assert part.cache_need().kind == ("window" if window else "full")
+
+
+def _variant_folder(tmp_path, name, extra):
+    d = make_model_dir(tmp_path, name, store_dtype=torch.bfloat16)
+    cfg = json.loads((d / "config.json").read_text())
+    cfg.update(extra)
+    (d / "config.json").write_text(json.dumps(cfg))
+    return d
+
+
+@pytest.fixture
+def variant_architecture():
+    """A test-only architecture: the Llama parts, with the order of layers and an attention
+    window taken from extra config.json keys."""
+    from kvforge_b200 import ModelConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.model import LayerCall
+
+    def parse(d):
+        cfg = ModelConfig.from_hf_dict(d)
+        cfg.extra = {"execution": d.get("test_execution"), "window": d.get("test_window")}
+        return cfg
+
+    def build(cfg):
+        spec = llama_spec(cfg)
+        if cfg.extra["execution"]:
+            spec.execution = [LayerCall(layer, src) for layer, src in cfg.extra["execution"]]
+            spec.__post_init__()
+        if cfg.extra["window"]:
+            for ls in spec.layers[1:]:  # layer 0 keeps every key, the others a window: two cache groups
+                mixer = ls.block.params["mixer"]
+                ls.block.params["mixer"] = type(mixer)(mixer.kind, {**mixer.params, "window": cfg.extra["window"]})
+        return spec
+
+    register_architecture("TestVariantForCausalLM", parse, build)
+    yield "TestVariantForCausalLM"
+    unregister_architecture("TestVariantForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_execution_list_names_a_layer_twice_and_shares_a_cache(tmp_path, variant_architecture, dtype):
+    from test_gpu_replay import MEAN_SLACK, TOL, check, plain_bfloat16_mean_error, replay_in_process
+
+    execution = [[0, None], [1, None], [0, None], [2, 1], [1, 2]]
+    folder = _variant_folder(tmp_path, "tiny-b", {"architectures": [variant_architecture], "test_execution": execution})
+    plain = PlainLlama(folder)
+    plain.execution = [(layer, src) for layer, src in execution]
+    reqs = {f"r{i}": random_tokens(320, n, seed=i) for i, n in enumerate([45, 9, 70])}
+    ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+    assert rel_err(ref["r0"], PlainLlama(folder).logits(reqs["r0"])) > 1e-2  # the order matters
+    mean_tol = None
+    if dtype == "bfloat16":
+        plain16 = PlainLlama(folder, dtype=torch.bfloat16)
+        plain16.execution = plain.execution
+        mean_tol = MEAN_SLACK * plain_bfloat16_mean_error(plain16, reqs, ref) + 5e-4
+    for steps in (traces.whole(reqs), traces.portions(reqs), traces.mixed(reqs, {r: len(t) - 10 for r, t in reqs.items()}, seed=1)):
+        check(steps, replay_in_process(folder, dtype, steps), ref, TOL[dtype], mean_tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_have_pages_of_their_own(tmp_path, variant_architecture, dtype):
+    from kvforge_b200.replay import TraceRunner
+    from test_gpu_replay import TOL, check
+
+    folder = _variant_folder(tmp_path, "tiny-c", {"architectures": [variant_architecture], "test_window": 21})
+    reqs = {f"r{i}": random_tokens(203, n, seed=i) for i, n in enumerate([150, 40, 97])}
+
+    class WindowedPlain(PlainLlama):
+        def attention(self, layer, x, positions, kv=None):
+            self.window = None if layer == 0 else 21
+            return super().attention(layer, x, positions, kv)
+
+    plain = WindowedPlain(folder)
+    ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+    assert rel_err(ref["r0"], PlainLlama(folder).logits(reqs["r0"])) > 1e-3
+    cuts = {"whole": traces.whole(reqs), "portions": traces.portions(reqs), "tail": traces.tail_one_by_one(reqs, 32),
+            "mixed": traces.mixed(reqs, {r: len(t) - 12 for r, t in reqs.items()}, seed=3)}  # fmt: skip
+    for cut, steps in cuts.items():
+        runner = TraceRunner(str(folder), dtype, traces.tokens_needed(steps))
+        bm = runner.core.block_manager
+        assert bm.num_groups == 2
+        window_group = [g for g in range(2) if bm.group_specs[g].kind == "window"][0]
+        outs, most_saved = [], 0
+        for s in steps:
+            o = runner.step(s)
+            outs.append(None if o is None else o.clone())
+            bm.check_invariants()
+            most_saved = max(most_saved, bm.free_blocks_of(window_group) - bm.free_blocks_of(1 - window_group))
+        check(steps, outs, ref, TOL[dtype])
+        if cut != "whole":  # pages behind the window were given back while the full group kept its own
+            assert most_saved >= 5, cut  # 150 tokens are 10 pages of 16; a window of 21 needs 3
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    """A mixer that keeps a decaying sum per request (no keys, no pages), written here with
+    torch operations, plugged in through the public registries only."""
+    from kvforge_b200 import ModelConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.base import CacheNeed, Mixer, PartSpec, WeightDecl, register_mixer, MIXERS
+    from kvforge_b200.replay import TraceRunner
+    from test_gpu_replay import check
+
+    decay = 0.9
+
+    class DecayingSum(Mixer):
+        """state_t = decay * state_{t-1} + x_t W_in^T ;  y_t = state_t W_out^T"""
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.h, self.s = params["hidden_size"], params["state_size"]
+
+        @classmethod
+        def weight_decls(cls, params):
+            return {"in_proj.weight": WeightDecl((params["state_size"], params["hidden_size"])),
+                    "out_proj.weight": WeightDecl((params["hidden_size"], params["state_size"]))}  # fmt: skip
+
+        def cache_need(self):
+            return CacheNeed("none")
+
+        def state_shape(self):
+            return (self.s,)
+
+        def bind(self, weights, rt):
+            super().bind(weights, rt)
+            self.w_in, self.w_out = weights["in_proj.weight"].float(), weights["out_proj.weight"].float()
+
+        def forward(self, ctx, x, cache):
+            u = x.float() @ self.w_in.t()
+            out = torch.empty_like(u)
+            for b in range(ctx.num_seqs):
+                lo, hi = int(ctx.h_query_start_loc[b]), int(ctx.h_query_start_loc[b + 1])
+                slot = int(ctx.h_state_slots[b])
+                state = cache.state[slot].clone()
+                for t in range(lo, hi):
+                    state = decay * state + u[t]
+                    out[t] = state
+                cache.state[slot] = state
+            return (out @ self.w_out.t()).to(x.dtype)
+
+    if "decaying_sum" not in MIXERS:
+        register_mixer("decaying_sum")(DecayingSum)
+
+    def build(cfg):
+        spec = llama_spec(cfg)
+        for i, ls in enumerate(spec.layers):
+            if i % 2 == 1:  # odd layers keep a state, even layers keep keys: both kinds in one model
+                ls.block.params["mixer"] = PartSpec("decaying_sum", {"hidden_size": cfg.hidden_size, "state_size": 24})
+                ls.block.params["mixer_name"] = "toy"
+        return spec
+
+    register_architecture("ToyStateForCausalLM", ModelConfig.from_hf_dict, build)
+    try:
+        from kvforge_b200.parts.model import DecoderModel
+        from kvforge_b200.weights.random_init import write_model_dir
+
+        cfg = TINY["tiny-b"]["cfg"]
+        cj = cfg.to_hf_dict()
+        cj["architectures"] = ["ToyStateForCausalLM"]
+        model = DecoderModel(build(cfg))
+        assert model.state_shapes == [None, (24,), None] and len(model.groups) == 1 and len(model.groups[0].calls) == 2
+        folder = write_model_dir(tmp_path / "toy", cj, model.expected_weights(), seed=5, store_dtype=torch.float32, init_std=0.1, norm_std=0.1)
+
+        class ToyPlain(PlainLlama):
+            def attention(self, layer, x, positions, kv=None):
+                if layer % 2 == 0:
+                    return super().attention(layer, x, positions, kv)
+                u = x @ self.w[f"layers.{layer}.toy.in_proj.weight"].t()
+                state = torch.zeros(24)
+                rows = []
+                for t in range(x.shape[0]):
+                    state = decay * state + u[t]
+                    rows.append(state)
+                return torch.stack(rows) @ self.w[f"layers.{layer}.toy.out_proj.weight"].t(), None
+
+        plain = ToyPlain(folder)
+        reqs = {f"r{i}": random_tokens(320, n, seed=i) for i, n in enumerate([33, 5, 48, 20, 27])}
+        ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: len(t) - 6 for r, t in reqs.items()}, max_live=3, seed=2)):
+            runner = TraceRunner(str(folder), "float32", traces.tokens_needed(steps), max_live=3)
+            outs = []
+            for s in steps:
+                o = runner.step(s)
+                outs.append(None if o is None else o.clone())
+            check(steps, outs, ref, 2e-5)  # slots are used again: a new request must start from zero
+            runner.core.state_slots.check_invariants()
+    finally:
+        unregister_architecture("ToyStateForCausalLM")

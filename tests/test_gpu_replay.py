@@ -21,10 +21,16 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"tiny-a": [5, 17, 33, 70, 100], "tiny-b": [1, 9, 40, 71, 130], "tiny-c": [3, 64, 65, 97, 2]}
+# Error of a logits row: largest difference over the row's largest magnitude.
 # float32: the engine's 32-bit kernels against 32-bit torch on the CPU (sums in other orders).
 # bfloat16: stored weights are bfloat16 in both, so what differs is the rounding of
-# activations: a few bfloat16 ulps (2^-8) accumulated over the layers.
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# activations (2^-8 each) accumulated over the layers.  Plain bfloat16 arithmetic on these
+# tiny models loses 0.7-1.5 % of a row's magnitude on average and up to 5 % at single
+# positions; the engine rounds less often (its residual stream and logits are 32-bit).  So a
+# row may be off by at most 6 %, and the mean over a trace must not exceed the mean error of
+# the plain implementation run in bfloat16 on the same model (``MEAN_SLACK`` for noise).
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+MEAN_SLACK = 1.15
 
 
 @pytest.fixture(scope="module")
@@ -45,6 +51,22 @@ def oracle(folders):
     return out
 
 
+def plain_bfloat16_mean_error(plain16, reqs, ref) -> float:
+    """Mean row error of the plain implementation run in bfloat16."""
+    errs = [rel_err(row, ref[rid][i]) for rid, t in reqs.items() for i, row in enumerate(plain16.logits(t))]
+    return sum(errs) / len(errs)
+
+
+@pytest.fixture(scope="module")
+def mean_bound(folders, oracle):
+    """Per model: the bound on the mean row error of a bfloat16 trace."""
+    out = {}
+    for name, d in folders.items():
+        reqs, ref = oracle[name]
+        out[name] = MEAN_SLACK * plain_bfloat16_mean_error(PlainLlama(d, dtype=torch.bfloat16), reqs, ref) + 5e-4
+    return out
+
+
 def replay_in_process(model_dir, dtype, steps, max_tokens=None):
     from kvforge_b200.replay import TraceRunner
 
@@ -58,9 +80,10 @@ def replay_in_process(model_dir, dtype, steps, max_tokens=None):
     return out
 
 
-def check(steps, outputs, ref_logits, tol):
+def check(steps, outputs, ref_logits, tol, mean_tol=None):
     worst = 0.0
     n = 0
+    total = 0.0
     for s, rows, got in zip(steps, traces.wanted_places(steps), outputs):
         if not rows:
             assert got is None
@@ -71,15 +94,18 @@ def check(steps, outputs, ref_logits, tol):
             err = rel_err(got[i], ref)
             assert err < tol, f"step {s['step']} request {rid} position {pos}: error {err:.3e} (tolerance {tol})"
             worst = max(worst, err)
+            total += err
             n += 1
     assert n > 0
+    if mean_tol is not None:
+        assert total / n <= mean_tol, f"mean row error {total / n:.3e} exceeds {mean_tol:.3e}"
     return worst
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(TINY))
 @pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
-def test_replay_regimes(folders, oracle, name, dtype, regime):
+def test_replay_regimes(folders, oracle, mean_bound, name, dtype, regime):
     reqs, ref = oracle[name]
     if regime == "whole":
         steps = traces.whole(reqs)
@@ -93,7 +119,7 @@ def test_replay_regimes(folders, oracle, name, dtype, regime):
         assert max(len(s["entries"]) for s in steps) >= 3
         assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and any(len(e["tokens"]) > 1 for s in steps for e in s["entries"])
     outputs = replay_in_process(folders[name], dtype, steps)
-    check(steps, outputs, ref, TOL[dtype])
+    check(steps, outputs, ref, TOL[dtype], mean_bound[name] if dtype == "bfloat16" else None)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -125,9 +151,11 @@ def test_bfloat16_engine_is_no_worse_than_plain_bfloat16(folders, oracle):
     outputs = replay_in_process(folders[name], "bfloat16", steps)
     for rows, got in zip(traces.wanted_places(steps), outputs):
         rid = rows[0][0]
-        e_plain = rel_err(plain16.logits(reqs[rid]), ref[rid])
-        e_engine = rel_err(got, ref[rid])
-        assert e_engine <= 1.5 * e_plain + 2e-3, (rid, e_engine, e_plain)
+        p16 = plain16.logits(reqs[rid])
+        e_plain = sum(rel_err(p16[i], ref[rid][i]) for i in range(len(reqs[rid]))) / len(reqs[rid])
+        e_engine = sum(rel_err(got[i], ref[rid][i]) for i in range(len(reqs[rid]))) / len(reqs[rid])
+        if len(reqs[rid]) >= 30:  # a mean over few rows is noise
+            assert e_engine <= MEAN_SLACK * e_plain + 5e-4, (rid, e_engine, e_plain)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
