@@ -1,0 +1,388 @@
+"""Decode and prefill throughput of the Llama-3.2-1B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A step is one decode step of a batch of 8 requests whose contexts start at 2,048 tokens
+(prompts of 2,048 random tokens, decoding towards 4,096).  ``value`` is decoded tokens a
+second, timed on the device with CUDA events around exactly K steps of the step function
+plus the sampling kernel; ``e2e`` is the same through ``InferenceEngine`` (scheduler, token
+ids from and to the host every step).  The same line carries a 2,048-token prefill, the
+decode step's HBM roofline fraction, and decode at batch 1 and 64.  One JSON line on stdout.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+
+
+def peaks() -> dict:
+    """Measured peaks if the driver wrote them, else the fallback figures of an earlier
+    measurement on this pool."""
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            data = json.loads(path.read_text())
+            for k in ("hbm_gbs", "bf16_tflops"):
+                if isinstance(data.get(k), (int, float)) and data[k] > 0:
+                    out[k] = float(data[k])
+            out["source"] = "measured"
+        except (OSError, ValueError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu: str = "0") -> None:
+        self.proc = None
+        self.gpu = gpu
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in text.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max_clock,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def model_numbers(cfg, layers: int) -> dict:
+    """Bytes and flops of the shape (bfloat16 weights)."""
+    h, d, nh, nkv, inter, v = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.intermediate_size, cfg.vocab_size
+    per_layer = h * d * (nh + 2 * nkv) + nh * d * h + 3 * h * inter
+    head = v * h
+    return {
+        "weight_bytes": 2 * (layers * per_layer + head),  # every weight a decode step reads once
+        "kv_bytes_per_token": 2 * layers * nkv * d * 2,
+        "linear_flops_per_token": 2 * layers * per_layer,
+        "head_flops_per_row": 2 * head,
+        "attn_flops_causal": lambda t: layers * 4 * nh * d * t * (t + 1) // 2,
+    }
+
+
+def make_core(cfg, batch: int, max_tokens: int, ctx_cap: int, cuda_graphs: bool = True):
+    from kvforge_b200.config.engine_config import CacheConfig
+    from kvforge_b200.engine.core import EngineCore, spec_from_config
+
+    blocks = batch * (-(-ctx_cap // 16)) + 8
+    return EngineCore(
+        spec_from_config(cfg), dtype="bfloat16", seed=0,
+        cache=CacheConfig(block_size=16, num_blocks=blocks, watermark=0.0),
+        max_num_seqs=batch, max_num_batched_tokens=max_tokens, max_model_len=ctx_cap, cuda_graphs=cuda_graphs,
+    )  # fmt: skip
+
+
+def time_decode(core, batch: int, start_ctx: int, steps: int, warmup: int, sample: bool = True):
+    """K decode steps of ``batch`` requests whose caches hold ``start_ctx`` tokens of synthetic
+    keys and values.  Returns (seconds, kernels launched, mean context over the timed steps)."""
+    import torch
+
+    from kvforge_b200.engine.step import BatchItem
+    from kvforge_b200.sampling.params import SamplingParams
+    from kvforge_b200.sampling.sampler import Sampler
+
+    bm = core.block_manager
+    ids = [f"b{i}" for i in range(batch)]
+    for rid in ids:
+        bm.allocate(rid, start_ctx)
+        core.state_slots.allocate(rid)
+    for t in core.pool.k + core.pool.v:  # synthetic cache contents
+        t.normal_(0.0, 0.5)
+    sampler = Sampler(core.device, batch)
+    params = [SamplingParams(temperature=0.0)] * batch
+    gen = torch.Generator().manual_seed(0)
+    vocab = core.spec.vocab_size
+    tokens = torch.randint(0, vocab, (warmup + steps, batch), generator=gen).tolist()
+    pos = start_ctx
+
+    def one(i):
+        nonlocal pos
+        for rid in ids:
+            bm.append_slots(rid, pos + 1, pos)
+        logits = core.runner.step([BatchItem(rid, [tokens[i][j]], pos, "last") for j, rid in enumerate(ids)])
+        if sample:
+            sampler.sample(logits, params, [0] * batch)
+        pos += 1
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    k0 = core.runner.num_kernel_launches
+    g0 = sum(core.runner.graph_kernels.values())
+    ctx0 = pos
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    end.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(end) / 1e3
+    # kernels of this library: those of the steps (inside replayed graphs) plus one sampling kernel a step
+    launched = (core.runner.num_kernel_launches - k0) + (steps if sample else 0)
+    if sum(core.runner.graph_kernels.values()) != g0:
+        launched = None  # a graph was captured inside the timed region: the count would mix things
+    for rid in ids:
+        bm.free(rid)
+        core.state_slots.free(rid)
+    return seconds, launched, (ctx0 + pos - 1) / 2.0
+
+
+def time_prefill(core, tokens: int, reps: int = 3):
+    import torch
+
+    from kvforge_b200.engine.step import BatchItem
+
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, core.spec.vocab_size, (tokens,), generator=gen).tolist()
+    times = []
+    for _ in range(reps + 1):
+        core.block_manager.allocate("p", tokens)
+        core.state_slots.allocate("p")
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        core.runner.step([BatchItem("p", prompt, 0, "last")])
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) / 1e3)
+        core.block_manager.free("p")
+        core.state_slots.free("p")
+    return min(times[1:])
+
+
+def time_e2e(cfg, batch: int, steps: int, warmup: int):
+    """The same decode steps through ``InferenceEngine``: prompts of 2,048 host token ids in,
+    a token id per request out to the host every step."""
+    import torch
+
+    from kvforge_b200 import CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
+
+    blocks = batch * (CONTEXT // 16) + 8
+    engine = InferenceEngine(
+        EngineConfig(
+            model=cfg, cache=CacheConfig(block_size=16, num_blocks=blocks, watermark=0.0),
+            scheduler=SchedulerConfig(max_num_seqs=batch, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT),
+            dtype="bfloat16", seed=0,
+        )
+    )  # fmt: skip
+    gen = torch.Generator().manual_seed(2)
+    # requests whose prompts are done decode while the others are still in theirs: leave room
+    sp = SamplingParams(max_tokens=warmup + steps + 2 * batch + 8, temperature=0.0, ignore_eos=True)
+    for _ in range(batch):
+        engine.add_request(torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=gen).tolist(), sp)
+    while any(r.is_prefill for r in engine.scheduler.requests.values()):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h0 = engine.runner.h2d_bytes
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    produced = 0
+    for _ in range(steps):
+        produced += sum(len(o.new_token_ids) for o in engine.step())
+    end.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    seconds = max(start.elapsed_time(end) / 1e3, wall)
+    assert produced == batch * steps, (produced, batch * steps)
+    return produced / seconds, (engine.runner.h2d_bytes - h0) / steps, 4 * batch
+
+
+def run_own(args) -> dict:
+    import torch
+
+    from kvforge_b200 import PRESETS
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    cfg = PRESETS["llama-3.2-1b"]
+    layers = cfg.num_layers
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    batch = 8
+    ctx_cap = CONTEXT
+
+    core = make_core(cfg, 64, PREFILL_TOKENS, ctx_cap)
+    try:
+        gpu = "GPU-" + str(torch.cuda.get_device_properties(0).uuid)
+    except Exception:  # an older torch without the uuid field
+        gpu = "0"
+    sampler = ClockSampler(gpu)
+    sampler.start()
+    seconds, launches, mean_ctx = time_decode(core, batch, PROMPT_LEN, args.steps, args.warmup)
+    clocks = sampler.stop()
+    tok_s = batch * args.steps / seconds
+    step_bytes = nums["weight_bytes"] + batch * mean_ctx * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (seconds / args.steps) / 1e9
+
+    points = {}
+    for b in (1, 64):
+        k = max(16, args.steps // 2)
+        s, _, _ = time_decode(core, b, PROMPT_LEN, k, max(3, args.warmup))
+        points[f"decode_b{b}"] = round(b * k / s, 1)
+
+    p_seconds = time_prefill(core, PREFILL_TOKENS)
+    p_flops = PREFILL_TOKENS * nums["linear_flops_per_token"] + nums["head_flops_per_row"] + nums["attn_flops_causal"](PREFILL_TOKENS)
+    del core
+    torch.cuda.empty_cache()
+
+    e2e_tok_s, h2d, d2h = time_e2e(cfg, batch, args.steps, args.warmup)
+
+    return {
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, context 2048->4096)",
+        "value": round(tok_s, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(1e3 * seconds / args.steps, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (random token ids, random-init weights, synthetic cache contents for the device-timed decode)",
+        "impl": "kvforge_b200",
+        "config": {
+            "model": "llama-3.2-1b-shape",
+            "layers": layers,
+            "layers_of_model": cfg.num_layers,
+            "hidden": cfg.hidden_size,
+            "heads": cfg.num_heads,
+            "kv_heads": cfg.num_kv_heads,
+            "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size,
+            "global_batch": batch,
+            "seq_len": CONTEXT,
+            "prompt_len": PROMPT_LEN,
+            "kv_block_size": 16,
+            "tied_embeddings": cfg.tie_word_embeddings,
+            "rope": "theta 5e5, llama3 x32",
+            "parallelism": "single-gpu",
+            "l2": "inputs larger than L2: every step streams 2.47 GB of weights",
+            "peaks": pk["source"],
+        },
+        "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": launches,
+        "prefill": {
+            "value": round(PREFILL_TOKENS / p_seconds, 1),
+            "tokens": PREFILL_TOKENS,
+            "ms": round(1e3 * p_seconds, 3),
+            "frac": round(p_flops / p_seconds / (pk["bf16_tflops"] * 1e12), 4),
+        },
+        "roofline": {
+            "bound": "hbm",
+            "achieved": round(achieved, 1),
+            "peak": pk["hbm_gbs"],
+            "unit": "GB/s",
+            "frac": round(achieved / pk["hbm_gbs"], 4),
+        },
+        "points": points,
+        "clocks": clocks,
+    }
+
+
+def run_only(args) -> dict:
+    """One part alone on a small footing: what the profiler is pointed at."""
+    from kvforge_b200 import PRESETS
+
+    cfg = PRESETS["llama-3.2-1b"]
+    ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
+    core = make_core(cfg, max(args.batch, 1), PREFILL_TOKENS, ctx_cap, cuda_graphs=not args.no_graphs)
+    if args.only == "decode":
+        seconds, launches, mean_ctx = time_decode(core, args.batch, args.context, args.steps, args.warmup)
+        return {"only": "decode", "batch": args.batch, "context": mean_ctx, "ms_per_step": round(1e3 * seconds / args.steps, 4),
+                "tokens_per_s": round(args.batch * args.steps / seconds, 1), "gpu_launches": launches}  # fmt: skip
+    seconds = time_prefill(core, PREFILL_TOKENS, reps=max(1, args.steps))
+    return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(1e3 * seconds, 3), "tokens_per_s": round(PREFILL_TOKENS / seconds, 1)}
+
+
+def run_reference(args) -> dict:
+    """umarhassan-cloud/kvforge builds with hatchling, which is in neither this image nor its
+    offline wheelhouse, so ``pip install --no-index --no-build-isolation`` cannot build it."""
+    ref = ROOT / "baseline" / "_ref" / "tokenvault"
+    if not ref.is_dir():
+        return {"impl": "reference", "unavailable": "offline install failed: build backend hatchling is not installed and not in the wheelhouse"}
+    return {"impl": "reference", "unavailable": "reference arm not wired: the reference has no GPU kernels of its own and publishes no GPU numbers"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["own", "reference"], default="own")
+    ap.add_argument("--only", choices=["decode", "prefill"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")
+    ap.add_argument("--context", type=int, default=PROMPT_LEN, help="with --only decode: tokens already in each cache")
+    ap.add_argument("--no-graphs", action="store_true", help="with --only: launch kernels one by one instead of replaying a graph")
+    args = ap.parse_args()
+    if args.gpus > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print("bench.py: this engine runs on one GPU; --gpus > 1 is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
+    if args.only:
+        print(json.dumps(run_only(args)))
+        return 0
+    print(json.dumps(run_own(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -21,6 +21,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.block_manager import BlockManager
 from ..cache.state_slots import StateSlotPool
 from .runtime import Runtime, StepContext
@@ -110,6 +111,9 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs)
         self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.graph_kernels: dict[int, int] = {}  # kernels of this library inside each captured graph
+        self.num_kernel_launches = 0  # kernels of this library launched by steps, replays included
+        self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
         self._cap = 0
         self._host: torch.Tensor | None = None
         self._dev: torch.Tensor | None = None
@@ -136,6 +140,7 @@ class ModelRunner:
     def _upload(self, total: int) -> None:
         """The one host-to-device copy of a step."""
         self._dev[:total].copy_(self._host[:total], non_blocking=True)
+        self.h2d_bytes += 4 * total
         if self._copy_done is None:
             self._copy_done = torch.cuda.Event()
         self._copy_done.record()
@@ -247,7 +252,9 @@ class ModelRunner:
         n, nb, r, max_q, max_ctx = self._fill(items, lay)
         self._upload(lay.total)
         ctx = self._context(lay, n, nb, r, max_q, max_ctx, bound=0)
+        before = ops.launch_count
         logits = self.model.forward(ctx)
+        self.num_kernel_launches += ops.launch_count - before
         self.num_forward_passes += 1
         self.num_tokens_processed += n
         return logits[:r]
@@ -279,6 +286,7 @@ class ModelRunner:
             entry = self._capture(bucket, lay)
         graph, logits = entry
         graph.replay()
+        self.num_kernel_launches += self.graph_kernels[bucket]
         self.num_forward_passes += 1
         self.num_tokens_processed += n
         return logits[:r]
@@ -290,10 +298,12 @@ class ModelRunner:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         self.rt.capturing = True
+        before = ops.launch_count
         try:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
         finally:
             self.rt.capturing = False
+        self.graph_kernels[bucket] = ops.launch_count - before
         self._graphs[bucket] = (graph, logits)
         return self._graphs[bucket]

@@ -63,9 +63,15 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def _check(rc: int, name: str) -> None:
+# Kernels of this library launched so far (library matrix products are not counted).
+launch_count = 0
+
+
+def _check(rc: int, name: str, kernels: int = 1) -> None:
+    global launch_count
     if rc != 0:
         raise RuntimeError(f"CUDA launcher {name} failed with cudaError {rc}")
+    launch_count += kernels
 
 
 def _need(t: torch.Tensor, dtype: torch.dtype | None, what: str, contiguous: bool = True) -> None:
@@ -294,6 +300,7 @@ def paged_attention_generic(
             int(window), split, max_splits, _ptr(pa), _ptr(pm), _stream(),
         ),
         name,
+        2 if scratch is not None else 1,
     )  # fmt: skip
 
 
