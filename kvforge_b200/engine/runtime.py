@@ -27,6 +27,7 @@ class Runtime:
         self._buffers: dict[tuple, torch.Tensor] = {}
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.capturing = False
+        self.graphs_captured = False  # captured graphs hold buffer addresses: no buffer may move afterwards
 
     def buf(self, name: str, rows: int, cols: int, dtype: torch.dtype | None = None, cap: int | None = None) -> torch.Tensor:
         """A ``[rows, cols]`` view of the persistent buffer ``name`` (contents undefined).
@@ -36,8 +37,8 @@ class Runtime:
         key = (name, cols, dtype)
         t = self._buffers.get(key)
         if t is None or t.shape[0] < rows:
-            if self.capturing:
-                raise RuntimeError(f"buffer {name} would have to grow during graph capture")
+            if self.capturing or (self.graphs_captured and t is not None):
+                raise RuntimeError(f"buffer {name} would have to grow after or during graph capture")
             if self.lazy:
                 cap = 1 << max(4, (max(rows, 1) - 1).bit_length())
             else:

@@ -305,5 +305,6 @@ class ModelRunner:
         finally:
             self.rt.capturing = False
         self.graph_kernels[bucket] = ops.launch_count - before
+        self.rt.graphs_captured = True
         self._graphs[bucket] = (graph, logits)
         return self._graphs[bucket]

@@ -24,6 +24,7 @@ _SIGNATURES = {
     "kvf_silu_mul_{s}": "pplip",
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiippp",
+    "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiippp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_sample_f32": "pliippppppp",
 }
@@ -225,12 +226,16 @@ def cast_from_float(src: torch.Tensor, out: torch.Tensor) -> None:
 
 # ------------------------------------------------------------------ attention
 
-ATTN_SPLIT_SIZE = 256  # keys per range of the decode form; ranges start at multiples of it
+def attention_split_size(num_seqs: int, nkv: int) -> int:
+    """Keys per range of the decode form: smaller ranges when few (sequence, kv head) pairs
+    would leave SMs idle.  Ranges start at multiples of it, whatever the batch."""
+    pairs = num_seqs * nkv
+    return 256 if pairs >= 64 else 128 if pairs >= 16 else 64
 
 
-def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int) -> tuple[tuple[int, ...], tuple[int, ...]]:
+def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, split_size: int = 256) -> tuple[tuple[int, ...], tuple[int, ...]]:
     """Shapes of the float scratch the decode form needs for contexts up to ``max_context``."""
-    splits = max(1, -(-max_context // ATTN_SPLIT_SIZE))
+    splits = max(1, -(-max_context // split_size))
     return (max_seqs, nh, splits, d), (max_seqs, nh, splits, 2)
 
 
@@ -239,7 +244,13 @@ def check_head_dim(d: int) -> None:
         raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 16, at most 256")
 
 
-def paged_attention_generic(
+def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:
+    """Whether the tensor-core kernel (``csrc/attention_mma.cu``) takes this shape."""
+    g = nh // max(nkv, 1)
+    return dtype == torch.bfloat16 and d in (64, 128) and g <= (16 if decode_form else 64)
+
+
+def paged_attention(
     q: torch.Tensor,
     out: torch.Tensor,
     kcache: torch.Tensor,
@@ -257,12 +268,18 @@ def paged_attention_generic(
     q_stride: int | None = None,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
     max_context: int | None = None,
+    split_size: int = 256,
+    kernel: str = "auto",
 ) -> None:
-    """Paged GQA attention of a flat batch (see ``csrc/attention_generic.cu`` for the contract).
+    """Paged GQA attention of a flat batch (the contract is at the top of
+    ``csrc/attention_generic.cu``).
 
     ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
     ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form
-    runs: key ranges in parallel, then a merge; ``max_context`` bounds the contexts.
+    runs: key ranges of ``split_size`` in parallel, then a merge; ``max_context`` bounds the
+    contexts.  ``kernel``: ``"auto"`` takes the tensor-core kernel where it applies
+    (bfloat16, head size 64 or 128) and the FP32-pipe kernel elsewhere; ``"generic"`` and
+    ``"mma"`` force one (tests).
     """
     s = _suffix(q.dtype)
     check_head_dim(d)
@@ -286,13 +303,20 @@ def paged_attention_generic(
         _need(pm, torch.float32, "scratch ml")
         if max_q_len != 1:
             raise ValueError("the decode form needs one query per sequence")
-        split = ATTN_SPLIT_SIZE
+        if split_size <= 0 or split_size % 64:
+            raise ValueError("split_size must be a positive multiple of 64")
+        split = split_size
         max_splits = pa.shape[2]
         if pa.shape[0] < num_seqs or pa.shape[1] != nh or pa.shape[3] != d:
             raise ValueError("paged_attention: scratch shape does not fit")
         if max_context is None or -(-max_context // split) > max_splits:
             raise ValueError("paged_attention: scratch is too small for the longest context")
-    name = f"kvf_paged_attention_generic_{s}"
+    use_mma = mma_attention_supported(q.dtype, nh, nkv, d, scratch is not None)
+    if kernel == "generic":
+        use_mma = False
+    elif kernel == "mma" and not use_mma:
+        raise ValueError("the tensor-core attention kernel does not take this shape")
+    name = "kvf_paged_attention_mma_bf16" if use_mma else f"kvf_paged_attention_generic_{s}"
     _check(
         _fn(name)(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
@@ -302,6 +326,12 @@ def paged_attention_generic(
         name,
         2 if scratch is not None else 1,
     )  # fmt: skip
+
+
+def paged_attention_generic(*args, **kw) -> None:
+    """``paged_attention`` on the FP32-pipe kernel whatever the shape."""
+    kw["kernel"] = "generic"
+    paged_attention(*args, **kw)
 
 
 # ------------------------------------------------------------------ matrix products

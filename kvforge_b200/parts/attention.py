@@ -74,10 +74,12 @@ class PagedAttention(Mixer):
     def _scratch(self, ctx):
         rt = self.rt
         bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
-        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound)
-        acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32).view(sa)
-        ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32).view(sm)
-        return (acc, ml), bound
+        split = ops.attention_split_size(ctx.num_seqs, self.nkv)
+        # made for the smallest range size, so that one buffer serves every batch size
+        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, 64)
+        acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
+        ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
+        return (acc, ml), bound, split
 
     def forward(self, ctx, x: torch.Tensor, cache) -> torch.Tensor:
         rt = self.rt
@@ -105,11 +107,11 @@ class PagedAttention(Mixer):
         return y
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
-        scratch, bound = (None, None)
+        scratch, bound, split = None, None, 256
         if ctx.all_single_query:
-            scratch, bound = self._scratch(ctx)
-        ops.paged_attention_generic(
+            scratch, bound, split = self._scratch(ctx)
+        ops.paged_attention(
             q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens,
             ctx.num_seqs, ctx.max_query_len, self.nh, self.nkv, self.d, self.scale,
-            window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound,
+            window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound, split_size=split,
         )  # fmt: skip

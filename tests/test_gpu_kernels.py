@@ -152,7 +152,7 @@ def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5):
     return kc, vc, tables
 
 
-def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None):
+def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256):
     g = torch.Generator().manual_seed(seed)
     kv = [(torch.randn(c, nkv, d, generator=g).to(dtype), torch.randn(c, nkv, d, generator=g).to(dtype)) for c in ctx_lens]
     qs = [torch.randn(ql, nh, d, generator=g).to(dtype) for ql in q_lens]
@@ -166,11 +166,12 @@ def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode
     scratch, bound = None, None
     if decode_form:
         bound = max(ctx_lens)
-        sa, sm = ops.attention_scratch_shapes(len(ctx_lens), nh, d, bound)
+        sa, sm = ops.attention_scratch_shapes(len(ctx_lens), nh, d, bound, split)
         scratch = (torch.full(sa, float("nan"), device="cuda"), torch.full(sm, float("nan"), device="cuda"))
-    ops.paged_attention_generic(
+    ops.paged_attention(
         dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
         len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
+        split_size=split, kernel=kernel,
     )  # fmt: skip
     refs = []
     for (k, v), qq, c, ql in zip(kv, qs, ctx_lens, q_lens):
@@ -263,6 +264,79 @@ def test_attention_rows_do_not_depend_on_the_cut(ops):
             dev(torch.tensor([ctx], dtype=torch.int32)), 1, ql, nh, nkv, d, 1.0 / math.sqrt(d),
         )  # fmt: skip
         assert torch.equal(out.cpu(), whole[ctx - ql :]), ql
+
+
+# ---- the tensor-core kernel (bfloat16, head sizes 64 and 128)
+
+MMA_SHAPES = [(8, 2, 64, 16), (32, 8, 64, 16), (3, 1, 64, 8), (6, 3, 128, 4), (24, 8, 128, 32), (5, 5, 64, 16), (14, 2, 128, 16), (32, 1, 64, 16)]
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs", MMA_SHAPES)
+@pytest.mark.parametrize(
+    "ctx_lens,q_lens",
+    [([7, 13, 1, 20], [1, 1, 1, 1]), ([9, 16], [9, 16]), ([12, 30, 5], [4, 7, 5]), ([17, 3, 25, 130], [1, 3, 5, 67]), ([300, 64, 65], [300, 2, 65])],
+)
+def test_paged_attention_mma(ops, nh, nkv, d, bs, ctx_lens, q_lens):
+    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx_lens, q_lens, kernel="mma")
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs", [s for s in MMA_SHAPES if s[0] // s[1] <= 16])
+@pytest.mark.parametrize("split", [64, 128, 256])
+def test_paged_attention_mma_decode_form(ops, nh, nkv, d, bs, split):
+    ctx = [700, 1, 256, 257, 33, 64, 65]
+    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form=True, kernel="mma", split=split)
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("decode_form", [False, True])
+def test_mma_attention_finds_a_far_key_and_respects_the_window(ops, decode_form):
+    for far in (0, 15, 16, 63, 64, 255, 256, 511, 640):
+
+        def craft(kv, qs, far=far):
+            k, v = kv[0]
+            k.mul_(0.01)
+            k[far, :, 0] = 40.0
+            qs[0][-1, :, 0] = 40.0
+
+        out, ref, kv = run_attention(ops, torch.bfloat16, 8, 2, 64, 16, [700], [1], decode_form=decode_form, craft=craft, kernel="mma", split=128)
+        v_far = kv[0][1][far].float().repeat_interleave(4, dim=0).reshape(-1)
+        assert torch.allclose(out[-1], v_far, atol=2e-2), far
+    ctx = 300
+    for window in (1, 5, 64, 65, 100):
+        for offset, seen in ((window - 1, True), (window, False)):
+            far = ctx - 1 - offset
+
+            def craft(kv, qs, far=far):
+                k, v = kv[0]
+                k.mul_(0.01)
+                k[far, :, 0] = 40.0
+                qs[0][-1, :, 0] = 40.0
+
+            q_lens = [1] if decode_form else [9]
+            out, ref, kv = run_attention(ops, torch.bfloat16, 4, 1, 64, 8, [ctx], q_lens, window=window, decode_form=decode_form, craft=craft, kernel="mma", split=64)
+            assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2), (window, offset)
+            v_far = kv[0][1][far].float().repeat(4, 1).reshape(-1)
+            assert torch.allclose(out[-1], v_far, atol=2e-2) == seen, (window, offset)
+
+
+def test_mma_attention_rows_do_not_depend_on_the_cut(ops):
+    nh, nkv, d, bs, ctx = 8, 2, 64, 16, 197
+    whole, _, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, [ctx], [ctx], seed=4, kernel="mma")
+    g = torch.Generator().manual_seed(4)
+    k = torch.randn(ctx, nkv, d, generator=g).bfloat16()
+    v = torch.randn(ctx, nkv, d, generator=g).bfloat16()
+    q = torch.randn(ctx, nh, d, generator=g).bfloat16()
+    for ql in (2, 30, 70):
+        kc, vc, tables = paged([(k, v)], nkv, d, bs, torch.bfloat16, seed=ql)
+        out = torch.empty(ql, nh * d, device="cuda", dtype=torch.bfloat16)
+        ops.paged_attention(
+            dev(q[ctx - ql :].reshape(ql, -1)), out, dev(kc), dev(vc), dev(tables), dev(torch.tensor([0, ql], dtype=torch.int32)),
+            dev(torch.tensor([ctx], dtype=torch.int32)), 1, ql, nh, nkv, d, 1.0 / math.sqrt(d), kernel="mma",
+        )  # fmt: skip
+        assert torch.equal(out.float().cpu(), whole[ctx - ql :]), ql
 
 
 def test_head_dim_is_checked(ops):
