@@ -8,6 +8,7 @@ CPU path: a tensor that is not on a CUDA device is an error.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 
 import torch
 
@@ -18,14 +19,15 @@ _SUF = {torch.float32: "f32", torch.bfloat16: "bf16"}
 # p = pointer, i = int, l = long long, f = float
 _SIGNATURES = {
     "kvf_embed_{s}": "pppiiipp",
-    "kvf_add_rmsnorm_{s}": "pppppiifp",
+    "kvf_add_rmsnorm_{s}": "pppilpppiifp",
     "kvf_add_residual_{s}": "pplp",
-    "kvf_rope_cache_{s}": "ppppppiiiiiilpp",
-    "kvf_silu_mul_{s}": "pplip",
+    "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
+    "kvf_silu_mul_{s}": "ppliip",
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiippp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiippp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
+    "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_sample_f32": "pliippppppp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
@@ -54,6 +56,22 @@ def _fn(name: str, lib: str = "core", signature: str | None = None):
         f.restype = ctypes.c_int
         _bound[key] = f
     return f
+
+
+@dataclass
+class Partials:
+    """The float slices ``[S, M, N]`` that a split-K product leaves; whoever consumes them
+    sums them in slice order."""
+
+    t: torch.Tensor
+
+    @property
+    def nsplit(self) -> int:
+        return self.t.shape[0]
+
+    @property
+    def split_stride(self) -> int:
+        return self.t.stride(0)
 
 
 def _stream() -> int:
@@ -109,7 +127,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torc
 
 def add_rmsnorm(
     resid: torch.Tensor,
-    delta: torch.Tensor | None,
+    delta: torch.Tensor | Partials | None,
     weight: torch.Tensor,
     out: torch.Tensor,
     eps: float,
@@ -117,6 +135,7 @@ def add_rmsnorm(
 ) -> None:
     """``v = resid (+ delta)``; ``out = T(v * rsqrt(mean(v^2) + eps) * weight)``.
 
+    ``delta`` is a tensor in the storage type or the ``Partials`` of a split-K product.
     Without ``rows`` the sum is written back into ``resid``.  With ``rows`` (int32 ``[R]``)
     row ``r`` of ``out`` comes from row ``rows[r]`` and ``resid`` is left as it is.
     """
@@ -128,10 +147,17 @@ def add_rmsnorm(
     n_rows = out.shape[0]
     if out.shape[-1] != h or weight.numel() != h:
         raise ValueError("add_rmsnorm: widths do not agree")
-    if delta is not None:
+    dptr, pptr, nsplit, stride = None, None, 0, 0
+    if isinstance(delta, Partials):
+        _need(delta.t, torch.float32, "partials", contiguous=False)
+        if delta.t.shape[-1] != h or delta.t.stride(1) != h or delta.t.stride(2) != 1:
+            raise ValueError("add_rmsnorm: partials must be [S, M, H] with dense rows")
+        pptr, nsplit, stride = _ptr(delta.t), delta.nsplit, delta.split_stride
+    elif delta is not None:
         _need(delta, out.dtype, "delta")
         if delta.shape[-1] != h:
             raise ValueError("add_rmsnorm: delta width")
+        dptr = _ptr(delta)
     if rows is not None:
         _need(rows, torch.int32, "rows")
         if rows.numel() < n_rows:
@@ -140,7 +166,7 @@ def add_rmsnorm(
         raise ValueError("add_rmsnorm: fewer residual rows than output rows")
     name = f"kvf_add_rmsnorm_{s}"
     _check(
-        _fn(name)(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_rows, h, float(eps), _stream()),
+        _fn(name)(_ptr(resid), dptr, pptr, nsplit, stride, _ptr(weight), _ptr(out), _ptr(rows), n_rows, h, float(eps), _stream()),
         name,
     )
 
@@ -157,7 +183,7 @@ def add_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
 
 
 def rope_cache_write(
-    qkv: torch.Tensor,
+    qkv: torch.Tensor | Partials,
     positions: torch.Tensor,
     inv_freq: torch.Tensor,
     slots: torch.Tensor | None,
@@ -168,50 +194,89 @@ def rope_cache_write(
     d: int,
     block_size: int,
     err: torch.Tensor | None = None,
+    q_out: torch.Tensor | None = None,
 ) -> None:
-    """Rotate q (in place) and k of ``qkv [N, (nh+2nkv)*d]``; write k and v to their slots.
+    """Rotate q and k of ``qkv [N, (nh+2nkv)*d]``; write k and v to their slots.
 
+    ``qkv`` in the storage type: q is rotated in place.  ``qkv`` as ``Partials`` of a split-K
+    product: the slices are summed in float and q goes to ``q_out [N, nh*d]``.
     ``inv_freq`` float ``[rot/2]`` fixes how many leading dims turn (``rot <= d``).
     ``kcache/vcache``: ``[num_blocks, nkv, block_size, d]``.  ``slots=None`` rotates q only.
     """
-    s = _suffix(qkv.dtype)
-    _need(qkv, None, "qkv")
+    width = (nh + 2 * nkv) * d
+    qptr, pptr, nsplit, stride, qo = None, None, 0, 0, None
+    if isinstance(qkv, Partials):
+        if q_out is None:
+            raise ValueError("rope_cache_write: partials need q_out")
+        _need(qkv.t, torch.float32, "partials", contiguous=False)
+        if qkv.t.shape[-1] != width or qkv.t.stride(1) != width or qkv.t.stride(2) != 1:
+            raise ValueError("rope_cache_write: partials must be [S, N, width] with dense rows")
+        n = qkv.t.shape[1]
+        dtype = q_out.dtype
+        _need(q_out, None, "q_out")
+        if tuple(q_out.shape) != (n, nh * d):
+            raise ValueError("rope_cache_write: q_out shape")
+        pptr, nsplit, stride, qo = _ptr(qkv.t), qkv.nsplit, qkv.split_stride, _ptr(q_out)
+    else:
+        _need(qkv, None, "qkv")
+        n = qkv.shape[0]
+        dtype = qkv.dtype
+        if qkv.shape[1] != width:
+            raise ValueError("rope_cache_write: qkv width")
+        qptr = _ptr(qkv)
+        if q_out is not None:
+            _need(q_out, dtype, "q_out")
+            qo = _ptr(q_out)
+    s = _suffix(dtype)
     _need(positions, torch.int32, "positions")
     _need(inv_freq, torch.float32, "inv_freq")
-    n = qkv.shape[0]
-    if qkv.shape[1] != (nh + 2 * nkv) * d:
-        raise ValueError("rope_cache_write: qkv width")
     rot = 2 * inv_freq.numel()
     if rot > d:
         raise ValueError("rope_cache_write: more frequencies than head_dim/2")
     num_slots = 0
     if slots is not None:
         _need(slots, torch.int32, "slots")
-        _need(kcache, qkv.dtype, "kcache")
-        _need(vcache, qkv.dtype, "vcache")
+        _need(kcache, dtype, "kcache")
+        _need(vcache, dtype, "vcache")
         if tuple(kcache.shape[1:]) != (nkv, block_size, d) or kcache.shape != vcache.shape:
             raise ValueError("rope_cache_write: cache shape must be [num_blocks, nkv, block_size, d]")
         num_slots = kcache.shape[0] * block_size
     name = f"kvf_rope_cache_{s}"
     _check(
         _fn(name)(
-            _ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(kcache), _ptr(vcache),
+            qptr, pptr, nsplit, stride, qo, _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(kcache), _ptr(vcache),
             n, nh, nkv, d, rot, block_size, num_slots, _ptr(err), _stream(),
         ),
         name,
     )  # fmt: skip
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]`` computed in float."""
+GATE_UP_BLOCK = 8  # gate and up rows alternate in blocks of this many in the interleaved layout
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``[g0..7, u0..7, g8..15, u8..15, ...]``: the row order in which the skinny product finds
+    ``gate_i`` and ``up_i`` in one thread's accumulators."""
+    i, h = w_gate.shape
+    if i % GATE_UP_BLOCK:
+        raise ValueError("interleave_gate_up: the intermediate size must be a multiple of 8")
+    b = GATE_UP_BLOCK
+    return torch.stack([w_gate.view(i // b, b, h), w_up.view(i // b, b, h)], dim=1).reshape(2 * i, h).contiguous()
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """``out[n, i] = silu(gate_i) * up_i`` computed in float.  Columns of ``gate_up [N, 2I]``:
+    all gates then all ups, or (``interleaved``) alternating in blocks of 8."""
     s = _suffix(gate_up.dtype)
     _need(gate_up, None, "gate_up")
     _need(out, gate_up.dtype, "out")
     n, i2 = gate_up.shape
     if out.shape[0] != n or out.shape[1] * 2 != i2:
         raise ValueError("silu_mul: shapes do not agree")
+    if interleaved and out.shape[1] % GATE_UP_BLOCK:
+        raise ValueError("silu_mul: interleaved layout needs a multiple of 8")
     name = f"kvf_silu_mul_{s}"
-    _check(_fn(name)(_ptr(gate_up), _ptr(out), n, out.shape[1], _stream()), name)
+    _check(_fn(name)(_ptr(gate_up), _ptr(out), n, out.shape[1], GATE_UP_BLOCK if interleaved else 0, _stream()), name)
 
 
 def cast_from_float(src: torch.Tensor, out: torch.Tensor) -> None:
@@ -353,6 +418,67 @@ def gemm_nt_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _fn(name)(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), w.stride(0), out.stride(0), _stream()),
         name,
     )
+
+
+SKINNY_MAX_M = 64
+SKINNY_MAX_SPLIT = 16
+
+
+def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the decode product (``csrc/gemm_skinny_bf16.cu``) takes ``x @ w^T``."""
+    return (
+        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_M
+        and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+    )  # fmt: skip
+
+
+def skinny_splits(n_out: int, k: int) -> int:
+    """Slices of K so that a product with few output rows still fills the SMs (about 256 CTAs
+    of 64 rows), each slice at least 256 wide."""
+    ctas = -(-n_out // 64)
+    want = round(256 / ctas)
+    return max(1, min(want, k // 256, SKINNY_MAX_SPLIT))
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | Partials, mode: str = "plain") -> None:
+    """``x [M<=64, K] @ w [N, K]^T`` in bfloat16 with float accumulation.
+
+    ``out``: a bfloat16 or float ``[M, N]`` tensor, ``Partials`` (``[S, M, N]`` float, one slice
+    of K each), or with ``mode="silu"`` a bfloat16 ``[M, N/2]`` tensor that receives
+    ``silu(gate) * up`` for ``w`` in the interleaved gate/up layout.
+    """
+    if not skinny_ok(x, w):
+        raise ValueError("gemm_skinny: needs bfloat16, M <= 64, K % 8 == 0, unit inner strides")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError("gemm_skinny: inner sizes differ")
+    ksplit, stride = 1, 0
+    if isinstance(out, Partials):
+        t = out.t
+        _need(t, torch.float32, "partials", contiguous=False)
+        if tuple(t.shape[1:]) != (m, n) or t.stride(2) != 1:
+            raise ValueError("gemm_skinny: partials must be [S, M, N]")
+        code, ksplit, stride, ldo, optr = 2, t.shape[0], t.stride(0), t.stride(1), _ptr(t)
+    else:
+        _need(out, None, "out", contiguous=False)
+        if out.stride(1) != 1:
+            raise ValueError("gemm_skinny: out needs unit inner stride")
+        if mode == "silu":
+            if out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n // 2):
+                raise ValueError("gemm_skinny: silu output must be bfloat16 [M, N/2]")
+            code = 3
+        elif tuple(out.shape) != (m, n):
+            raise ValueError("gemm_skinny: out shape")
+        elif out.dtype == torch.bfloat16:
+            code = 0
+        elif out.dtype == torch.float32:
+            code = 1
+        else:
+            raise TypeError("gemm_skinny: out must be bfloat16 or float32")
+        ldo, optr = out.stride(0), _ptr(out)
+    name = "kvf_gemm_skinny_bf16"
+    _check(_fn(name)(_ptr(x), _ptr(w), optr, m, n, k, x.stride(0), w.stride(0), ldo, code, ksplit, stride, _stream()), name)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

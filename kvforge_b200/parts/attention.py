@@ -17,6 +17,27 @@ from .. import ops
 from .base import CacheNeed, Mixer, PartSpec, WeightDecl, build_part, register_mixer
 
 
+_PART_ROWS = ops.SKINNY_MAX_M * ops.SKINNY_MAX_SPLIT  # rows of the largest set of split-K slices
+
+
+def _project(rt, name: str, x: torch.Tensor, w: torch.Tensor):
+    """``x @ w^T`` back to the model width: the decode product (slices of K, summed by the norm
+    that follows) for a few tokens, the library product otherwise."""
+    n, width = x.shape[0], w.shape[0]
+    if ops.skinny_ok(x, w):
+        splits = ops.skinny_splits(width, w.shape[1])
+        if splits > 1:
+            part = ops.Partials(rt.buf(name + "_part", splits * n, width, torch.float32, cap=_PART_ROWS).view(splits, n, width))
+            ops.gemm_skinny(x, w, part)
+            return part
+        y = rt.buf(name, n, width)
+        ops.gemm_skinny(x, w, y)
+        return y
+    y = rt.buf(name, n, width)
+    ops.linear(x, w, y)
+    return y
+
+
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``; optional
@@ -86,14 +107,25 @@ class PagedAttention(Mixer):
         n = x.shape[0]
         if cache is None:
             raise RuntimeError("paged_attention needs a cache")
+        skinny = ops.skinny_ok(x, self.w_qkv)
         if cache.writable:
-            qkv = rt.buf("attn.qkv", n, self.qkv_dim)
-            ops.linear(x, self.w_qkv, qkv)
-            ops.rope_cache_write(
-                qkv, ctx.positions, self.inv_freq, ctx.slot_mappings[cache.group], cache.k, cache.v,
-                self.nh, self.nkv, self.d, ctx.block_size, rt.err,
-            )  # fmt: skip
-            q, q_stride = qkv, self.qkv_dim
+            slots = ctx.slot_mappings[cache.group]
+            splits = ops.skinny_splits(self.qkv_dim, self.hidden) if skinny else 1
+            if splits > 1:
+                # decode: slices of K in parallel; the rotation kernel sums them
+                part = ops.Partials(rt.buf("attn.qkv_part", splits * n, self.qkv_dim, torch.float32, cap=_PART_ROWS).view(splits, n, self.qkv_dim))
+                ops.gemm_skinny(x, self.w_qkv, part)
+                q = rt.buf("attn.q", n, self.q_dim)
+                ops.rope_cache_write(part, ctx.positions, self.inv_freq, slots, cache.k, cache.v, self.nh, self.nkv, self.d, ctx.block_size, rt.err, q_out=q)
+                q_stride = self.q_dim
+            else:
+                qkv = rt.buf("attn.qkv", n, self.qkv_dim)
+                if skinny:
+                    ops.gemm_skinny(x, self.w_qkv, qkv)
+                else:
+                    ops.linear(x, self.w_qkv, qkv)
+                ops.rope_cache_write(qkv, ctx.positions, self.inv_freq, slots, cache.k, cache.v, self.nh, self.nkv, self.d, ctx.block_size, rt.err)
+                q, q_stride = qkv, self.qkv_dim
         else:
             # reads another call's keys and values: only the queries are needed
             q = rt.buf("attn.q", n, self.q_dim)
@@ -102,9 +134,7 @@ class PagedAttention(Mixer):
             q_stride = self.q_dim
         out = rt.buf("attn.out", n, self.q_dim)
         self.attend(ctx, q, q_stride, out, cache)
-        y = rt.buf("attn.proj", n, self.hidden)
-        ops.linear(out, self.w_o, y)
-        return y
+        return _project(rt, "attn.proj", out, self.w_o)
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256

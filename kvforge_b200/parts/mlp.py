@@ -7,6 +7,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from .attention import _project
 from .base import FeedForward, WeightDecl, register_feed_forward
 
 
@@ -33,16 +34,24 @@ class GatedMLP(FeedForward):
 
     def bind(self, weights, rt):
         super().bind(weights, rt)
-        self.w_gate_up = torch.cat([weights["gate_proj.weight"], weights["up_proj.weight"]], dim=0).contiguous()
+        gate, up = weights["gate_proj.weight"], weights["up_proj.weight"]
+        # bfloat16: gate and up rows alternate in blocks of 8, the order in which the decode
+        # product finds gate_i and up_i in one thread; float32: all gates, then all ups
+        self.interleaved = gate.dtype == torch.bfloat16 and self.inter % ops.GATE_UP_BLOCK == 0 and self.inter % 8 == 0
+        if self.interleaved:
+            self.w_gate_up = ops.interleave_gate_up(gate, up)
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights["down_proj.weight"].contiguous()
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, x: torch.Tensor):
         rt = self.rt
         n = x.shape[0]
-        gu = rt.buf("mlp.gate_up", n, 2 * self.inter)
-        ops.linear(x, self.w_gate_up, gu)
         act = rt.buf("mlp.act", n, self.inter)
-        ops.silu_mul(gu, act)
-        y = rt.buf("mlp.out", n, self.hidden)
-        ops.linear(act, self.w_down, y)
-        return y
+        if self.interleaved and ops.skinny_ok(x, self.w_gate_up):
+            ops.gemm_skinny(x, self.w_gate_up, act, mode="silu")
+        else:
+            gu = rt.buf("mlp.gate_up", n, 2 * self.inter)
+            ops.linear(x, self.w_gate_up, gu)
+            ops.silu_mul(gu, act, interleaved=self.interleaved)
+        return _project(rt, "mlp.out", act, self.w_down)

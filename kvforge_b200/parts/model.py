@@ -173,5 +173,8 @@ class DecoderModel:
         if r == 0:
             return logits
         x = self.final_norm.forward(ctx, resid, delta, rows=ctx.logit_rows, num_rows=r)
-        ops.linear(x, self.lm_head, logits)
+        if ops.skinny_ok(x, self.lm_head):
+            ops.gemm_skinny(x, self.lm_head, logits)
+        else:
+            ops.linear(x, self.lm_head, logits)
         return logits

@@ -30,7 +30,8 @@ class RMSNorm(Norm):
         super().bind(weights, rt)
         self.weight = weights["weight"]
 
-    def forward(self, ctx, resid: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None, num_rows: int | None = None):
+    def forward(self, ctx, resid: torch.Tensor, delta, rows: torch.Tensor | None = None, num_rows: int | None = None):
+        """``delta``: ``None``, a tensor in the storage type, or ``ops.Partials``."""
         n = num_rows if rows is not None else resid.shape[0]
         out = self.rt.buf("norm.out" if rows is None else "norm.rows", n, self.dim)
         ops.add_rmsnorm(resid, delta, self.weight, out, self.eps, rows)

@@ -75,6 +75,8 @@ def test_silu_mul(ops, dtype):
     g, u = gu[:, :93].float(), gu[:, 93:].float()
     ref = torch.nn.functional.silu(g) * u
     assert torch.allclose(out.float().cpu(), ref, rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+    with pytest.raises(ValueError):
+        ops.silu_mul(dev(gu), out, interleaved=True)  # 93 is no multiple of 8
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 100, 33), (7, 64, 64), (130, 203, 80), (65, 3, 1000)])
@@ -125,6 +127,88 @@ def test_rope_and_cache_write(ops, dtype, nh, nkv, d, rot, bs):
     untouched = torch.ones(nb * bs, dtype=torch.bool)
     untouched[slots.long()] = False
     assert (kc_flat[untouched] == 0).all() and (vc_flat[untouched] == 0).all()
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("n,k", [(64, 64), (203, 80), (3072, 2048), (100, 1000), (2048, 8192), (16, 8)])
+def test_gemm_skinny(ops, m, n, k):
+    g = torch.Generator().manual_seed(m * 1000 + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.1).bfloat16()
+    ref = x.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    out16 = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(dev(x), dev(w), out16)
+    assert float((out16.double().cpu() - ref).abs().max()) < 1e-2 * scale
+    out32 = torch.empty(m, n, device="cuda")
+    ops.gemm_skinny(dev(x), dev(w), out32)
+    assert float((out32.double().cpu() - ref).abs().max()) < 2e-5 * scale * max(1.0, k**0.5 / 8)
+    for splits in {1, ops.skinny_splits(n, k), min(3, max(1, k // 64))}:
+        part = ops.Partials(torch.full((splits, m, n), float("nan"), device="cuda"))
+        ops.gemm_skinny(dev(x), dev(w), part)
+        assert float((part.t.double().sum(0).cpu() - ref).abs().max()) < 2e-5 * scale * max(1.0, k**0.5 / 8), splits
+
+
+def test_gemm_skinny_rows_do_not_depend_on_the_batch(ops):
+    x = torch.randn(40, 256).bfloat16()
+    w = torch.randn(300, 256).bfloat16()
+    full = torch.empty(40, 300, device="cuda")
+    ops.gemm_skinny(dev(x), dev(w), full)
+    one = torch.empty(1, 300, device="cuda")
+    ops.gemm_skinny(dev(x[17:18]), dev(w), one)
+    assert torch.equal(one[0], full[17])
+
+
+@pytest.mark.parametrize("m,i,h", [(5, 96, 64), (64, 8192, 256), (1, 200, 80)])
+def test_gemm_skinny_with_the_gate(ops, m, i, h):
+    x = torch.randn(m, h).bfloat16()
+    wg, wu = (torch.randn(i, h) * 0.2).bfloat16(), (torch.randn(i, h) * 0.2).bfloat16()
+    w = ops.interleave_gate_up(dev(wg), dev(wu))
+    out = torch.empty(m, i, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(dev(x), w, out, mode="silu")
+    ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert float((out.float().cpu() - ref).abs().max()) < 1e-2 * float(ref.abs().max())
+    # the library product on the interleaved weight followed by the gate kernel agrees
+    gu = (x.float() @ w.float().cpu().t()).bfloat16()
+    out2 = torch.empty(m, i, device="cuda", dtype=torch.bfloat16)
+    ops.silu_mul(dev(gu), out2, interleaved=True)
+    assert float((out2.float().cpu() - ref).abs().max()) < 2e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_and_rope_sum_the_slices_of_a_split_product(ops, dtype):
+    n, h, splits = 6, 100, 3
+    resid = torch.randn(n, h)
+    parts = torch.randn(splits, n, h)
+    w = torch.rand(h) + 0.5
+    r = dev(resid)
+    out = torch.empty(n, h, device="cuda", dtype=dtype)
+    ops.add_rmsnorm(r, ops.Partials(dev(parts)), dev(w), out, 1e-5)
+    summed = resid + parts.sum(0)
+    assert torch.allclose(r.cpu(), summed, atol=1e-5)
+    assert torch.allclose(out.float().cpu(), rms_norm(summed, w, 1e-5), rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+    rows = torch.tensor([5, 5, 0], dtype=torch.int32)
+    r2 = dev(resid)
+    out2 = torch.empty(3, h, device="cuda", dtype=dtype)
+    ops.add_rmsnorm(r2, ops.Partials(dev(parts)), dev(w), out2, 1e-5, rows=dev(rows))
+    assert torch.equal(r2.cpu(), resid)
+    assert torch.allclose(out2.float().cpu(), rms_norm(summed, w, 1e-5)[rows.long()], rtol=tol(dtype) * 4, atol=tol(dtype) * 4)
+    # rotation from slices: the same as from their sum
+    nh, nkv, d, bs, nb = 3, 1, 32, 8, 4
+    width = (nh + 2 * nkv) * d
+    qkv_parts = torch.randn(splits, n, width)
+    positions = torch.tensor([0, 1, 7, 8, 100, 4000], dtype=torch.int32)
+    slots = torch.tensor([3, 9, 17, 31, 0, 12], dtype=torch.int32)
+    inv = plain_inv_freq(d, 10000.0)
+    kc1 = torch.zeros(nb, nkv, bs, d, device="cuda", dtype=dtype)
+    vc1, kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(kc1), torch.zeros_like(kc1)
+    q1 = torch.empty(n, nh * d, device="cuda", dtype=dtype)
+    ops.rope_cache_write(ops.Partials(dev(qkv_parts)), dev(positions), dev(inv), dev(slots), kc1, vc1, nh, nkv, d, bs, q_out=q1)
+    whole = dev(qkv_parts.sum(0).to(dtype))
+    ops.rope_cache_write(whole, dev(positions), dev(inv), dev(slots), kc2, vc2, nh, nkv, d, bs)
+    t = tol(dtype) * 8
+    assert torch.allclose(q1.float(), whole[:, : nh * d].float(), rtol=t, atol=t)
+    assert torch.allclose(kc1.float(), kc2.float(), rtol=t, atol=t) and torch.allclose(vc1.float(), vc2.float(), rtol=t, atol=t)
 
 
 # ------------------------------------------------------------------ attention
