@@ -311,7 +311,7 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
                             const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                             int max_q_len, int q_stride, int out_stride, int bt_stride, int nh, int nkv,
                             int d, int block_size, float scale, int window, int split_size, int max_splits,
-                            float* part_acc, float* part_ml, cudaStream_t st) {
+                            int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (d <= 0 || d > 256 || (d % 8) != 0 || nkv <= 0 || nh % nkv != 0 || block_size <= 0)
     return (int)cudaErrorInvalidValue;
@@ -332,7 +332,8 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
     // decode form: one query per sequence, key ranges in grid.x, then a merge
     if (split_size % TK != 0 || max_splits <= 0 || !part_acc || !part_ml) return (int)cudaErrorInvalidValue;
     p.tq = 1;
-    dim3 grid(max_splits, B, nkv * p.chunks);
+    // grid over the ranges that can be non-empty; max_splits is the scratch's stride
+    dim3 grid(grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits, B, nkv * p.chunks);
     int rc = dispatch_dpl<T, true>(p, grid, st);
     if (rc) return rc;
     attn_combine_kernel<T><<<dim3(nh, B), 64, 0, st>>>(part_acc, part_ml, (T*)out, qsl, ctx_lens, nh, d,
@@ -350,10 +351,11 @@ int paged_attention_generic(const void* q, void* out, const void* kcache, const 
       const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables,          \
       const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,            \
       int bt_stride, int nh, int nkv, int d, int block_size, float scale, int window, int split_size,     \
-      int max_splits, float* part_acc, float* part_ml, cudaStream_t st) {                                 \
+      int max_splits, int grid_splits, float* part_acc, float* part_ml, cudaStream_t st) {                \
     return paged_attention_generic<T>(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len,  \
                                       q_stride, out_stride, bt_stride, nh, nkv, d, block_size, scale,     \
-                                      window, split_size, max_splits, part_acc, part_ml, st);             \
+                                      window, split_size, max_splits, grid_splits, part_acc, part_ml,     \
+                                      st);                                                                \
   }
 
 KVF_ATTN_API(f32, float)

@@ -39,7 +39,8 @@ struct MmaParams {
   int q_stride, out_stride, bt_stride;
   int nh, nkv, block_size;
   int window;
-  int split_size, max_splits;
+  int split_size, max_splits;  // max_splits: slices the scratch has room for per (sequence, head)
+  int grid_splits;             // ranges that can be non-empty: ceil(longest context / split_size)
   float scale_log2;  // scale * log2(e)
 };
 
@@ -412,30 +413,43 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
 }
 
 // Merge the partial results of the key ranges of one (sequence, head), in range order.
-__global__ void attn_mma_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                      bf16* __restrict__ out, const int* __restrict__ qsl,
-                                      const int* __restrict__ ctx_lens, int nh, int d, int out_stride,
-                                      int split_size, int max_splits) {
+// One CTA of 128 threads per (sequence, head): weights of the ranges first, then each thread
+// one output dim.
+__global__ void __launch_bounds__(128)
+attn_mma_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                      bf16* __restrict__ out, const int* __restrict__ qsl, const int* __restrict__ ctx_lens,
+                      int nh, int d, int out_stride, int split_size, int max_splits) {
+  __shared__ float wgt[1024];
+  __shared__ float red[32];
   const int b = blockIdx.y, head = blockIdx.x;
   const int q_begin = qsl[b], q_len = qsl[b + 1] - q_begin;
   const int ctx = ctx_lens[b];
   if (q_len <= 0 || ctx <= 0) return;
-  const int ns = min(max_splits, (ctx + split_size - 1) / split_size);
+  const int ns = min(min(max_splits, 1024), (ctx + split_size - 1) / split_size);
   const size_t base = ((size_t)b * nh + head) * max_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < ns; ++s) {
+  float mx = -INFINITY;
+  for (int s = threadIdx.x; s < ns; s += blockDim.x) {
     const float ms = part_ml[(base + s) * 2];
-    if (ms != -INFINITY) L += __expf(ms - M) * part_ml[(base + s) * 2 + 1];
+    wgt[s] = ms;
+    mx = fmaxf(mx, ms);
   }
+  const float M = block_max(mx, red);
+  float lsum = 0.f;
+  for (int s = threadIdx.x; s < ns; s += blockDim.x) {
+    const float ms = wgt[s];
+    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+    wgt[s] = w;
+    lsum += w * part_ml[(base + s) * 2 + 1];
+  }
+  const float L = block_sum(lsum, red);  // also orders the writes of wgt before the reads below
   const float inv = L > 0.f ? 1.f / L : 0.f;
   bf16* o = out + (size_t)(q_begin + q_len - 1) * out_stride + (size_t)head * d;
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float a = 0.f;
+#pragma unroll 4
     for (int s = 0; s < ns; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      if (ms != -INFINITY) a += __expf(ms - M) * part_acc[(base + s) * d + j];
+      const float w = wgt[s];
+      if (w != 0.f) a += w * part_acc[(base + s) * d + j];  // an empty range wrote no sums
     }
     o[j] = __float2bfloat16_rn(a * inv);
   }
@@ -452,10 +466,10 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
       if (e != cudaSuccess) return (int)e;
     }
-    kern<<<dim3(p.max_splits, B, p.nkv), NWARPS * 32, need, st>>>(p);
+    kern<<<dim3(p.grid_splits, B, p.nkv), NWARPS * 32, need, st>>>(p);
     int rc = KVF_LAUNCH_STATUS();
     if (rc) return rc;
-    attn_mma_merge_kernel<<<dim3(p.nh, B), 64, 0, st>>>(p.part_acc, p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D,
+    attn_mma_merge_kernel<<<dim3(p.nh, B), 128, 0, st>>>(p.part_acc, p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D,
                                                         p.out_stride, p.split_size, p.max_splits);
     return KVF_LAUNCH_STATUS();
   }
@@ -478,7 +492,8 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
                                          const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                          int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
                                          int nkv, int d, int block_size, float scale, int window, int split_size,
-                                         int max_splits, float* part_acc, float* part_ml, cudaStream_t st) {
+                                         int max_splits, int grid_splits, float* part_acc, float* part_ml,
+                                         cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || block_size <= 0) return (int)cudaErrorInvalidValue;
   const int g = nh / nkv;
@@ -491,9 +506,10 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.split_size = split_size; p.max_splits = max_splits;
+  p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   if (split_size > 0) {
-    if (g > 16 || split_size % BN != 0 || max_splits <= 0 || !part_acc || !part_ml || max_q_len != 1)
+    if (g > 16 || split_size % BN != 0 || max_splits <= 0 || max_splits > 1024 || !part_acc || !part_ml || max_q_len != 1)
       return (int)cudaErrorInvalidValue;
   }
   return d == 64 ? launch_mma<64>(p, B, max_q_len, st) : launch_mma<128>(p, B, max_q_len, st);

@@ -71,6 +71,72 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   }
 }
 
+// The same for H % 4 == 0: 16-byte loads, the slices of a split product loaded side by side,
+// and the summed row kept in shared memory so that global memory is read once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       const float* __restrict__ partials, int nsplit, size_t split_stride,
+                                       const float* __restrict__ weight, T* __restrict__ out,
+                                       const int* __restrict__ rows, int H, float eps) {
+  extern __shared__ __align__(16) float rowbuf[];  // H floats
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* h = resid + (size_t)src * H;
+  const T* dl = delta ? delta + (size_t)src * H : nullptr;
+  const float* pt = partials ? partials + (size_t)src * H : nullptr;
+  const bool write_back = ((dl != nullptr) || (pt != nullptr)) && (rows == nullptr);
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(h + i);
+    if (dl) {
+      const float4 d = Vec4<T>::load(dl + i);
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    if (pt) {
+      float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int s = 0; s < nsplit; ++s) {  // slice order: reproducible
+        const float4 q = *reinterpret_cast<const float4*>(pt + (size_t)s * split_stride + i);
+        d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+      }
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    if (write_back) *reinterpret_cast<float4*>(h + i) = v;
+    *reinterpret_cast<float4*>(rowbuf + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  T* o = out + (size_t)r * H;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+    const float4 w = *reinterpret_cast<const float4*>(weight + i);
+    Vec4<T>::store(o + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+  }
+}
+
 // resid[r,:] += float(delta[r,:]) without a norm (used after the last layer when the
 // final norm reads gathered rows).
 template <typename T>
@@ -155,6 +221,66 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__
   }
 }
 
+// The same with one thread per (head, pair): grid (tokens, groups of heads), so that a few
+// tokens still spread over many SMs, and the slices of a split product loaded side by side.
+// Needs rot == d (the whole head turns) and an even d.
+template <typename T>
+__global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __restrict__ partials, int nsplit,
+                                        size_t split_stride, T* __restrict__ q_out,
+                                        const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                        const int* __restrict__ slots, T* __restrict__ kcache,
+                                        T* __restrict__ vcache, int nh, int nkv, int d, int block_size,
+                                        long long num_slots, int heads_per_cta, int* __restrict__ err) {
+  const int n = blockIdx.x;
+  const int half = d >> 1;
+  const int total_heads = nh + 2 * nkv;
+  const int stride = total_heads * d;
+  const int head = blockIdx.y * heads_per_cta + threadIdx.x / half;
+  const int j = threadIdx.x % half;
+  if (threadIdx.x >= heads_per_cta * half || head >= total_heads) return;
+  T* row = qkv ? qkv + (size_t)n * stride : nullptr;
+  const float* prow = partials ? partials + (size_t)n * stride : nullptr;
+  const int i1 = head * d + j, i2 = i1 + half;
+  float x1, x2;
+  if (prow) {
+    x1 = x2 = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) {  // slice order: reproducible
+      x1 += prow[(size_t)s * split_stride + i1];
+      x2 += prow[(size_t)s * split_stride + i2];
+    }
+  } else {
+    x1 = to_float<T>(row[i1]);
+    x2 = to_float<T>(row[i2]);
+  }
+  long long slot = slots ? (long long)slots[n] : -1;
+  if (slot >= num_slots) {
+    if (j == 0 && err) atomicOr(err, 2);
+    slot = -1;
+  }
+  T y1, y2;
+  if (head < nh + nkv) {
+    float sn, cs;
+    sincosf((float)positions[n] * inv_freq[j], &sn, &cs);
+    y1 = from_float<T>(x1 * cs - x2 * sn);
+    y2 = from_float<T>(x2 * cs + x1 * sn);
+  } else {
+    y1 = from_float<T>(x1);
+    y2 = from_float<T>(x2);
+  }
+  if (head < nh) {
+    T* qdst = q_out ? q_out + (size_t)n * nh * d : row;
+    qdst[(size_t)head * d + j] = y1;
+    qdst[(size_t)head * d + j + half] = y2;
+  } else if (slot >= 0) {
+    const bool is_k = head < nh + nkv;
+    const int kvh = is_k ? head - nh : head - nh - nkv;
+    T* dst = (is_k ? kcache : vcache) + (((size_t)(slot / block_size) * nkv + kvh) * block_size + (slot % block_size)) * d;
+    dst[j] = y1;
+    dst[j + half] = y2;
+  }
+}
+
 // ---------------------------------------------------------------- SiLU gate
 // out[n, i] = T( silu(float(g_i)) * float(u_i) ),  silu(t) = t / (1 + exp(-t)).
 // Columns of gu [N, 2I]: gates then ups (block == 0), or alternating in blocks of `block`
@@ -197,6 +323,20 @@ static inline int norm_threads(int H) {
                                     long long split_stride, const float* weight, void* out,              \
                                     const int* rows, int n_rows, int H, float eps, cudaStream_t st) {    \
     if (n_rows <= 0) return 0;                                                                           \
+    if ((H & 3) == 0 && H <= 32768 && (split_stride & 3) == 0) {                                         \
+      int t = 32;                                                                                        \
+      while (t < 1024 && t * 4 < H) t <<= 1;                                                             \
+      const size_t smem = (size_t)H * sizeof(float);                                                     \
+      if (smem > 48 * 1024) {                                                                            \
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<T>,                                  \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        if (e != cudaSuccess) return (int)e;                                                             \
+      }                                                                                                  \
+      add_rmsnorm_vec_kernel<T><<<n_rows, t, smem, st>>>(resid, (const T*)delta, partials, nsplit,       \
+                                                         (size_t)split_stride, weight, (T*)out, rows, H, \
+                                                         eps);                                           \
+      return KVF_LAUNCH_STATUS();                                                                        \
+    }                                                                                                    \
     add_rmsnorm_kernel<T><<<n_rows, norm_threads(H), 0, st>>>(resid, (const T*)delta, partials, nsplit,  \
                                                               (size_t)split_stride, weight, (T*)out,     \
                                                               rows, H, eps);                             \
@@ -215,6 +355,19 @@ static inline int norm_threads(int H) {
     if (N <= 0) return 0;                                                                                \
     if (rot < 0 || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;                              \
     if (!qkv && !(partials && q_out)) return (int)cudaErrorInvalidValue;                                 \
+    if (rot == d && d >= 2 && d <= 512) {                                                                \
+      const int half = d / 2;                                                                            \
+      int hpc = 128 / half;                                                                              \
+      if (hpc < 1) hpc = 1;                                                                              \
+      const int heads = nh + 2 * nkv;                                                                    \
+      dim3 grid(N, (heads + hpc - 1) / hpc);                                                             \
+      if (grid.y <= 65535u) {                                                                            \
+        rope_cache_heads_kernel<T><<<grid, hpc * half, 0, st>>>(                                         \
+            (T*)qkv, partials, nsplit, (size_t)split_stride, (T*)q_out, positions, inv_freq, slots,      \
+            (T*)kcache, (T*)vcache, nh, nkv, d, block_size, num_slots, hpc, err);                        \
+        return KVF_LAUNCH_STATUS();                                                                      \
+      }                                                                                                  \
+    }                                                                                                    \
     rope_cache_kernel<T><<<N, 256, 0, st>>>((T*)qkv, partials, nsplit, (size_t)split_stride, (T*)q_out,  \
                                             positions, inv_freq, slots, (T*)kcache, (T*)vcache, nh, nkv, \
                                             d, rot, block_size, num_slots, err);                         \

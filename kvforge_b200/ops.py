@@ -24,8 +24,8 @@ _SIGNATURES = {
     "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
     "kvf_silu_mul_{s}": "ppliip",
     "kvf_cast_from_float_{s}": "pplp",
-    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiippp",
-    "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiippp",
+    "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiiippp",
+    "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_sample_f32": "pliippppppp",
@@ -291,11 +291,18 @@ def cast_from_float(src: torch.Tensor, out: torch.Tensor) -> None:
 
 # ------------------------------------------------------------------ attention
 
-def attention_split_size(num_seqs: int, nkv: int) -> int:
+MAX_ATTN_SPLITS = 1024  # ranges per (sequence, head) the merge kernel takes
+
+
+def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
     """Keys per range of the decode form: smaller ranges when few (sequence, kv head) pairs
-    would leave SMs idle.  Ranges start at multiples of it, whatever the batch."""
+    would leave SMs idle, larger ones when the context is so long that there would be more
+    than ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of it, whatever the batch."""
     pairs = num_seqs * nkv
-    return 256 if pairs >= 64 else 128 if pairs >= 16 else 64
+    split = 256 if pairs >= 64 else 128 if pairs >= 16 else 64
+    while -(-max_context // split) > MAX_ATTN_SPLITS:
+        split *= 2
+    return split
 
 
 def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, split_size: int = 256) -> tuple[tuple[int, ...], tuple[int, ...]]:
@@ -361,7 +368,7 @@ def paged_attention(
     if q_stride is None:
         q_stride = q.shape[-1]
     bt_stride = block_tables.shape[-1] if block_tables.dim() == 2 else block_tables.numel() // max(1, num_seqs)
-    split, max_splits, pa, pm = 0, 0, None, None
+    split, max_splits, grid_splits, pa, pm = 0, 0, 0, None, None
     if scratch is not None:
         pa, pm = scratch
         _need(pa, torch.float32, "scratch acc")
@@ -376,6 +383,9 @@ def paged_attention(
             raise ValueError("paged_attention: scratch shape does not fit")
         if max_context is None or -(-max_context // split) > max_splits:
             raise ValueError("paged_attention: scratch is too small for the longest context")
+        grid_splits = max(1, -(-max_context // split))
+        if grid_splits > MAX_ATTN_SPLITS:
+            raise ValueError("paged_attention: too many key ranges; use a larger split_size")
     use_mma = mma_attention_supported(q.dtype, nh, nkv, d, scratch is not None)
     if kernel == "generic":
         use_mma = False
@@ -386,7 +396,7 @@ def paged_attention(
         _fn(name)(
             _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
             num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
-            int(window), split, max_splits, _ptr(pa), _ptr(pm), _stream(),
+            int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _stream(),
         ),
         name,
         2 if scratch is not None else 1,

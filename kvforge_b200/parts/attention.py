@@ -95,9 +95,10 @@ class PagedAttention(Mixer):
     def _scratch(self, ctx):
         rt = self.rt
         bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
-        split = ops.attention_split_size(ctx.num_seqs, self.nkv)
+        split = ops.attention_split_size(ctx.num_seqs, self.nkv, bound)
         # made for the smallest range size, so that one buffer serves every batch size
-        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, 64)
+        smallest = ops.attention_split_size(1, 1, bound)
+        sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)
         acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
         ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
         return (acc, ml), bound, split
