@@ -33,6 +33,9 @@ LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
         ["elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "attention_mma.cu", "gemm_skinny_bf16.cu", "sampling.cu"],
         [],
     ),
+    # one entry point that allocates nothing (csrc/kvforge_noalloc.h); a library of its own, so
+    # that only a process that asks for it holds its built-in scratch array
+    "noalloc": (["attention_decode_noalloc.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -63,7 +66,8 @@ def _digest(name: str) -> str:
     sources, flags = LIBRARIES[name]
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + flags).encode())
-    for f in sorted(set(sources) | {p.name for p in CSRC.glob("*.cuh")} | {p.name for p in CSRC.glob("*.h")}):
+    # every source and header: a source may include another (the hash errs on the side of rebuilding)
+    for f in sorted({p.name for pat in ("*.cu", "*.cuh", "*.h") for p in CSRC.glob(pat)} | set(sources)):
         h.update(f.encode())
         h.update((CSRC / f).read_bytes())
     return h.hexdigest()[:16]
