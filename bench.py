@@ -333,11 +333,84 @@ def run_own(args) -> dict:
     }
 
 
+def _graph_time(fn, calls: int, reps: int) -> float:
+    """Seconds per call of ``fn(i)``, ``calls`` of them captured in one CUDA graph (so that
+    launch overhead of the host does not count) and replayed ``reps`` times."""
+    import torch
+
+    for i in range(2):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(calls):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / 1e3 / (reps * calls)
+
+
+def run_kernel_only(args, cfg) -> dict:
+    """A single kernel of the decode step on the 1B shape, on inputs larger than L2 (several
+    copies of the weights or of the cache are cycled through)."""
+    import torch
+
+    from kvforge_b200 import ops
+
+    pk = peaks()
+    dev = "cuda"
+    nh, nkv, d, bs = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, 16
+    if args.only == "attention":
+        b, ctx = args.batch, args.context
+        nblk = b * (-(-ctx // bs))
+        copies = max(2, min(8, int(1.5e9 // max(1, nblk * nkv * bs * d * 4))))
+        kcs = [torch.randn(nblk, nkv, bs, d, device=dev).bfloat16() for _ in range(copies)]
+        vcs = [torch.randn(nblk, nkv, bs, d, device=dev).bfloat16() for _ in range(copies)]
+        tables = torch.randperm(nblk, device=dev).int().view(b, -1).contiguous()
+        q = torch.randn(b, nh * d, device=dev).bfloat16()
+        out = torch.empty(b, nh * d, device=dev, dtype=torch.bfloat16)
+        qsl = torch.arange(b + 1, device=dev, dtype=torch.int32)
+        cl = torch.full((b,), ctx, device=dev, dtype=torch.int32)
+        split = args.split or ops.attention_split_size(b, nkv, ctx)
+        sa, sm = ops.attention_scratch_shapes(b, nh, d, ctx, split)
+        scratch = (torch.empty(sa, device=dev), torch.empty(sm, device=dev))
+        sec = _graph_time(
+            lambda i: ops.paged_attention(q, out, kcs[i % copies], vcs[i % copies], tables, qsl, cl, b, 1, nh, nkv, d,
+                                          d**-0.5, scratch=scratch, max_context=ctx, split_size=split),
+            calls=max(2, args.steps), reps=3,
+        )  # fmt: skip
+        nbytes = b * ctx * 2 * nkv * d * 2
+        return {"only": "attention", "batch": b, "context": ctx, "split": split, "us": round(sec * 1e6, 2),
+                "GB/s": round(nbytes / sec / 1e9, 1), "frac_of_hbm_peak": round(nbytes / sec / 1e9 / pk["hbm_gbs"], 3)}  # fmt: skip
+    shapes = {"qkv": ((nh + 2 * nkv) * d, cfg.hidden_size), "o": (cfg.hidden_size, nh * d),
+              "gate_up": (2 * cfg.intermediate_size, cfg.hidden_size), "down": (cfg.hidden_size, cfg.intermediate_size),
+              "lm_head": (cfg.vocab_size, cfg.hidden_size)}  # fmt: skip
+    n, k = shapes[args.shape]
+    m = args.batch
+    copies = max(2, min(12, int(1.2e9 // (n * k * 2))))
+    ws = [(torch.randn(n, k, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+    x = torch.randn(m, k, device=dev).bfloat16()
+    splits = ops.skinny_splits(n, k)
+    out = ops.Partials(torch.empty(splits, m, n, device=dev)) if splits > 1 else torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+    sec = _graph_time(lambda i: ops.gemm_skinny(x, ws[i % copies], out), calls=max(2, args.steps), reps=3)
+    nbytes = n * k * 2
+    return {"only": "gemm", "shape": args.shape, "M": m, "N": n, "K": k, "splits": splits, "us": round(sec * 1e6, 2),
+            "GB/s": round(nbytes / sec / 1e9, 1), "frac_of_hbm_peak": round(nbytes / sec / 1e9 / pk["hbm_gbs"], 3)}  # fmt: skip
+
+
 def run_only(args) -> dict:
     """One part alone on a small footing: what the profiler is pointed at."""
     from kvforge_b200 import PRESETS
 
     cfg = PRESETS["llama-3.2-1b"]
+    if args.only in ("attention", "gemm"):
+        return run_kernel_only(args, cfg)
     ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
     core = make_core(cfg, max(args.batch, 1), PREFILL_TOKENS, ctx_cap, cuda_graphs=not args.no_graphs)
     if args.only == "decode":
@@ -363,7 +436,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--only", choices=["decode", "prefill", "attention", "gemm"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
+    ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="with --only decode: tokens already in each cache")
     ap.add_argument("--no-graphs", action="store_true", help="with --only: launch kernels one by one instead of replaying a graph")

@@ -38,6 +38,7 @@ struct MmaParams {
   float* part_ml;   // split form: [B][nh][max_splits][2]  (m in natural-log units, l)
   int q_stride, out_stride, bt_stride;
   int nh, nkv, block_size;
+  int bs_shift;  // log2(block_size) if it is a power of two, else -1
   int window;
   int split_size, max_splits;  // max_splits: slices the scratch has room for per (sequence, head)
   int grid_splits;             // ranges that can be non-empty: ceil(longest context / split_size)
@@ -82,21 +83,44 @@ template <int D> __device__ __forceinline__ uint32_t tile_off(int row, int chunk
 }
 
 // Bring keys [t0, t0+BN) of one kv head into a K and a V tile.  Keys at or past `ctx` and
-// keys in pages that were given back (table entry < 0) are zero-filled.
+// keys in pages that were given back (table entry < 0) are zero-filled.  What does not
+// change from tile to tile (which keys and chunk a thread moves, where they land in the
+// swizzled tile) is worked out once.
 template <int D>
-__device__ __forceinline__ void load_kv_tile(const MmaParams& p, const int* bt, int kvh, int ctx, int t0,
-                                             uint32_t ks, uint32_t vs) {
-  constexpr int CH = D / 8;
-  for (int idx = threadIdx.x; idx < BN * CH; idx += NWARPS * 32) {
-    const int key = idx / CH, c = idx - key * CH;
-    const int kp = t0 + key;
-    const int blk = kp < ctx ? bt[kp / p.block_size] : -1;
-    const bool valid = blk >= 0;
-    const size_t base = valid ? ((((size_t)blk * p.nkv + kvh) * p.block_size + (kp % p.block_size)) * D + c * 8) : 0;
-    cp_async16(ks + tile_off<D>(key, c), p.kcache + base, valid);
-    cp_async16(vs + tile_off<D>(key, c), p.vcache + base, valid);
+struct TileLoader {
+  static constexpr int CH = D / 8;                       // 16-byte chunks per key
+  static constexpr int ITER = BN * CH / (NWARPS * 32);   // chunks per thread and tile
+  static constexpr int KEY_STEP = (NWARPS * 32) / CH;    // keys between a thread's chunks
+  int key0, chunk;
+  uint32_t soff[ITER];
+  __device__ __forceinline__ void init() {
+    key0 = threadIdx.x / CH;
+    chunk = threadIdx.x % CH;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) soff[i] = tile_off<D>(key0 + i * KEY_STEP, chunk);
   }
-}
+  __device__ __forceinline__ void load(const MmaParams& p, const int* bt, int kvh, int ctx, int t0, uint32_t ks,
+                                       uint32_t vs) const {
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+      const int kp = t0 + key0 + i * KEY_STEP;
+      int blk = -1, off = 0;
+      if (kp < ctx) {
+        if (p.bs_shift >= 0) {
+          blk = bt[kp >> p.bs_shift];
+          off = kp & (p.block_size - 1);
+        } else {
+          blk = bt[kp / p.block_size];
+          off = kp % p.block_size;
+        }
+      }
+      const bool valid = blk >= 0;
+      const size_t base = valid ? (((size_t)blk * p.nkv + kvh) * p.block_size + off) * D + chunk * 8 : 0;
+      cp_async16(ks + soff[i], p.kcache + base, valid);
+      cp_async16(vs + soff[i], p.vcache + base, valid);
+    }
+  }
+};
 
 // S[16 x (8*NT)] += Q[16 x D] K^T for the n-tiles [nt0, nt0+NT) of the K tile at `ks`.
 template <int D, int NT>
@@ -145,26 +169,40 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[2
 template <int NT, int ND>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4], float (&m)[2], float (&l)[2],
                                              const int (&lo)[2], const int (&hi)[2], int key0, float scale_log2,
-                                             int lane) {
+                                             int lane, bool need_mask) {
   float mx[2] = {-INFINITY, -INFINITY};
+  if (need_mask) {  // warp-uniform: only tiles that straddle an edge of what the rows see
 #pragma unroll
-  for (int j = 0; j < NT; ++j) {
+    for (int j = 0; j < NT; ++j) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int r = e >> 1;
-      const int kp = key0 + j * 8 + ((lane & 3) << 1) + (e & 1);
-      const bool vis = (kp <= hi[r]) && (kp >= lo[r]);
-      const float v = vis ? s[j][e] * scale_log2 : -INFINITY;
-      s[j][e] = v;
-      mx[r] = fmaxf(mx[r], v);
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int kp = key0 + j * 8 + ((lane & 3) << 1) + (e & 1);
+        const bool vis = (kp <= hi[r]) && (kp >= lo[r]);
+        const float v = vis ? s[j][e] * scale_log2 : -INFINITY;
+        s[j][e] = v;
+        mx[r] = fmaxf(mx[r], v);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float v = s[j][e] * scale_log2;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
     }
   }
   float corr[2], m_use[2];
+  bool changed = false;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     const float m_new = fmaxf(m[r], mx[r]);
+    changed = changed || (m_new != m[r]);
     m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen nothing yet
     corr[r] = fast_exp2(m[r] - m_use[r]);
     m[r] = m_new;
@@ -183,15 +221,20 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[ND][4
   for (int r = 0; r < 2; ++r) {
     sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
     sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-    l[r] = l[r] * corr[r] + sum[r];
   }
+  if (__any_sync(0xffffffffu, changed)) {  // a maximum moved: old sums shrink (else the factor is exactly 1)
+    l[0] *= corr[0];
+    l[1] *= corr[1];
 #pragma unroll
-  for (int j = 0; j < ND; ++j) {
-    o[j][0] *= corr[0];
-    o[j][1] *= corr[0];
-    o[j][2] *= corr[1];
-    o[j][3] *= corr[1];
+    for (int j = 0; j < ND; ++j) {
+      o[j][0] *= corr[0];
+      o[j][1] *= corr[0];
+      o[j][2] *= corr[1];
+      o[j][3] *= corr[1];
+    }
   }
+  l[0] += sum[0];
+  l[1] += sum[1];
 }
 
 // Query fragments of 16 rows straight from global memory.  Row r of the CTA is
@@ -217,6 +260,8 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[D / 16][4], const Mm
 // ------------------------------------------------------------------ tile form
 template <int D>
 __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaParams p) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int TILE_BYTES = BN * D * 2;
   const uint32_t smem = smem_u32(smem_raw);  // stage s: K at s*2*TILE, V at (s*2+1)*TILE
@@ -235,6 +280,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
   const int kv_lo = p.window > 0 ? (max(0, p_first - p.window + 1) / BN) * BN : 0;
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
 
+  TileLoader<D> loader;
+  loader.init();
   uint32_t qf[D / 16][4];
   load_q_frags<D>(qf, p, q_begin + q0, n_tok, kvh, g, warp * 16, lane);
   int pos[2], lo[2];
@@ -253,13 +300,19 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
-  load_kv_tile<D>(p, bt, kvh, ctx, kv_lo, smem, smem + TILE_BYTES);
+  // the warp's rows all see every key of a tile that ends at or before the first row's position
+  // and starts at or after the last row's window
+  const int warp_tok0 = (warp * 16) / g, warp_tok1 = min(n_tok - 1, (warp * 16 + 15) / g);
+  const int all_hi = p_first + warp_tok0;  // keys <= this are seen by every valid row of the warp
+  const int all_lo = p.window > 0 ? p_first + warp_tok1 - p.window + 1 : 0;
+  const bool rows_full = (warp * 16 + 15) / g < n_tok;  // no row of the warp lies past the tile's tokens
+  loader.load(p, bt, kvh, ctx, kv_lo, smem, smem + TILE_BYTES);
   cp_async_commit();
   for (int t = 0; t < n_tiles; ++t) {
     const int st = t & 1;
     if (t + 1 < n_tiles) {
-      load_kv_tile<D>(p, bt, kvh, ctx, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
-                      smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
+      loader.load(p, bt, kvh, ctx, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
+                  smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -272,7 +325,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
 #pragma unroll
       for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
       qk_tile<D, BN / 8>(s, qf, ks, 0, lane);
-      softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, kv_lo + t * BN, p.scale_log2, lane);
+      const int key0 = kv_lo + t * BN;
+      const bool need_mask = !rows_full || key0 + BN - 1 > all_hi || key0 < all_lo;
+      softmax_step<BN / 8, D / 8>(s, o, m, l, lo, pos, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, BN / 16>(o, s, vs, 0, lane);
     }
     __syncthreads();  // the stage is free for the load after next
@@ -294,6 +349,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
 // ------------------------------------------------------------------ split form
 template <int D>
 __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaParams p) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int TILE_BYTES = BN * D * 2;
   const uint32_t smem = smem_u32(smem_raw);
@@ -318,6 +375,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
     return;
   }
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
+  TileLoader<D> loader;
+  loader.init();
 
   // rows are the heads of the group: row r is head r of this kv head; rows >= g are zero
   uint32_t qf[D / 16][4];
@@ -345,13 +404,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
-  load_kv_tile<D>(p, bt, kvh, kv_hi, kv_lo, smem, smem + TILE_BYTES);
+  loader.load(p, bt, kvh, kv_hi, kv_lo, smem, smem + TILE_BYTES);
   cp_async_commit();
   for (int t = 0; t < n_tiles; ++t) {
     const int st = t & 1;
     if (t + 1 < n_tiles) {
-      load_kv_tile<D>(p, bt, kvh, kv_hi, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
-                      smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
+      loader.load(p, bt, kvh, kv_hi, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
+                  smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -365,7 +424,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
       s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
       qk_tile<D, 2>(s, qf, ks, 2 * warp, lane);  // this warp's 16 keys of the tile
       const int key0 = kv_lo + t * BN + warp * 16;
-      softmax_step<2, D / 8>(s, o, m, l, lo, hi, key0, p.scale_log2, lane);
+      const bool need_mask = key0 < first_seen || key0 + 15 > kv_hi - 1;
+      softmax_step<2, D / 8>(s, o, m, l, lo, hi, key0, p.scale_log2, lane, need_mask);
       pv_tile<D, 1>(o, s, vs, warp, lane);
     }
     __syncthreads();
@@ -419,6 +479,8 @@ __global__ void __launch_bounds__(128)
 attn_mma_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                       bf16* __restrict__ out, const int* __restrict__ qsl, const int* __restrict__ ctx_lens,
                       int nh, int d, int out_stride, int split_size, int max_splits) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float wgt[1024];
   __shared__ float red[32];
   const int b = blockIdx.y, head = blockIdx.x;
@@ -466,12 +528,10 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
       if (e != cudaSuccess) return (int)e;
     }
-    kern<<<dim3(p.grid_splits, B, p.nkv), NWARPS * 32, need, st>>>(p);
-    int rc = KVF_LAUNCH_STATUS();
+    int rc = launch(kern, dim3(p.grid_splits, B, p.nkv), dim3(NWARPS * 32), need, st, p);
     if (rc) return rc;
-    attn_mma_merge_kernel<<<dim3(p.nh, B), 128, 0, st>>>(p.part_acc, p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D,
-                                                        p.out_stride, p.split_size, p.max_splits);
-    return KVF_LAUNCH_STATUS();
+    return launch(attn_mma_merge_kernel, dim3(p.nh, B), dim3(128), 0, st, (const float*)p.part_acc,
+                  (const float*)p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D, p.out_stride, p.split_size, p.max_splits);
   }
   auto kern = attn_mma_tile_kernel<D>;
   if (smem > 48 * 1024) {
@@ -479,8 +539,7 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
   }
   const int tq = BM / g;
-  kern<<<dim3((max_q_len + tq - 1) / tq, B, p.nkv), NWARPS * 32, smem, st>>>(p);
-  return KVF_LAUNCH_STATUS();
+  return launch(kern, dim3((max_q_len + tq - 1) / tq, B, p.nkv), dim3(NWARPS * 32), smem, st, p);
 }
 
 }  // namespace
@@ -505,6 +564,9 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
   p.part_acc = part_acc; p.part_ml = part_ml;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == block_size) p.bs_shift = sh;
   p.split_size = split_size; p.max_splits = max_splits;
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -18,6 +18,36 @@ namespace kvf {
 
 typedef __nv_bfloat16 bf16;
 
+// ---- programmatic dependent launch: a kernel may be scheduled while the kernel before it in
+// the stream is still running, do what does not depend on that kernel (set-up, prefetching
+// weights), and wait where it first touches that kernel's results.
+//   pdl_launch(): "the next kernel in the stream may be scheduled now".
+//   pdl_wait():   returns once every kernel before this one has finished and its writes are
+//                 visible.  Nothing that an earlier kernel wrote may be read, and nothing that
+//                 an earlier kernel reads may be written, before it.
+// Both do nothing when the launch carries no such dependency.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Whether launches of this library ask for programmatic dependent launch (one flag per
+// shared library; off unless the host turns it on).
+inline int g_pdl_enabled = 0;
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<bf16>(bf16 v) { return __bfloat162float(v); }

@@ -13,6 +13,8 @@ using namespace kvf;
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ resid, int H, int vocab, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
   const int n = blockIdx.x;
   const int id = ids[n];
   const bool ok = (id >= 0 && id < vocab);
@@ -34,6 +36,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    const float* __restrict__ partials, int nsplit, size_t split_stride,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[32];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -99,6 +103,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
                                        const float* __restrict__ partials, int nsplit, size_t split_stride,
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int H, float eps) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(16) float rowbuf[];  // H floats
   __shared__ float red[32];
   const int r = blockIdx.x;
@@ -141,6 +147,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
 // final norm reads gathered rows).
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restrict__ delta, size_t n) {
+  pdl_launch();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) resid[i] += to_float<T>(delta[i]);
 }
@@ -159,6 +167,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__
                                   const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int nh, int nkv, int d,
                                   int rot, int block_size, long long num_slots, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
   const int n = blockIdx.x;
   const int half = rot >> 1;
   const int stride = (nh + 2 * nkv) * d;
@@ -231,6 +241,8 @@ __global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __rest
                                         const int* __restrict__ slots, T* __restrict__ kcache,
                                         T* __restrict__ vcache, int nh, int nkv, int d, int block_size,
                                         long long num_slots, int heads_per_cta, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
   const int n = blockIdx.x;
   const int half = d >> 1;
   const int total_heads = nh + 2 * nkv;
@@ -287,6 +299,8 @@ __global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __rest
 // ([g0..b-1, u0..b-1, gb.., ...]), the order the decode product wants its weight rows in.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int block, size_t total) {
+  pdl_launch();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t n = idx / I;
@@ -298,10 +312,61 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
+// The same, 8 bfloat16 outputs (one 16-byte load of gates, one of ups, one 16-byte store) per
+// thread; needs I % 8 == 0, which the interleaved layout (blocks of 8) has by construction.
+__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int block,
+                                       size_t groups) {
+  pdl_launch();
+  pdl_wait();
+  const size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gidx >= groups) return;
+  const int per_row = I >> 3;
+  const size_t n = gidx / per_row;
+  const int i0 = (int)(gidx - n * per_row) << 3;
+  const int cg = block ? (i0 / block) * 2 * block + (i0 % block) : i0;
+  const int cu = block ? cg + block : I + i0;
+  const bf16* row = gu + n * 2 * (size_t)I;
+  const uint4 gv = *reinterpret_cast<const uint4*>(row + cg);
+  const uint4 uv = *reinterpret_cast<const uint4*>(row + cu);
+  float g[8], u[8];
+  bf16x8_to_float(gv, g);
+  bf16x8_to_float(uv, u);
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float a = g[2 * e] / (1.f + expf(-g[2 * e])) * u[2 * e];
+    const float b = g[2 * e + 1] / (1.f + expf(-g[2 * e + 1])) * u[2 * e + 1];
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    op[e] = *reinterpret_cast<uint32_t*>(&v);
+  }
+  *reinterpret_cast<uint4*>(out + n * (size_t)I + i0) = o;
+}
+
+template <typename T>
+int launch_silu_mul(const void* gu, void* out, long long N, int I, int block, cudaStream_t st) {
+  const size_t total = (size_t)N * I;
+  return launch(silu_mul_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (const T*)gu, (T*)out, I, block, total);
+}
+template <>
+int launch_silu_mul<bf16>(const void* gu, void* out, long long N, int I, int block, cudaStream_t st) {
+  const size_t total = (size_t)N * I;
+  const bool aligned = ((((uintptr_t)gu) | ((uintptr_t)out)) & 15) == 0;
+  if ((I & 7) == 0 && (block == 0 || block == 8) && aligned) {
+    const size_t groups = total >> 3;
+    return launch(silu_mul_bf16x8_kernel, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, st, (const bf16*)gu,
+                  (bf16*)out, I, block, groups);
+  }
+  return launch(silu_mul_kernel<bf16>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (const bf16*)gu,
+                (bf16*)out, I, block, total);
+}
+
 // ---------------------------------------------------------------- cast
 // float -> T rows (used when a float tensor feeds a T-typed product).
 template <typename T>
 __global__ void cast_from_float_kernel(const float* __restrict__ in, T* __restrict__ out, size_t n) {
+  pdl_launch();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = from_float<T>(in[i]);
 }
@@ -316,8 +381,7 @@ static inline int norm_threads(int H) {
   KVF_API int kvf_embed_##SUF(const void* table, const int* ids, float* resid, int N, int H, int vocab,  \
                               int* err, cudaStream_t st) {                                               \
     if (N <= 0) return 0;                                                                                \
-    embed_kernel<T><<<N, 256, 0, st>>>((const T*)table, ids, resid, H, vocab, err);                      \
-    return KVF_LAUNCH_STATUS();                                                                          \
+    return launch(embed_kernel<T>, dim3(N), dim3(256), 0, st, (const T*)table, ids, resid, H, vocab, err); \
   }                                                                                                      \
   KVF_API int kvf_add_rmsnorm_##SUF(float* resid, const void* delta, const float* partials, int nsplit, \
                                     long long split_stride, const float* weight, void* out,              \
@@ -332,20 +396,17 @@ static inline int norm_threads(int H) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
         if (e != cudaSuccess) return (int)e;                                                             \
       }                                                                                                  \
-      add_rmsnorm_vec_kernel<T><<<n_rows, t, smem, st>>>(resid, (const T*)delta, partials, nsplit,       \
-                                                         (size_t)split_stride, weight, (T*)out, rows, H, \
-                                                         eps);                                           \
-      return KVF_LAUNCH_STATUS();                                                                        \
+      return launch(add_rmsnorm_vec_kernel<T>, dim3(n_rows), dim3(t), smem, st, resid, (const T*)delta,   \
+                    partials, nsplit, (size_t)split_stride, weight, (T*)out, rows, H, eps);              \
     }                                                                                                    \
-    add_rmsnorm_kernel<T><<<n_rows, norm_threads(H), 0, st>>>(resid, (const T*)delta, partials, nsplit,  \
-                                                              (size_t)split_stride, weight, (T*)out,     \
-                                                              rows, H, eps);                             \
-    return KVF_LAUNCH_STATUS();                                                                          \
+    return launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(norm_threads(H)), 0, st, resid,              \
+                  (const T*)delta, partials, nsplit, (size_t)split_stride, weight, (T*)out, rows, H,     \
+                  eps);                                                                                  \
   }                                                                                                      \
   KVF_API int kvf_add_residual_##SUF(float* resid, const void* delta, long long n, cudaStream_t st) {    \
     if (n <= 0) return 0;                                                                                \
-    add_residual_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(resid, (const T*)delta, (size_t)n); \
-    return KVF_LAUNCH_STATUS();                                                                          \
+    return launch(add_residual_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, resid,    \
+                  (const T*)delta, (size_t)n);                                                           \
   }                                                                                                      \
   KVF_API int kvf_rope_cache_##SUF(void* qkv, const float* partials, int nsplit, long long split_stride, \
                                    void* q_out, const int* positions, const float* inv_freq,             \
@@ -362,31 +423,33 @@ static inline int norm_threads(int H) {
       const int heads = nh + 2 * nkv;                                                                    \
       dim3 grid(N, (heads + hpc - 1) / hpc);                                                             \
       if (grid.y <= 65535u) {                                                                            \
-        rope_cache_heads_kernel<T><<<grid, hpc * half, 0, st>>>(                                         \
-            (T*)qkv, partials, nsplit, (size_t)split_stride, (T*)q_out, positions, inv_freq, slots,      \
-            (T*)kcache, (T*)vcache, nh, nkv, d, block_size, num_slots, hpc, err);                        \
-        return KVF_LAUNCH_STATUS();                                                                      \
+        return launch(rope_cache_heads_kernel<T>, grid, dim3(hpc * half), 0, st, (T*)qkv, partials,      \
+                      nsplit, (size_t)split_stride, (T*)q_out, positions, inv_freq, slots, (T*)kcache,   \
+                      (T*)vcache, nh, nkv, d, block_size, num_slots, hpc, err);                          \
       }                                                                                                  \
     }                                                                                                    \
-    rope_cache_kernel<T><<<N, 256, 0, st>>>((T*)qkv, partials, nsplit, (size_t)split_stride, (T*)q_out,  \
-                                            positions, inv_freq, slots, (T*)kcache, (T*)vcache, nh, nkv, \
-                                            d, rot, block_size, num_slots, err);                         \
-    return KVF_LAUNCH_STATUS();                                                                          \
+    return launch(rope_cache_kernel<T>, dim3(N), dim3(256), 0, st, (T*)qkv, partials, nsplit,            \
+                  (size_t)split_stride, (T*)q_out, positions, inv_freq, slots, (T*)kcache, (T*)vcache,   \
+                  nh, nkv, d, rot, block_size, num_slots, err);                                          \
   }                                                                                                      \
   KVF_API int kvf_silu_mul_##SUF(const void* gu, void* out, long long N, int I, int block,               \
                                  cudaStream_t st) {                                                      \
     const size_t total = (size_t)N * I;                                                                  \
     if (total == 0) return 0;                                                                            \
     if (block < 0 || (block && I % block)) return (int)cudaErrorInvalidValue;                            \
-    silu_mul_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)out, I, block, \
-                                                                        total);                          \
-    return KVF_LAUNCH_STATUS();                                                                          \
+    return launch_silu_mul<T>(gu, out, N, I, block, st);                                                 \
   }                                                                                                      \
   KVF_API int kvf_cast_from_float_##SUF(const float* in, void* out, long long n, cudaStream_t st) {      \
     if (n <= 0) return 0;                                                                                \
-    cast_from_float_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, (T*)out, (size_t)n);      \
-    return KVF_LAUNCH_STATUS();                                                                          \
+    return launch(cast_from_float_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, in,    \
+                  (T*)out, (size_t)n);                                                                   \
   }
+
+// Turn programmatic dependent launch on or off for every launch of this library.
+KVF_API int kvf_set_pdl(int enabled) {
+  kvf::g_pdl_enabled = enabled ? 1 : 0;
+  return 0;
+}
 
 KVF_ELEMENTWISE_API(f32, float)
 KVF_ELEMENTWISE_API(bf16, bf16)

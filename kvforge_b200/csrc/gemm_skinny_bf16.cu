@@ -71,9 +71,10 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(const SkinnyParams
   const int n_iters = (k_end - k_begin + BK - 1) / BK;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  auto load_stage = [&](int stage, int it) {
+  // W does not depend on the kernel before this one; x does.
+  auto load_w = [&](int stage, int it) {
     const int k0 = k_begin + it * BK;
-    const uint32_t ws = smem + stage * STAGE_BYTES, xs = ws + W_BYTES;
+    const uint32_t ws = smem + stage * STAGE_BYTES;
 #pragma unroll
     for (int i = 0; i < (BN * 8) / THREADS; ++i) {
       const int idx = threadIdx.x + i * THREADS;
@@ -82,6 +83,10 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(const SkinnyParams
       const bool valid = (n0 + row < p.N) && (k < k_end);
       cpa16(ws + toff(row, c), p.w + (valid ? (size_t)(n0 + row) * p.ldw + k : 0), valid);
     }
+  };
+  auto load_x = [&](int stage, int it) {
+    const int k0 = k_begin + it * BK;
+    const uint32_t xs = smem + stage * STAGE_BYTES + W_BYTES;
     for (int idx = threadIdx.x; idx < X_ROWS * 8; idx += THREADS) {
       const int row = idx >> 3, c = idx & 7;
       const int k = k0 + c * 8;
@@ -94,15 +99,29 @@ __global__ void __launch_bounds__(THREADS) gemm_skinny_kernel(const SkinnyParams
 #pragma unroll
   for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
+  // Weight tiles of the first stages start streaming before the kernel ahead of this one in
+  // the stream has finished; the activations are fetched once it has.  Group order is
+  // W_0..W_{S-2}, x_0..x_{S-2}, then one group per later stage: "all but the newest S-2
+  // groups are done" then means that both halves of the current stage have landed.
+  pdl_launch();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < n_iters) load_stage(s, s);
+    if (s < n_iters) load_w(s, s);
+    cpa_commit();
+  }
+  pdl_wait();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_iters) load_x(s, s);
     cpa_commit();
   }
   for (int it = 0; it < n_iters; ++it) {
     cpa_wait<STAGES - 2>();
     __syncthreads();  // stage `it` has landed for every thread; stage `it-1` has been consumed
-    if (it + STAGES - 1 < n_iters) load_stage((it + STAGES - 1) % STAGES, it + STAGES - 1);
+    if (it + STAGES - 1 < n_iters) {
+      load_w((it + STAGES - 1) % STAGES, it + STAGES - 1);
+      load_x((it + STAGES - 1) % STAGES, it + STAGES - 1);
+    }
     cpa_commit();
     const uint32_t ws = smem + (it % STAGES) * STAGE_BYTES, xs = ws + W_BYTES;
 #pragma unroll
@@ -162,8 +181,7 @@ int launch_skinny(const SkinnyParams& p, int ksplit, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((p.N + BN - 1) / BN, ksplit);
-  kern<<<grid, THREADS, smem, st>>>(p);
-  return KVF_LAUNCH_STATUS();
+  return launch(kern, grid, dim3(THREADS), smem, st, p);
 }
 
 }  // namespace

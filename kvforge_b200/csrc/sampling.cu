@@ -120,6 +120,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
               const unsigned long long* __restrict__ rand_keys, int* __restrict__ out_tokens,
               float* __restrict__ probs_out) {
   __shared__ Shared sh;
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   float* prow = probs_out ? probs_out + (size_t)r * V : nullptr;
@@ -280,6 +282,6 @@ KVF_API int kvf_sample_f32(const float* logits, long long ld, int R, int V, cons
                            int* out_tokens, float* probs_out, cudaStream_t st) {
   if (R <= 0) return 0;
   if (V <= 0) return (int)cudaErrorInvalidValue;
-  sample_kernel<<<R, THREADS, 0, st>>>(logits, ld, V, temps, top_ks, top_ps, rand_keys, out_tokens, probs_out);
-  return KVF_LAUNCH_STATUS();
+  return launch(sample_kernel, dim3(R), dim3(THREADS), 0, st, logits, ld, V, temps, top_ks, top_ps, rand_keys,
+                out_tokens, probs_out);
 }

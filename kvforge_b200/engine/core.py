@@ -9,6 +9,7 @@ The order of construction follows umarhassan-cloud/kvforge's ``InferenceEngine._
 
 from __future__ import annotations
 
+import os
 from pathlib import Path
 
 import torch
@@ -54,6 +55,7 @@ class EngineCore:
         max_model_len: int = 2048,
         cuda_graphs: bool = False,
         lazy_buffers: bool = False,
+        pdl: bool | None = None,
     ) -> None:
         if not torch.cuda.is_available():
             raise RuntimeError("kvforge_b200 needs a CUDA device: there is no CPU path")
@@ -81,8 +83,9 @@ class EngineCore:
         self.state_slots = StateSlotPool(max_num_seqs)
         self.pool = KVPool(self.model, self.num_blocks, cache.block_size, max_num_seqs, self.dtype, self.device)
         self.runner = ModelRunner(
-            self.model, self.rt, self.block_manager, self.state_slots, self.max_model_len, cuda_graphs=cuda_graphs
-        )
+            self.model, self.rt, self.block_manager, self.state_slots, self.max_model_len, cuda_graphs=cuda_graphs,
+            pdl=(self.dtype == torch.bfloat16 and os.environ.get("KVFORGE_PDL", "1") != "0") if pdl is None else pdl,
+        )  # fmt: skip
         self.runner.attach_pool(self.pool)
 
     @classmethod

@@ -99,6 +99,7 @@ class ModelRunner:
         max_model_len: int,
         cuda_graphs: bool = False,
         graph_buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64, 128, 256),
+        pdl: bool = False,
     ) -> None:
         self.model = model
         self.rt = rt
@@ -109,6 +110,7 @@ class ModelRunner:
         self.max_width = max(1, -(-self.max_model_len // self.block_size))
         self.n_groups = block_manager.num_groups
         self.cuda_graphs = bool(cuda_graphs)
+        self.pdl = bool(pdl)  # programmatic dependent launch between the kernels of a step
         self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.graph_kernels: dict[int, int] = {}  # kernels of this library inside each captured graph
@@ -232,6 +234,7 @@ class ModelRunner:
         next step overwrites."""
         if not items:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        ops.set_pdl(self.pdl)
         if self.state_slots is not None:
             fresh = self.state_slots.take_fresh()
             if fresh and self._pool is not None:

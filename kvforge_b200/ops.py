@@ -28,6 +28,7 @@ _SIGNATURES = {
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
+    "kvf_set_pdl": "i",
     "kvf_sample_f32": "pliippppppp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
@@ -80,6 +81,20 @@ def _stream() -> int:
 
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
+
+
+_pdl_state = None
+
+
+def set_pdl(enabled: bool) -> None:
+    """Ask for programmatic dependent launch on every later launch of this library: a kernel
+    may then be scheduled, and prefetch weights, while the kernel ahead of it in the stream is
+    still running; it waits before it touches that kernel's results."""
+    global _pdl_state
+    enabled = bool(enabled)
+    if _pdl_state is not enabled:
+        _fn("kvf_set_pdl")(1 if enabled else 0)
+        _pdl_state = enabled
 
 
 # Kernels of this library launched so far (library matrix products are not counted).
@@ -299,7 +314,7 @@ def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
     would leave SMs idle, larger ones when the context is so long that there would be more
     than ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of it, whatever the batch."""
     pairs = num_seqs * nkv
-    split = 256 if pairs >= 64 else 128 if pairs >= 16 else 64
+    split = 512 if pairs >= 256 else 256 if pairs >= 32 else 128
     while -(-max_context // split) > MAX_ATTN_SPLITS:
         split *= 2
     return split
@@ -430,14 +445,15 @@ def gemm_nt_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     )
 
 
-SKINNY_MAX_M = 64
+SKINNY_MAX_M = 64  # what the kernel takes
+SKINNY_USE_M = 16  # up to here it beats the library product (measured on B200); above, the library is used
 SKINNY_MAX_SPLIT = 16
 
 
 def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the decode product (``csrc/gemm_skinny_bf16.cu``) takes ``x @ w^T``."""
     return (
-        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_M
+        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_USE_M
         and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
     )  # fmt: skip
 
@@ -457,9 +473,10 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | Partials, 
     of K each), or with ``mode="silu"`` a bfloat16 ``[M, N/2]`` tensor that receives
     ``silu(gate) * up`` for ``w`` in the interleaved gate/up layout.
     """
-    if not skinny_ok(x, w):
-        raise ValueError("gemm_skinny: needs bfloat16, M <= 64, K % 8 == 0, unit inner strides")
     m, k = x.shape
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_M and k % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0):  # fmt: skip
+        raise ValueError("gemm_skinny: needs bfloat16, M <= 64, K % 8 == 0, unit inner strides")
     n = w.shape[0]
     if w.shape[1] != k:
         raise ValueError("gemm_skinny: inner sizes differ")
