@@ -141,6 +141,8 @@ class BlockManager:
         when writing starts at ``write_start``."""
         table = pool.tables.get(seq_id, []) if seq_id is not None else []
         want = self.blocks_needed(total_tokens)
+        if pool.spec.kind != "window":
+            return max(0, want - len(table)), 0  # a full group never gives pages back: no holes in its table
         first = self._first_live_block(pool, write_start)
         take = sum(1 for i in range(first, want) if i >= len(table) or table[i] < 0)
         back = sum(1 for i in range(min(first, len(table))) if table[i] >= 0)
@@ -205,6 +207,10 @@ class BlockManager:
         want = self.blocks_needed(total_tokens)
         for pool in self._pools:
             table = pool.tables[seq_id]
+            if pool.spec.kind != "window":
+                while len(table) < want:
+                    table.append(pool.pop())
+                continue
             first = self._first_live_block(pool, write_start)
             for i in range(min(first, len(table))):
                 if table[i] >= 0:
@@ -257,6 +263,12 @@ class BlockManager:
             for b in range(pool.num_blocks):
                 if pool.held[b] != (b in seen):
                     raise AssertionError(f"group {gi}: held flag of block {b} is wrong")
+
+    @property
+    def utilization(self) -> float:
+        """Share of the first group's pages that are in use."""
+        pool = self._pools[0]
+        return (pool.num_blocks - len(pool.free)) / self.num_blocks
 
     def stats(self) -> BlockManagerStats:
         """Figures of the first group (block_manager.py:288-314)."""

@@ -138,9 +138,7 @@ class InferenceEngine:
             return []
         new_tokens = self._run(sched.scheduled)
         outputs = self._postprocess(sched.scheduled, new_tokens)
-        self.metrics.record_step(
-            len(sched.scheduled), sched.num_batched_tokens, time.perf_counter() - t0, self.block_manager.stats()
-        )
+        self.metrics.record_step(len(sched.scheduled), sched.num_batched_tokens, time.perf_counter() - t0, self.block_manager.utilization)
         return outputs
 
     def _run(self, group: list[ScheduledRequest]) -> dict[str, int]:

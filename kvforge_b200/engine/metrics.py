@@ -34,12 +34,12 @@ class MetricsCollector:
     def reset(self) -> None:
         self.__init__()  # type: ignore[misc]
 
-    def record_step(self, batch_size: int, num_tokens: int, step_time: float, kv) -> None:
+    def record_step(self, batch_size: int, num_tokens: int, step_time: float, kv_utilization: float) -> None:
         self.num_steps += 1
         self.batch_sizes.append(batch_size)
         self.batched_tokens.append(num_tokens)
         self.step_times.append(step_time)
-        self.kv_utilization.append(kv.utilization)
+        self.kv_utilization.append(kv_utilization)
 
     def record_finished(self, req) -> None:
         if req.finish_reason is not None and req.finish_reason.value == "abort":

@@ -227,7 +227,6 @@ class ModelRunner:
         )
 
     # ------------------------------------------------------------------ running
-    @torch.inference_mode()
     def step(self, items: Sequence[BatchItem]) -> torch.Tensor:
         """Run one batch.  Returns float logits ``[R, vocab]`` on the device, rows ordered by
         item, then by the item's wanted places.  The tensor is a view of a buffer that the
