@@ -56,6 +56,8 @@ class Runtime:
                 what.append("a token id outside the vocabulary")
             if flag & 2:
                 what.append("a cache slot outside the pool")
+            if flag & 4:
+                what.append("a bounded wait inside a kernel ran out")
             raise RuntimeError("device-side check failed: " + ", ".join(what or [f"flag {flag}"]))
 
 

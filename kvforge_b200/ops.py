@@ -29,6 +29,7 @@ _SIGNATURES = {
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
+    "kvf_gemm_tcgen05_bf16": "pppiiiiiiipp",
     "kvf_sample_f32": "pliippppppp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
@@ -506,6 +507,45 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | Partials, 
         ldo, optr = out.stride(0), _ptr(out)
     name = "kvf_gemm_skinny_bf16"
     _check(_fn(name)(_ptr(x), _ptr(w), optr, m, n, k, x.stride(0), w.stride(0), ldo, code, ksplit, stride, _stream()), name)
+
+
+TCGEN05_MIN_TILES = 120  # below this many 128 x 256 output tiles the persistent grid leaves SMs idle
+
+
+def tcgen05_ok(x: torch.Tensor, w: torch.Tensor, min_tiles: int = TCGEN05_MIN_TILES) -> bool:
+    """Whether the tensor-memory product (``csrc/gemm_tcgen05_bf16.cu``) takes ``x @ w^T`` and
+    has enough output tiles to fill the device."""
+    tiles = -(-x.shape[0] // 128) * -(-w.shape[0] // 256)
+    return tiles >= min_tiles and (
+        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(1) == 1
+        and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+        and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+    )  # fmt: skip
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str = "plain", err: torch.Tensor | None = None) -> None:
+    """``x [M, K] @ w [N, K]^T`` in bfloat16 on the tcgen05 tensor cores (TMA loads, float
+    accumulation in tensor memory).  ``out``: bfloat16 ``[M, N]``, or with ``mode="silu"``
+    bfloat16 ``[M, N/2] = silu(gate) * up`` for ``w`` in the interleaved gate/up layout."""
+    if not tcgen05_ok(x, w, min_tiles=0):
+        raise ValueError("gemm_tcgen05: needs bfloat16, K % 8 == 0, unit inner strides, 16-byte aligned rows")
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError("gemm_tcgen05: inner sizes differ")
+    _need(out, torch.bfloat16, "out", contiguous=False)
+    if out.stride(1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16:
+        raise ValueError("gemm_tcgen05: out needs unit inner stride and 16-byte aligned rows")
+    if mode == "silu":
+        if tuple(out.shape) != (m, n // 2) or n % 16:
+            raise ValueError("gemm_tcgen05: silu output must be [M, N/2] with N % 16 == 0")
+        code = 3
+    else:
+        if tuple(out.shape) != (m, n):
+            raise ValueError("gemm_tcgen05: out shape")
+        code = 0
+    name = "kvf_gemm_tcgen05_bf16"
+    _check(_fn(name)(_ptr(x), _ptr(w), _ptr(out), m, n, k, x.stride(0), w.stride(0), out.stride(0), code, _ptr(err), _stream()), name)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -49,7 +49,10 @@ class GatedMLP(FeedForward):
         n = x.shape[0]
         act = rt.buf("mlp.act", n, self.inter)
         if self.interleaved and ops.skinny_ok(x, self.w_gate_up):
-            ops.gemm_skinny(x, self.w_gate_up, act, mode="silu")
+            ops.gemm_skinny(x, self.w_gate_up, act, mode="silu")  # a few tokens: stream the weights once
+        elif self.interleaved and ops.tcgen05_ok(x, self.w_gate_up):
+            # many tokens: tcgen05 tensor cores, the gate applied as the accumulator leaves tensor memory
+            ops.gemm_tcgen05(x, self.w_gate_up, act, mode="silu", err=rt.err)
         else:
             gu = rt.buf("mlp.gate_up", n, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gu)

@@ -175,6 +175,35 @@ def test_gemm_skinny_with_the_gate(ops, m, i, h):
     assert float((out2.float().cpu() - ref).abs().max()) < 2e-2 * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 128), (200, 384, 2048), (65, 100, 80), (2048, 512, 256), (300, 203, 1000), (1, 16, 8)])
+def test_gemm_tcgen05(ops, m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.1).bfloat16()
+    ref = x.double() @ w.double().t()
+    n_pad = -(-n // 8) * 8  # output rows must be 16-byte aligned
+    out = torch.full((m, n_pad), float("nan"), device="cuda", dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tcgen05(dev(x), dev(w), out[:, :n], err=err)
+    assert int(err.item()) == 0, "a wait inside the kernel ran out"
+    got = out[:, :n].double().cpu()
+    assert not torch.isnan(got).any()
+    assert float((got - ref).abs().max()) < 1e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("m,i,h", [(130, 96, 64), (256, 512, 256), (70, 200, 80)])
+def test_gemm_tcgen05_with_the_gate(ops, m, i, h):
+    x = torch.randn(m, h).bfloat16()
+    wg, wu = (torch.randn(i, h) * 0.2).bfloat16(), (torch.randn(i, h) * 0.2).bfloat16()
+    w = ops.interleave_gate_up(dev(wg), dev(wu))
+    out = torch.full((m, i), float("nan"), device="cuda", dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tcgen05(dev(x), w, out, mode="silu", err=err)
+    assert int(err.item()) == 0
+    ref = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert float((out.float().cpu() - ref).abs().max()) < 1e-2 * float(ref.abs().max())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_norm_and_rope_sum_the_slices_of_a_split_product(ops, dtype):
     n, h, splits = 6, 100, 3
