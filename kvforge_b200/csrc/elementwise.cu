@@ -293,6 +293,106 @@ __global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __rest
   }
 }
 
+// The same again for many tokens: one CTA per token, each thread moves 8 consecutive dims of a
+// head (16-byte loads and stores for bfloat16) together with the 8 dims half a head further on
+// that they pair with.  Needs rot == d and d % 16 == 0.
+template <typename T> struct Ld8;
+template <> struct Ld8<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float* f) { bf16x8_to_float(*reinterpret_cast<const uint4*>(p), f); }
+  static __device__ __forceinline__ void store(bf16* p, const float* f) {
+    uint4 u;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Ld8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+template <typename T>
+__global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restrict__ partials, int nsplit,
+                                      size_t split_stride, T* __restrict__ q_out,
+                                      const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                      const int* __restrict__ slots, T* __restrict__ kcache,
+                                      T* __restrict__ vcache, int nh, int nkv, int d, int block_size,
+                                      long long num_slots, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int half = d >> 1, cph = half >> 3;  // chunks of 8 pairs per head
+  const int stride = (nh + 2 * nkv) * d;
+  T* row = qkv ? qkv + (size_t)n * stride : nullptr;
+  const float* prow = partials ? partials + (size_t)n * stride : nullptr;
+  auto load8 = [&](int idx, float* f) {
+    if (prow) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+      for (int s = 0; s < nsplit; ++s) {  // slice order: reproducible
+        float g[8];
+        Ld8<float>::load(prow + (size_t)s * split_stride + idx, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += g[e];
+      }
+    } else {
+      Ld8<T>::load(row + idx, f);
+    }
+  };
+  long long slot = slots ? (long long)slots[n] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0 && err) atomicOr(err, 2);
+    slot = -1;
+  }
+  const size_t cache_row = slot >= 0 ? ((size_t)(slot / block_size) * nkv) * block_size + (slot % block_size) : 0;
+  const float pos = (float)positions[n];
+  T* qdst = q_out ? q_out + (size_t)n * nh * d : row;
+  // rotated heads (q then k): one item = 8 pairs of one head
+  const int rot_items = (nh + nkv) * cph;
+  for (int w = threadIdx.x; w < rot_items; w += blockDim.x) {
+    const int head = w / cph, j0 = (w - head * cph) << 3;
+    float x1[8], x2[8], y1[8], y2[8];
+    load8(head * d + j0, x1);
+    load8(head * d + half + j0, x2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float sn, cs;
+      sincosf(pos * inv_freq[j0 + e], &sn, &cs);
+      y1[e] = x1[e] * cs - x2[e] * sn;
+      y2[e] = x2[e] * cs + x1[e] * sn;
+    }
+    T* dst = nullptr;
+    if (head < nh) {
+      dst = qdst + (size_t)head * d;
+    } else if (slot >= 0) {
+      dst = kcache + (cache_row + (size_t)(head - nh) * block_size) * d;
+    }
+    if (dst) {
+      Ld8<T>::store(dst + j0, y1);
+      Ld8<T>::store(dst + half + j0, y2);
+    }
+  }
+  if (slot < 0) return;
+  // values: plain copies, 8 dims per item
+  const int v_items = nkv * (d >> 3);
+  for (int w = threadIdx.x; w < v_items; w += blockDim.x) {
+    const int kvh = w / (d >> 3), j0 = (w - kvh * (d >> 3)) << 3;
+    float f[8];
+    load8((nh + nkv + kvh) * d + j0, f);
+    Ld8<T>::store(vcache + (cache_row + (size_t)kvh * block_size) * d + j0, f);
+  }
+}
+
 // ---------------------------------------------------------------- SiLU gate
 // out[n, i] = T( silu(float(g_i)) * float(u_i) ),  silu(t) = t / (1 + exp(-t)).
 // Columns of gu [N, 2I]: gates then ups (block == 0), or alternating in blocks of `block`
@@ -416,6 +516,11 @@ static inline int norm_threads(int H) {
     if (N <= 0) return 0;                                                                                \
     if (rot < 0 || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;                              \
     if (!qkv && !(partials && q_out)) return (int)cudaErrorInvalidValue;                                 \
+    if (rot == d && (d & 15) == 0 && N > 16 && (split_stride & 3) == 0) {                                \
+      return launch(rope_cache_vec_kernel<T>, dim3(N), dim3(256), 0, st, (T*)qkv, partials, nsplit,      \
+                    (size_t)split_stride, (T*)q_out, positions, inv_freq, slots, (T*)kcache, (T*)vcache, \
+                    nh, nkv, d, block_size, num_slots, err);                                             \
+    }                                                                                                    \
     if (rot == d && d >= 2 && d <= 512) {                                                                \
       const int half = d / 2;                                                                            \
       int hpc = 128 / half;                                                                              \

@@ -99,11 +99,14 @@ def test_gemm_f32_rows_do_not_depend_on_the_batch(ops):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("many", [False, True])  # a few tokens and many tokens take different kernels
 @pytest.mark.parametrize("nh,nkv,d,rot,bs", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 24, 4), (5, 5, 128, 128, 32)])
-def test_rope_and_cache_write(ops, dtype, nh, nkv, d, rot, bs):
-    n, nb = 11, 9
+def test_rope_and_cache_write(ops, dtype, nh, nkv, d, rot, bs, many):
+    base = [0, 1, 2, 63, 64, 65, 1000, 4095, 4096, 7, 8]
+    positions = torch.tensor(base + ([p + 3 for p in base] + [p + 17 for p in base] + [p + 90 for p in base] if many else []), dtype=torch.int32)
+    n = positions.numel()
+    nb = -(-n // bs) + 8
     qkv = torch.randn(n, (nh + 2 * nkv) * d).to(dtype)
-    positions = torch.tensor([0, 1, 2, 63, 64, 65, 1000, 4095, 4096, 7, 8], dtype=torch.int32)
     inv = plain_inv_freq(rot, 500000.0)
     slots = torch.tensor(random.Random(1).sample(range(nb * bs), n), dtype=torch.int32)
     kc = torch.zeros(nb, nkv, bs, d, device="cuda", dtype=dtype)
