@@ -236,7 +236,7 @@ def time_e2e(cfg, batch: int, steps: int, warmup: int):
     wall = time.perf_counter() - t0
     seconds = max(start.elapsed_time(end) / 1e3, wall)
     assert produced == batch * steps, (produced, batch * steps)
-    return produced / seconds, (engine.runner.h2d_bytes - h0) / steps, 4 * batch
+    return produced / seconds, (engine.runner.h2d_bytes - h0) / steps, 4 * batch + 4  # token ids and the error flag
 
 
 def run_own(args) -> dict:

@@ -75,6 +75,9 @@ class EngineConfig:
     seed: int = 0
     # Replay single-token batches as CUDA graphs (bfloat16 serving path).
     cuda_graphs: bool = True
+    # Read a step's tokens while the next step runs (a decoded token feeds the next step on the
+    # device; stop tokens are seen one step late).  False: read them before the next step.
+    async_output: bool = True
 
     def __post_init__(self) -> None:
         self.dtype = parse_dtype(self.dtype)

@@ -7,16 +7,20 @@
 using namespace kvf;
 
 // ---------------------------------------------------------------- embedding
-// resid[n, :] = float(table[ids[n], :]).  An id outside the table writes zeros and raises
-// the error flag (the host validates ids before; this only keeps a bad id from reading
-// outside the table).
+// resid[n, :] = float(table[id, :]) with id = ids[n], or, where feedback_rows[n] >= 0, the
+// token that the sampling kernel of the step before left at feedback[feedback_rows[n]] (so a
+// decoded token goes round on the device and the host need not have read it yet).  An id
+// outside the table writes zeros and raises the error flag (the host validates ids before;
+// this only keeps a bad id from reading outside the table).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             const int* __restrict__ feedback_rows, const int* __restrict__ feedback,
                              float* __restrict__ resid, int H, int vocab, int* __restrict__ err) {
   pdl_launch();
   pdl_wait();
   const int n = blockIdx.x;
-  const int id = ids[n];
+  int id = ids[n];
+  if (feedback_rows && feedback_rows[n] >= 0) id = feedback[feedback_rows[n]];
   const bool ok = (id >= 0 && id < vocab);
   if (!ok && threadIdx.x == 0 && err) atomicOr(err, 1);
   const T* row = table + (size_t)(ok ? id : 0) * H;
@@ -478,10 +482,12 @@ static inline int norm_threads(int H) {
 }
 
 #define KVF_ELEMENTWISE_API(SUF, T)                                                                      \
-  KVF_API int kvf_embed_##SUF(const void* table, const int* ids, float* resid, int N, int H, int vocab,  \
-                              int* err, cudaStream_t st) {                                               \
+  KVF_API int kvf_embed_##SUF(const void* table, const int* ids, const int* feedback_rows,               \
+                              const int* feedback, float* resid, int N, int H, int vocab, int* err,      \
+                              cudaStream_t st) {                                                         \
     if (N <= 0) return 0;                                                                                \
-    return launch(embed_kernel<T>, dim3(N), dim3(256), 0, st, (const T*)table, ids, resid, H, vocab, err); \
+    return launch(embed_kernel<T>, dim3(N), dim3(256), 0, st, (const T*)table, ids, feedback_rows,       \
+                  feedback, resid, H, vocab, err);                                                       \
   }                                                                                                      \
   KVF_API int kvf_add_rmsnorm_##SUF(float* resid, const void* delta, const float* partials, int nsplit, \
                                     long long split_stride, const float* weight, void* out,              \

@@ -14,7 +14,7 @@ from __future__ import annotations
 import itertools
 import time
 from collections.abc import Sequence
-from dataclasses import asdict
+from dataclasses import asdict, dataclass, field
 from pathlib import Path
 from typing import Any
 
@@ -29,6 +29,21 @@ from .request import FinishReason, Request, RequestOutput
 from .scheduler import ScheduledRequest, Scheduler
 from .step import BatchItem
 from .tokenizer import Tokenizer
+
+
+PLACEHOLDER = -1  # stands in an output list for a token that is still on the device
+
+
+@dataclass
+class _Pending:
+    """A launched step whose tokens the host has not read yet."""
+
+    sampled: list  # requests that get a token from this step, in row order
+    indices: list[int]  # where in each request's output list the token goes
+    host: torch.Tensor  # pinned: [rows] tokens, then the device error flag
+    event: torch.cuda.Event
+    rows: dict  # request id -> row
+    skip: set = field(default_factory=set)  # requests that ended meanwhile
 
 
 class InferenceEngine:
@@ -68,6 +83,11 @@ class InferenceEngine:
         self.kv_cache = self.core.pool
         self.runner = self.core.runner
         self.sampler = Sampler(self.core.device, sc.max_num_seqs)
+        self.runner.token_feedback = self.sampler._tokens  # a sampled token can feed the next step on the device
+        self._host_tokens = [torch.zeros(sc.max_num_seqs + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._flip = 0
+        self._pending: _Pending | None = None
         self.scheduler = Scheduler(sc, self.block_manager, self.core.state_slots)
         self.metrics = MetricsCollector()
         self._ids = itertools.count()
@@ -109,10 +129,12 @@ class InferenceEngine:
         req = self.scheduler.abort_request(request_id)
         if req is not None:
             self.metrics.record_finished(req)
+            if self._pending is not None:
+                self._pending.skip.add(request_id)
+            if req.output_token_ids and req.output_token_ids[-1] == PLACEHOLDER:
+                req.output_token_ids.pop()
+                req.token_times.pop()
         return req is not None
-
-    def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished()
 
     def generate(
         self,
@@ -131,17 +153,49 @@ class InferenceEngine:
         return [done[i] for i in ids if i in done]
 
     # ------------------------------------------------------------------ step
+    def has_unfinished_requests(self) -> bool:
+        if self.scheduler.has_unfinished():
+            return True
+        # a launched step whose tokens have not been reported yet
+        return self._pending is not None and any(r.request_id not in self._pending.skip for r in self._pending.sampled)
+
     def step(self) -> list[RequestOutput]:
+        """One scheduler decision and one forward.  With ``async_output`` (the default) the
+        tokens of a step are read from the device while the *next* step runs: a decoded token
+        goes round on the device (the sampling kernel's output feeds the next embedding
+        lookup), the host appends a placeholder, and patches it, checks stop tokens and
+        reports the outputs one call later.  Stops by count (``max_tokens``, the model's
+        length) are decided at once; a stop token is seen one step late, and the one token
+        computed in between is dropped."""
         t0 = time.perf_counter()
         sched = self.scheduler.schedule()
         if sched.is_empty:
-            return []
-        new_tokens = self._run(sched.scheduled)
-        outputs = self._postprocess(sched.scheduled, new_tokens)
+            return self._resolve(self._take_pending())
+        outputs: list[RequestOutput] = []
+        if self._pending is not None and any(self._needs_host_tokens(s) for s in sched.scheduled):
+            # a portion of known tokens (a re-run after preemption) includes a token not read yet
+            outputs += self._resolve(self._take_pending())
+        previous = self._take_pending()
+        self._pending = self._launch(sched.scheduled, previous)
+        outputs += self._resolve(previous)
+        if not self.config.async_output:
+            outputs += self._resolve(self._take_pending())
         self.metrics.record_step(len(sched.scheduled), sched.num_batched_tokens, time.perf_counter() - t0, self.block_manager.utilization)
         return outputs
 
-    def _run(self, group: list[ScheduledRequest]) -> dict[str, int]:
+    def _take_pending(self):
+        pending, self._pending = self._pending, None
+        return pending
+
+    @staticmethod
+    def _needs_host_tokens(s: ScheduledRequest) -> bool:
+        r = s.request
+        start = r.num_computed_tokens
+        if s.num_new_tokens == 1 and start == r.num_tokens - 1:
+            return False  # a single newest token can come from the device
+        return PLACEHOLDER in r.output_token_ids[max(0, start - r.num_prompt_tokens) :]
+
+    def _launch(self, group: list[ScheduledRequest], previous) -> "_Pending | None":
         """engine.py:196-228: a portion that reaches the end of the known tokens asks for the
         logits of its last place and gets a token sampled; others ask for none."""
         items: list[BatchItem] = []
@@ -150,46 +204,85 @@ class InferenceEngine:
             r = s.request
             start = r.num_computed_tokens
             completes = start + s.num_new_tokens == r.num_tokens
-            items.append(BatchItem(r.request_id, r.all_token_ids[start : start + s.num_new_tokens], start, "last" if completes else "none"))
+            want = "last" if completes else "none"
+            row = None
+            if previous is not None and s.num_new_tokens == 1 and r.output_token_ids and r.output_token_ids[-1] == PLACEHOLDER:
+                row = previous.rows.get(r.request_id)
+            if row is not None:
+                items.append(BatchItem(r.request_id, [0], start, want, feedback_row=row))
+            else:
+                items.append(BatchItem(r.request_id, r.all_token_ids[start : start + s.num_new_tokens], start, want))
             if completes:
                 sampled.append(r)
         logits = self.runner.step(items)
         for s in group:
             s.request.num_computed_tokens += s.num_new_tokens
-        out: dict[str, int] = {}
-        if sampled:
-            keys = [r.stream_base + r.num_output_tokens for r in sampled]
-            tokens = self.sampler.sample(logits, [r.sampling_params for r in sampled], keys)
-            host = tokens.tolist()  # the step's one device-to-host read
-            self.core.rt.check_error_flag()
-            for r, t in zip(sampled, host):
-                out[r.request_id] = t
-        return out
-
-    def _postprocess(self, scheduled: list[ScheduledRequest], new_tokens: dict[str, int]) -> list[RequestOutput]:
-        """engine.py:243-272."""
+        if not sampled:
+            return None
+        keys = [r.stream_base + r.num_output_tokens for r in sampled]
+        tokens = self.sampler.sample(logits, [r.sampling_params for r in sampled], keys)
+        # tokens and the device's error flag go to pinned host memory behind the kernels
+        host = self._host_tokens[self._flip]
+        self._flip ^= 1
+        n = len(sampled)
+        host[:n].copy_(tokens, non_blocking=True)
+        host[n : n + 1].copy_(self.core.rt.err, non_blocking=True)
+        event = self._events[self._flip]
+        event.record()
         now = time.perf_counter()
         max_len = self.config.scheduler.max_model_len
+        pending = _Pending(sampled, [r.num_output_tokens for r in sampled], host, event, {r.request_id: i for i, r in enumerate(sampled)})
+        for r in sampled:
+            r.append_token(PLACEHOLDER, now)
+            # stops by count need no token value: decide them now, so the request is not run again
+            if r.num_output_tokens >= r.sampling_params.max_tokens or r.num_tokens >= max_len:
+                self.scheduler.finish_request(r, FinishReason.LENGTH)
+        return pending
+
+    def _resolve(self, pending) -> list[RequestOutput]:
+        """Read a launched step's tokens, put them in place of the placeholders, check stop
+        tokens, report (engine.py:243-272)."""
+        if pending is None:
+            return []
+        pending.event.synchronize()
+        n = len(pending.sampled)
+        values = pending.host[: n + 1].tolist()  # the step's one device-to-host read
+        if values[n]:
+            self.core.rt.check_error_flag()
         outputs: list[RequestOutput] = []
-        for s in scheduled:
-            r = s.request
-            emitted: list[int] = []
-            reason: FinishReason | None = None
-            if r.request_id in new_tokens:
-                t = new_tokens[r.request_id]
-                r.append_token(t, now)
-                emitted.append(t)
-                reason = r.check_stop(max_len)
-            if reason is not None:
-                self.scheduler.finish_request(r, reason)
+        for r, idx, tok in zip(pending.sampled, pending.indices, values):
+            if r.request_id in pending.skip or idx >= len(r.output_token_ids):
+                continue  # stopped or aborted meanwhile: this token is not part of its output
+            r.output_token_ids[idx] = tok
+            params = r.sampling_params
+            stop = not params.ignore_eos and (tok == r.eos_token_id or tok in params.stop_token_ids)  # request.py:99-110
+            if stop and not (r.is_finished and r.finish_reason == FinishReason.STOP):
+                # whatever was appended after it (a placeholder of the step in flight) is dropped
+                del r.output_token_ids[idx + 1 :]
+                del r.token_times[idx + 1 :]
+                if not r.is_finished:
+                    self.scheduler.finish_request(r, FinishReason.STOP)
+                else:  # already closed by count in the same step: the stop token wins
+                    r.finish_reason = FinishReason.STOP
+                if self._pending is not None:
+                    self._pending.skip.add(r.request_id)
+            last = idx == len(r.output_token_ids) - 1
+            finished = r.is_finished and last
+            if finished:
                 self.metrics.record_finished(r)
-            else:
+            elif not r.is_finished:
                 self.block_manager.mark_computed(r.request_id, r.num_computed_tokens)
-            if emitted or r.is_finished:
-                out = RequestOutput.from_request(r, emitted)
-                if self.tokenizer is not None:
-                    out.text = self.tokenizer.decode(out.output_token_ids)
-                outputs.append(out)
+            out = RequestOutput(
+                request_id=r.request_id,
+                prompt_token_ids=r.prompt_token_ids,
+                output_token_ids=[t for t in r.output_token_ids[: idx + 1]],
+                new_token_ids=[tok],
+                finished=finished,
+                finish_reason=r.finish_reason if finished else None,
+            )
+            if self.tokenizer is not None:
+                out.text = self.tokenizer.decode(out.output_token_ids)
+            outputs.append(out)
         return outputs
 
     # ------------------------------------------------------------------ stats

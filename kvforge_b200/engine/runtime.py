@@ -84,6 +84,9 @@ class StepContext:
     h_query_start_loc: np.ndarray | None = None
     h_context_lens: np.ndarray | None = None
     h_state_slots: np.ndarray | None = None
+    # Where a token comes from the device: per token a row of ``token_feedback`` or -1.
+    feedback_rows: torch.Tensor | None = None
+    token_feedback: torch.Tensor | None = None
     # Upper bound on any context (fixes grid sizes of captured decode steps).
     context_bound: int = 0
     extras: dict = field(default_factory=dict)

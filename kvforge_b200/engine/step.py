@@ -36,6 +36,9 @@ class BatchItem:
     token_ids: Sequence[int]
     start_pos: int
     logits: str | Sequence[int] = "last"
+    # For a single token that the device sampled in the step before and the host has not read
+    # yet: its row in the runner's ``token_feedback`` buffer (``token_ids`` is then ignored).
+    feedback_row: int | None = None
 
     def wanted(self) -> list[int]:
         n = len(self.token_ids)
@@ -75,6 +78,7 @@ class _Layout:
         for name, size in (
             ("token_ids", self.n_cap),
             ("positions", self.n_cap),
+            ("feedback_rows", self.n_cap),
             ("logit_rows", self.r_cap),
             ("qsl", self.b_cap + 1),
             ("ctx", self.b_cap),
@@ -122,6 +126,8 @@ class ModelRunner:
         self._copy_done: torch.cuda.Event | None = None
         # made once for the widest step there can be, so its address never changes
         self._ensure(self._layout(rt.max_tokens, rt.max_seqs, self.max_width, rt.max_tokens).total)
+        # tokens sampled on the device that may feed the next step (set by whoever samples)
+        self.token_feedback: torch.Tensor | None = None
         self.num_forward_passes = 0  # continuous.py:105-106
         self.num_tokens_processed = 0
 
@@ -168,7 +174,14 @@ class ModelRunner:
             end = item.start_pos + k
             if end > self.max_model_len:
                 raise ValueError(f"request {item.seq_id} would reach {end} tokens, beyond max_model_len {self.max_model_len}")
-            host[o["token_ids"] + n : o["token_ids"] + n + k] = item.token_ids
+            if item.feedback_row is None:
+                host[o["token_ids"] + n : o["token_ids"] + n + k] = item.token_ids
+                host[o["feedback_rows"] + n : o["feedback_rows"] + n + k] = -1
+            else:
+                if k != 1 or self.token_feedback is None:
+                    raise ValueError("a token fed back on the device must be a single token, and a feedback buffer must be set")
+                host[o["token_ids"] + n] = 0
+                host[o["feedback_rows"] + n] = item.feedback_row
             host[o["positions"] + n : o["positions"] + n + k] = np.arange(item.start_pos, end, dtype=np.int32)
             for g in range(self.n_groups):
                 base = o["slots"] + g * lay.n_cap + n
@@ -210,6 +223,8 @@ class ModelRunner:
             num_seqs=nb,
             token_ids=view("token_ids", n),
             positions=view("positions", n),
+            feedback_rows=view("feedback_rows", n) if self.token_feedback is not None else None,
+            token_feedback=self.token_feedback,
             query_start_loc=view("qsl", nb + 1),
             context_lens=view("ctx", nb),
             state_slots=view("state_slots", nb),
@@ -278,6 +293,7 @@ class ModelRunner:
         host, o = self._host.numpy(), lay.off
         host[o["token_ids"] : o["token_ids"] + bucket] = 0
         host[o["positions"] : o["positions"] + bucket] = 0
+        host[o["feedback_rows"] : o["feedback_rows"] + bucket] = -1
         host[o["logit_rows"] : o["logit_rows"] + bucket] = 0
         for g in range(self.n_groups):
             host[o["slots"] + g * bucket : o["slots"] + (g + 1) * bucket] = -1

@@ -18,7 +18,7 @@ _SUF = {torch.float32: "f32", torch.bfloat16: "bf16"}
 
 # p = pointer, i = int, l = long long, f = float
 _SIGNATURES = {
-    "kvf_embed_{s}": "pppiiipp",
+    "kvf_embed_{s}": "pppppiiipp",
     "kvf_add_rmsnorm_{s}": "pppilpppiifp",
     "kvf_add_residual_{s}": "pplp",
     "kvf_rope_cache_{s}": "ppilppppppiiiiiilpp",
@@ -128,8 +128,17 @@ def _suffix(dtype: torch.dtype) -> str:
 # ------------------------------------------------------------------ elementwise
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torch.Tensor | None = None) -> None:
-    """``resid[n, :] = float(table[ids[n], :])``; ``ids`` int32 ``[N]``, ``resid`` float ``[N, H]``."""
+def embed(
+    table: torch.Tensor,
+    ids: torch.Tensor,
+    resid: torch.Tensor,
+    err: torch.Tensor | None = None,
+    feedback_rows: torch.Tensor | None = None,
+    feedback: torch.Tensor | None = None,
+) -> None:
+    """``resid[n, :] = float(table[id, :])``; ``ids`` int32 ``[N]``, ``resid`` float ``[N, H]``.
+    Where ``feedback_rows[n] >= 0`` the id is ``feedback[feedback_rows[n]]`` (a token sampled on
+    the device in the step before) instead of ``ids[n]``."""
     s = _suffix(table.dtype)
     _need(table, None, "table")
     _need(ids, torch.int32, "ids")
@@ -137,8 +146,13 @@ def embed(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torc
     n, h = resid.shape
     if table.shape[1] != h or ids.numel() < n:
         raise ValueError("embed: shapes do not agree")
+    if feedback_rows is not None:
+        _need(feedback_rows, torch.int32, "feedback_rows")
+        _need(feedback, torch.int32, "feedback")
+        if feedback_rows.numel() < n:
+            raise ValueError("embed: feedback_rows is too short")
     name = f"kvf_embed_{s}"
-    _check(_fn(name)(_ptr(table), _ptr(ids), _ptr(resid), n, h, table.shape[0], _ptr(err), _stream()), name)
+    _check(_fn(name)(_ptr(table), _ptr(ids), _ptr(feedback_rows), _ptr(feedback), _ptr(resid), n, h, table.shape[0], _ptr(err), _stream()), name)
 
 
 def add_rmsnorm(

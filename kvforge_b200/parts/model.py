@@ -158,7 +158,7 @@ class DecoderModel:
         """Runs the blocks.  Returns the float residual stream and the sum still pending."""
         rt = self.rt
         resid = rt.buf("model.resid", ctx.num_tokens, self.spec.hidden_size, torch.float32)
-        ops.embed(self.embed_table, ctx.token_ids, resid, rt.err)
+        ops.embed(self.embed_table, ctx.token_ids, resid, rt.err, ctx.feedback_rows, ctx.token_feedback)
         delta = None
         for idx, call in enumerate(self.spec.execution):
             delta = self.blocks[call.layer].forward(ctx, resid, delta, self.caches[idx])

@@ -27,11 +27,13 @@ def engine_for(folder, name, dtype="float32", num_blocks=256, **sched):
     sched.setdefault("max_num_batched_tokens", 256)
     sched.setdefault("max_model_len", 256)
     cuda_graphs = sched.pop("cuda_graphs", True)
+    async_output = sched.pop("async_output", True)
     cfg = EngineConfig(
         cache=CacheConfig(block_size=TINY[name]["block_size"], num_blocks=num_blocks),
         scheduler=SchedulerConfig(**sched),
         dtype=dtype,
         cuda_graphs=cuda_graphs,
+        async_output=async_output,
     )
     return InferenceEngine(cfg, model=folder)
 
@@ -149,6 +151,32 @@ def test_stop_token_abort_and_length_limit(folders):
     assert engine.block_manager.num_free_blocks == engine.block_manager.num_blocks
     with pytest.raises(ValueError):
         engine.add_request([0, 256], greedy(1))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_reading_tokens_a_step_late_changes_no_output(folders, dtype):
+    """Tokens read while the next step runs (the default) and tokens read before it: the same
+    outputs, also when stop tokens end requests at different times and pages are short."""
+    from kvforge_b200 import SamplingParams
+
+    name = "tiny-c"
+    prompts = prompts_for(name, [10, 14, 9, 12, 3, 13], seed=31)
+    plain = PlainLlama(folders[name])
+    stops = [plain.greedy(p, 9)[5] for p in prompts]  # each request stops at a token it will really produce
+    sp = [SamplingParams(max_tokens=11, temperature=0.0, stop_token_ids=[t]) for t in stops]
+    runs = {}
+    for mode in (True, False):
+        engine = engine_for(folders[name], name, dtype, num_blocks=16, max_num_seqs=6, async_output=mode)
+        outs = engine.generate(prompts, sp)
+        runs[mode] = [(o.output_token_ids, o.finish_reason.value) for o in outs]
+        assert engine.block_manager.num_free_blocks == 16 and not engine.has_unfinished_requests()
+        engine.block_manager.check_invariants()
+    assert runs[True] == runs[False]
+    if dtype == "float32":
+        for p, t, (ids, reason) in zip(prompts, stops, runs[True]):
+            want = plain.greedy(p, 11)
+            want = want[: want.index(t) + 1]
+            assert ids == want and reason == "stop"
 
 
 def test_temperature_sampling_does_not_depend_on_the_batch(folders):
