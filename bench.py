@@ -156,7 +156,9 @@ def time_decode(core, batch: int, start_ctx: int, steps: int, warmup: int, sampl
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
-    k0 = core.runner.num_kernel_launches
+    from kvforge_b200 import ops
+
+    k0 = ops.launch_count + core.runner.num_graph_kernels
     g0 = sum(core.runner.graph_kernels.values())
     ctx0 = pos
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -166,8 +168,9 @@ def time_decode(core, batch: int, start_ctx: int, steps: int, warmup: int, sampl
     end.record()
     torch.cuda.synchronize()
     seconds = start.elapsed_time(end) / 1e3
-    # kernels of this library: those of the steps (inside replayed graphs) plus one sampling kernel a step
-    launched = (core.runner.num_kernel_launches - k0) + (steps if sample else 0)
+    # kernels of this library: launched one by one (sampling; the model's when graphs are off) plus
+    # those inside replayed graphs
+    launched = ops.launch_count + core.runner.num_graph_kernels - k0
     if sum(core.runner.graph_kernels.values()) != g0:
         launched = None  # a graph was captured inside the timed region: the count would mix things
     for rid in ids:

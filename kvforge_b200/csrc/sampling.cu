@@ -272,6 +272,47 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   }
 }
 
+// ---- greedy for a whole batch in two short kernels: many CTAs per row find the best
+// (value, lowest index) of a stretch of the vocabulary, one warp per row picks among them.
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, long long ld, int V, int chunks,
+                      unsigned long long* __restrict__ partial) {
+  __shared__ unsigned long long red[8];
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.y, c = blockIdx.x;
+  const int len = (V + chunks - 1) / chunks;
+  const int lo = c * len, hi = min(V, lo + len);
+  const float* row = logits + (size_t)r * ld;
+  unsigned long long best = 0;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const unsigned long long v = ((unsigned long long)ordered_key(row[i]) << 32) | (0xFFFFFFFFu - (unsigned)i);
+    best = v > best ? v : best;
+  }
+  best = warp_max_u64(best);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    unsigned long long v = threadIdx.x < 8 ? red[threadIdx.x] : 0ull;
+    v = warp_max_u64(v);
+    if (threadIdx.x == 0) partial[(size_t)r * chunks + c] = v;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const unsigned long long* __restrict__ partial, int chunks, int* __restrict__ out_tokens) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x;
+  unsigned long long best = 0;
+  for (int c = threadIdx.x; c < chunks; c += 32) {
+    const unsigned long long v = partial[(size_t)r * chunks + c];
+    best = v > best ? v : best;
+  }
+  best = warp_max_u64(best);
+  if (threadIdx.x == 0) out_tokens[r] = (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull));
+}
+
 }  // namespace
 
 // logits: [R, V] float with row stride ld.  temps/top_ks/top_ps/rand_keys: [R] (null temps =
@@ -284,4 +325,15 @@ KVF_API int kvf_sample_f32(const float* logits, long long ld, int R, int V, cons
   if (V <= 0) return (int)cudaErrorInvalidValue;
   return launch(sample_kernel, dim3(R), dim3(THREADS), 0, st, logits, ld, V, temps, top_ks, top_ps, rand_keys,
                 out_tokens, probs_out);
+}
+
+// Greedy tokens of float logits [R, V] (row stride ld): the highest logit, the lowest index
+// among equals.  `partial` is scratch of R * chunks 64-bit words.
+KVF_API int kvf_argmax_f32(const float* logits, long long ld, int R, int V, unsigned long long* partial, int chunks,
+                           int* out_tokens, cudaStream_t st) {
+  if (R <= 0) return 0;
+  if (V <= 0 || chunks <= 0 || !partial || (unsigned)R > 65535u) return (int)cudaErrorInvalidValue;
+  int rc = launch(argmax_partial_kernel, dim3(chunks, R), dim3(256), 0, st, logits, ld, V, chunks, partial);
+  if (rc) return rc;
+  return launch(argmax_final_kernel, dim3(R), dim3(32), 0, st, (const unsigned long long*)partial, chunks, out_tokens);
 }

@@ -119,6 +119,7 @@ class ModelRunner:
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.graph_kernels: dict[int, int] = {}  # kernels of this library inside each captured graph
         self.num_kernel_launches = 0  # kernels of this library launched by steps, replays included
+        self.num_graph_kernels = 0  # those of them that ran inside replayed graphs
         self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
         self._cap = 0
         self._host: torch.Tensor | None = None
@@ -305,6 +306,7 @@ class ModelRunner:
         graph, logits = entry
         graph.replay()
         self.num_kernel_launches += self.graph_kernels[bucket]
+        self.num_graph_kernels += self.graph_kernels[bucket]
         self.num_forward_passes += 1
         self.num_tokens_processed += n
         return logits[:r]

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "kvf_set_pdl": "i",
     "kvf_gemm_tcgen05_bf16": "pppiiiiiiipp",
     "kvf_sample_f32": "pliippppppp",
+    "kvf_argmax_f32": "pliipipp",
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 
@@ -626,6 +627,24 @@ def sample(
         ),
         name,
     )  # fmt: skip
+
+
+ARGMAX_CHUNKS = 32
+
+
+def argmax(logits: torch.Tensor, out_tokens: torch.Tensor, partial: torch.Tensor) -> None:
+    """Greedy tokens of float ``logits [R, V]`` (lowest index among equal maxima) in two short
+    kernels; ``partial``: int64 scratch ``[R, ARGMAX_CHUNKS]``."""
+    _need(logits, torch.float32, "logits", contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("argmax: logits must be [R, V] with unit inner stride")
+    r, v = logits.shape
+    _need(out_tokens, torch.int32, "out_tokens")
+    _need(partial, torch.int64, "partial")
+    if out_tokens.numel() < r or partial.numel() < r * ARGMAX_CHUNKS:
+        raise ValueError("argmax: an output or scratch buffer is too small")
+    name = "kvf_argmax_f32"
+    _check(_fn(name)(_ptr(logits), logits.stride(0), r, v, _ptr(partial), ARGMAX_CHUNKS, _ptr(out_tokens), _stream()), name, 2)
 
 
 def splitmix64(z: int) -> int:

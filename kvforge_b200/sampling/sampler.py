@@ -40,11 +40,12 @@ class Sampler:
         self._host = torch.empty(6 * m, dtype=torch.int32, pin_memory=True)
         self._dev = torch.empty(6 * m, dtype=torch.int32, device=self.device)
         self._tokens = torch.empty(m, dtype=torch.int32, device=self.device)
+        self._argmax_scratch = torch.empty(m * ops.ARGMAX_CHUNKS, dtype=torch.int64, device=self.device)
         self._copied: torch.cuda.Event | None = None
 
     def _grow(self, rows: int) -> None:
         if rows > self.max_rows:
-            self.__init__(self.device, rows)
+            raise ValueError(f"{rows} rows to sample, but the sampler was made for {self.max_rows}")
 
     def sample(
         self,
@@ -60,7 +61,10 @@ class Sampler:
         m = self.max_rows
         tokens = self._tokens[:r]
         if all(p.greedy for p in params):
-            ops.sample(logits, tokens, probs_out=probs_out)
+            if probs_out is None:
+                ops.argmax(logits, tokens, self._argmax_scratch)
+            else:
+                ops.sample(logits, tokens, probs_out=probs_out)
             return tokens
         if self._copied is not None:
             self._copied.synchronize()  # the last call's copy has left the host buffer

@@ -476,6 +476,23 @@ def test_greedy_is_argmax_with_lowest_index_on_ties(ops):
 
 
 @pytest.mark.parametrize("v", [5, 320, 1003, 128256])
+def test_batched_argmax(ops, v):
+    logits = torch.randn(9, v + 3)[:, :v]  # a row stride that is not the width
+    if v > 100:
+        logits[2, 77] = logits[2, v - 1] = 9.0
+        logits[5, 0] = 11.0
+    out = torch.empty(9, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(9 * ops.ARGMAX_CHUNKS, dtype=torch.int64, device="cuda")
+    dl = torch.empty(9, v + 3, device="cuda")[:, :v]
+    dl.copy_(logits)
+    ops.argmax(dl, out, scratch)
+    want = logits.argmax(-1)
+    if v > 100:
+        want[2] = 77
+    assert out.cpu().tolist() == want.tolist()
+
+
+@pytest.mark.parametrize("v", [5, 320, 1003, 128256])
 def test_sampling_distribution_matches_the_formula(ops, v):
     g = torch.Generator().manual_seed(v)
     logits = torch.randn(8, v, generator=g) * 3
