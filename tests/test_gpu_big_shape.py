@@ -1,0 +1,77 @@
+"""The kernels that only real layer sizes reach (tensor-core attention with head size 64 and
+four query heads per kv head, the decode GEMM with slices of K, the tcgen05 GEMM with its
+fused gate, the 128k-wide output head), checked through the engine at the width of
+Llama-3.2-1B with two layers and random weights, against the plain implementation."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import traces
+from helpers import random_tokens, rel_err
+from kvforge_b200 import PRESETS, ModelConfig
+from kvforge_b200.models.folder import write_random_model
+from plain_llama import PlainLlama
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    base = PRESETS["llama-3.2-1b"]
+    cfg = ModelConfig(**{**base.__dict__, "num_layers": 2, "max_position_embeddings": 4096})
+    folder = tmp_path_factory.mktemp("big") / "llama-1b-width-2-layers"
+    # weights large enough that attention is not uniform: q.k has a spread of a few units
+    write_random_model(folder, cfg, seed=5, store_dtype=torch.bfloat16, init_std=0.03, norm_std=0.05)
+    reqs = {"a": random_tokens(cfg.vocab_size, 300, seed=1), "b": random_tokens(cfg.vocab_size, 97, seed=2)}
+    plain = PlainLlama(folder, device="cuda")  # the plain implementation in 32-bit, run on the GPU for speed
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = {rid: plain.logits(t).cpu() for rid, t in reqs.items()}
+    del plain
+    torch.cuda.empty_cache()
+    return folder, reqs, ref
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 6e-2)])
+def test_llama_1b_width_whole_portions_and_decode(big, dtype, tol):
+    from test_gpu_replay import check, replay_in_process
+
+    folder, reqs, ref = big
+    for steps in (traces.whole(reqs), traces.tail_one_by_one(reqs, 20), traces.mixed(reqs, {"a": 280, "b": 80}, max_live=2, seed=4)):
+        outputs = replay_in_process(folder, dtype, steps)
+        worst = check(steps, outputs, ref, tol)
+        assert worst < tol
+
+
+def test_llama_1b_width_bfloat16_is_no_worse_than_plain_bfloat16(big):
+    from test_gpu_replay import MEAN_SLACK, check, replay_in_process
+
+    folder, reqs, ref = big
+    plain16 = PlainLlama(folder, dtype=torch.bfloat16, device="cuda")
+    errs = []
+    for rid, t in reqs.items():
+        p16 = plain16.logits(t).cpu()
+        errs += [rel_err(p16[i], ref[rid][i]) for i in range(len(t))]
+    bound = MEAN_SLACK * sum(errs) / len(errs) + 5e-4
+    steps = traces.whole(reqs)
+    check(steps, replay_in_process(folder, "bfloat16", steps), ref, 6e-2, bound)
+
+
+def test_llama_1b_width_generation_uses_graphs_and_the_device_token_loop(big):
+    from kvforge_b200 import CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
+
+    folder, reqs, ref = big
+    prompts = [reqs["a"][:150], reqs["b"][:40], reqs["a"][150:170]]
+    outs = {}
+    for mode in ("graphs+async", "plain"):
+        cfg = EngineConfig(
+            cache=CacheConfig(block_size=16, num_blocks=64),
+            scheduler=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=256, max_model_len=512),
+            dtype="bfloat16", cuda_graphs=mode != "plain", async_output=mode != "plain",
+        )  # fmt: skip
+        engine = InferenceEngine(cfg, model=folder)
+        res = engine.generate(prompts, SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))
+        outs[mode] = [o.output_token_ids for o in res]
+        assert all(len(o) == 12 for o in outs[mode])
+    assert outs["graphs+async"] == outs["plain"]
