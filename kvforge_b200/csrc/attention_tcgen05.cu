@@ -1,0 +1,491 @@
+// Paged grouped-query attention for many queries (prompts, portions, mixed batches) on the
+// tcgen05 tensor cores; bfloat16, head size 64.  Same contract as attention_generic.cu.
+//
+// One CTA serves 128 rows of one kv head of one sequence; a row is a (query token, head of the
+// group) pair, so 128/g tokens.  Keys are walked in tiles of 64 from position 0 (or from the
+// tile that holds the window's first key).  Per tile t:
+//   S = Q K^T      tcgen05.mma 128 x 64 x 64, Q and the K tile in 128-byte-swizzled shared memory
+//                  (K-major), S in tensor memory: two buffers of 64 float columns, so the tensor
+//                  core writes S(t+1) while the softmax reads S(t);
+//   softmax        thread r owns row r (tensor-memory lane r): it reads the 64 scores once with
+//                  tcgen05.ld, keeps the running maximum and sum in registers, and writes
+//                  P = exp2(S * scale - m) as bfloat16 into shared memory (two buffers) in the
+//                  swizzled K-major layout of an A operand;
+//   O += P V       tcgen05.mma 128 x 64 x 64, the V tile [keys][64] as an MN-major B operand; O
+//                  stays in tensor memory (64 columns) over all tiles.
+// The maximum m that P is scaled by follows the row's true maximum lazily: a thread raises it
+// only when the true maximum has grown by more than 8 (in log2 units), so P <= 256; then the
+// warp multiplies its rows of O by exp2(m_old - m_new) in tensor memory (tcgen05.ld / st) before
+// the next P V.  The sum l carries the same factor, so O / l is the exact softmax average.
+// Whether a thread rescales depends on its own row only: a row's result does not depend on the
+// rows beside it.
+// Warps 0-3 do the softmax, warp 4 brings Q and the K/V tiles in with cp.async (pages are not
+// contiguous, so no tensor-map copy; two tiles in flight) and hands them to the tensor core
+// through a proxy fence and mbarriers, one thread of warp 5 issues the MMAs.  Two CTAs fit an SM
+// (112 KB of shared memory and 256 tensor-memory columns each).  CTAs with the most keys to
+// walk (the last queries) come first in the grid.
+//
+// Every mbarrier wait is bounded; if one runs out the kernel raises bit 4 of the error flag and
+// winds down.  No cluster launch, no multicast.
+#include "common.cuh"
+
+using namespace kvf;
+
+namespace {
+
+constexpr int D = 64;
+constexpr int BM = 128;  // rows per CTA
+constexpr int BN = 64;   // keys per tile
+constexpr int THREADS = 192;
+constexpr int KV_STAGES = 4;
+constexpr int LOOKAHEAD = 2;                 // tiles in flight behind the one being handed over
+constexpr uint32_t Q_BYTES = BM * 128;       // [128 rows][64] bfloat16
+constexpr uint32_t KV_BYTES = BN * 128;      // a [64 keys][64] bfloat16 tile
+constexpr uint32_t P_BYTES = BM * 128;       // [128 rows][64 keys] bfloat16
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
+constexpr float RESCALE_STEP = 8.f;          // log2 units
+
+struct TcAttnParams {
+  const bf16* q;
+  bf16* out;
+  const bf16* kcache;
+  const bf16* vcache;
+  const int* block_tables;
+  const int* qsl;
+  const int* ctx_lens;
+  int* err;
+  int q_stride, out_stride, bt_stride;
+  int nh, nkv, block_size, bs_shift;
+  int window;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* err) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(32);
+  }
+  if (err) atomicOr(err, 4);
+  return false;
+}
+__device__ __forceinline__ void cpa16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cpa_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+// writes made through the generic proxy (cp.async, st.shared) become visible to the tensor core
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 16-byte chunk `c` (0..7) of row `row` of a [rows][64] bfloat16 tile with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(int row, int c) { return (uint32_t)(row * 128 + ((c ^ (row & 7)) << 4)); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (the same
+// fields serve a K-major tile and an MN-major tile that is one swizzle row wide).
+__device__ __forceinline__ uint64_t sdesc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: float accumulator, bfloat16 operands, A K-major, B K-major
+// or MN-major (bit 16), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t idesc(int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t id, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// Waits for the thread's tensor-memory loads; naming the registers as operands keeps the
+// compiler from using them before the wait.
+__device__ __forceinline__ void tmem_wait(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+        "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+        "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pk(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One tile of the softmax for the thread's row.  v: the 64 raw scores (in place: not kept).
+// MASK: some key of the tile may be hidden from some row of the warp.  Returns the tile's sum of
+// P and stores P (bfloat16) into the row of the A-operand tile at p_row (a shared address of
+// the row's first byte; chunk c of the row lies at p_row + ((c ^ (r & 7)) << 4)).
+template <bool MASK>
+__device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)[32], float& m_ref, float& corr,
+                                              float scale_log2, int first, int last, uint32_t p_row, int r7) {
+  // first/last: the tile-local range of visible keys of this row (MASK only)
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (!MASK || (j >= first && j <= last)) mx = fmaxf(mx, __uint_as_float(va[j]));
+    if (!MASK || (j + 32 >= first && j + 32 <= last)) mx = fmaxf(mx, __uint_as_float(vb[j]));
+  }
+  mx *= scale_log2;  // scale > 0
+  corr = 1.f;
+  if (mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY)) {
+    corr = ex2(m_ref - mx);  // 0 the first time
+    m_ref = mx;
+  }
+  const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t(&v)[32] = half ? vb : va;
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const int c = half * 32 + j;
+      float e0 = ex2(fmaf(__uint_as_float(v[j]), scale_log2, -m_use));
+      float e1 = ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, -m_use));
+      if (MASK) {
+        if (c < first || c > last) e0 = 0.f;
+        if (c + 1 < first || c + 1 > last) e1 = 0.f;
+      }
+      sum0 += e0;
+      sum1 += e1;
+      w[j >> 1] = pk(e0, e1);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const uint32_t dst = p_row + (uint32_t)(((half * 4 + q4) ^ r7) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[4 * q4]), "r"(w[4 * q4 + 1]),
+                   "r"(w[4 * q4 + 2]), "r"(w[4 * q4 + 3])
+                   : "memory");
+    }
+  }
+  return sum0 + sum1;
+}
+
+__global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // no slack for rounding up (two CTAs have to fit an SM): the base must be 1024-byte aligned
+  // as declared, else the kernel refuses (bit 8 of the error flag) rather than compute garbage
+  const uint32_t base = sm32(smem_raw);
+  const uint32_t q_s = base;                                    // [128 rows][64]
+  const uint32_t kv_s = q_s + Q_BYTES;                          // per stage: K [64 keys][64], V [64 keys][64]
+  const uint32_t p_s = kv_s + KV_STAGES * 2 * KV_BYTES;         // two [128 rows][64 keys] buffers
+  const uint32_t bars = p_s + 2 * P_BYTES;
+  const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * KV_STAGES;
+  const uint32_t s_full0 = kv_empty0 + 8 * KV_STAGES, p_full0 = s_full0 + 16, pv_done0 = p_full0 + 16;
+  const uint32_t tmem_slot = pv_done0 + 16;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - base));
+
+  pdl_launch();
+  if (base & 1023u) {
+    if (threadIdx.x == 0 && p.err) atomicOr(p.err, 8);
+    pdl_wait();
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, kvh = blockIdx.z;
+  const int g = p.nh / p.nkv;
+  const int tq = BM / g;
+  const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
+  const int ctx = p.ctx_lens[b];
+  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tq;  // the longest walks first
+  const bool live = q_len > 0 && ctx > 0 && q0 < q_len;  // uniform over the CTA
+  const int n_tok = live ? min(tq, q_len - q0) : 0;
+  const int p_first = ctx - q_len + q0;
+  const int kv_hi = p_first + n_tok;
+  const int kv_lo = p.window > 0 ? (max(0, p_first - p.window + 1) / BN) * BN : 0;
+  const int n_tiles = live ? (kv_hi - kv_lo + BN - 1) / BN : 0;
+
+  if (threadIdx.x == 0) {
+    bar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      bar_init(kv_full0 + 8 * s, 1);
+      bar_init(kv_empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      bar_init(s_full0 + 8 * s, 1);
+      bar_init(p_full0 + 8 * s, BM);
+      bar_init(pv_done0 + 8 * s, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;  // S buffers: columns 0..63, 64..127; O: 128..191
+
+  pdl_wait();
+
+  if (live && warp == 4) {
+    // ---- loader: Q, then a K and a V tile per stage; 16-byte chunks into the swizzled layout
+    const bf16* qg = p.q + (size_t)(q_begin + q0) * p.q_stride + (size_t)(kvh * g) * D;
+    for (int idx = lane; idx < BM * 8; idx += 32) {
+      const int r = idx >> 3, c = idx & 7;
+      const int tok = r / g, hh = r - tok * g;
+      const bool valid = tok < n_tok;
+      cpa16(q_s + sw128(r, c), qg + (valid ? (size_t)tok * p.q_stride + (size_t)hh * D + c * 8 : 0), valid);
+    }
+    const int* bt = p.block_tables + (size_t)b * p.bt_stride;
+    // A tile's 64 keys sit in up to 64 pages: lane l looks up keys l and l+32 (independent table
+    // reads), and the copy loop, in which 8 lanes share a key, gets each key's row from the lane
+    // that holds it.
+    auto issue_tile = [&](int t) {
+      const int s = t % KV_STAGES;
+      const uint32_t ks = kv_s + s * 2 * KV_BYTES, vs = ks + KV_BYTES;
+      const int t0 = kv_lo + t * BN;
+      long long row[2];  // element offset of the key's row in the cache, or -1
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int kp = t0 + lane + 32 * j;
+        int blk = -1, off = 0;
+        if (kp < ctx) {
+          if (p.bs_shift >= 0) {
+            blk = bt[kp >> p.bs_shift];
+            off = kp & (p.block_size - 1);
+          } else {
+            blk = bt[kp / p.block_size];
+            off = kp % p.block_size;
+          }
+        }
+        row[j] = blk >= 0 ? (((long long)blk * p.nkv + kvh) * p.block_size + off) * D : -1;
+      }
+      const int c = lane & 7, sub = lane >> 3;
+#pragma unroll
+      for (int i = 0; i < BN / 4; ++i) {
+        const int key = 4 * i + sub;  // held by lane key % 32 in slot key / 32 = i / 8
+        const long long src = __shfl_sync(0xffffffffu, row[i >> 3], 4 * (i & 7) + sub);
+        const bool valid = src >= 0;
+        const long long at = valid ? src + c * 8 : 0;
+        cpa16(ks + sw128(key, c), p.kcache + at, valid);
+        cpa16(vs + sw128(key, c), p.vcache + at, valid);
+      }
+    };
+    // groups: {Q, tile 0}, {tile 1}, ...; an empty group stands for a tile past the end
+#pragma unroll
+    for (int t = 0; t < LOOKAHEAD; ++t) {
+      if (t < n_tiles) issue_tile(t);
+      cpa_commit();
+    }
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      // tile t (and, the first time, Q) has landed: hand it to the tensor core
+      cpa_wait<LOOKAHEAD - 1>();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (t == 0) bar_arrive(q_full);
+        bar_arrive(kv_full0 + 8 * (t % KV_STAGES));
+      }
+      const int nx = t + LOOKAHEAD;
+      if (nx < n_tiles) {
+        if (nx >= KV_STAGES) ok = bar_wait(kv_empty0 + 8 * (nx % KV_STAGES), ((nx / KV_STAGES) - 1) & 1, p.err);
+        if (ok) issue_tile(nx);
+      }
+      cpa_commit();
+    }
+    cpa_wait<0>();
+  } else if (live && warp == 5) {
+    if (lane == 0) {
+      // ---- MMA issuer: S(t+1) goes out before P(t) V(t), so the softmax never waits for it
+      constexpr uint32_t id_s = idesc(BN, 0), id_o = idesc(D, 1);
+      const uint64_t qd = sdesc(q_s);
+      auto issue_s = [&](int t) {
+        const uint64_t kd = sdesc(kv_s + (t % KV_STAGES) * 2 * KV_BYTES);
+        const uint32_t dst = tmem_s + (uint32_t)((t & 1) * BN);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma(dst, qd + 2 * kk, kd + 2 * kk, id_s, kk > 0);
+        umma_commit(s_full0 + 8 * (t & 1));
+      };
+      bool ok = bar_wait(q_full, 0, p.err);
+      if (ok) ok = bar_wait(kv_full0, 0, p.err);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s(0);
+      }
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (t + 1 < n_tiles) {
+          // the S buffer of tile t+1 was read by the softmax of tile t-1 (P(t-1) arrived before P(t-1) V)
+          ok = bar_wait(kv_full0 + 8 * ((t + 1) % KV_STAGES), ((t + 1) / KV_STAGES) & 1, p.err);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(t + 1);
+        }
+        ok = bar_wait(p_full0 + 8 * (t & 1), (t >> 1) & 1, p.err);  // P(t) is in shared memory, O has been rescaled
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vs = kv_s + (t % KV_STAGES) * 2 * KV_BYTES + KV_BYTES;
+        const uint64_t pd = sdesc(p_s + (t & 1) * P_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          // A: 16 keys of P = 32 bytes along the row; B: 16 keys of V = 16 rows of 128 bytes
+          umma(tmem_o, pd + 2 * kk, sdesc(vs + kk * 16 * 128), id_o, (t > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(pv_done0 + 8 * (t & 1));         // O holds tiles 0..t; P buffer t&1 may be rewritten
+        umma_commit(kv_empty0 + 8 * (t % KV_STAGES));  // and the stage may be refilled
+      }
+    }
+  } else if (live && warp < 4) {
+    // ---- softmax and output: thread r owns row r
+    const int r = threadIdx.x;
+    const int tok = r / g, hh = r - tok * g;
+    const bool valid = tok < n_tok;
+    const int pos = valid ? p_first + tok : -1;
+    const int lo = p.window > 0 ? pos - p.window + 1 : 0;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int key0 = kv_lo + t * BN;
+      // (tcgen05.ld and st are warp-wide: the lanes of a warp leave the loop together)
+      ok = __all_sync(0xffffffffu, bar_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1, p.err));
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t va[32], vb[32];
+      tmem_ld32(tmem_s + lane_addr + (uint32_t)((t & 1) * BN), va);
+      tmem_ld32(tmem_s + lane_addr + (uint32_t)((t & 1) * BN + 32), vb);
+      // the P buffer of this tile was the A operand of P(t-2) V
+      if (t >= 2) ok = bar_wait(pv_done0 + 8 * (t & 1), ((t >> 1) - 1) & 1, p.err);
+      tmem_wait(va);
+      tmem_wait(vb);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const bool need_mask = (key0 + BN - 1 > pos) || (key0 < lo);
+      const uint32_t p_row = p_s + (uint32_t)(t & 1) * P_BYTES + (uint32_t)r * 128u;
+      float corr, sum;
+      if (__any_sync(0xffffffffu, need_mask))
+        sum = softmax_tile<true>(va, vb, m_ref, corr, p.scale_log2, max(lo, key0) - key0, min(pos, key0 + BN - 1) - key0, p_row, r & 7);
+      else
+        sum = softmax_tile<false>(va, vb, m_ref, corr, p.scale_log2, 0, BN - 1, p_row, r & 7);
+      l = l * corr + sum;
+      if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+        // O *= corr, once every earlier P V has been added to it
+        ok = __all_sync(0xffffffffu, bar_wait(pv_done0 + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, p.err));
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_addr + (uint32_t)c0, v);
+          tmem_wait(v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+          tmem_st32(tmem_o + lane_addr + (uint32_t)c0, v);
+        }
+        tmem_wait_st();
+      }
+      fence_async_smem();
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      bar_arrive(p_full0 + 8 * (t & 1));
+    }
+    if (ok) ok = __all_sync(0xffffffffu, bar_wait(pv_done0 + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.err));
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + (size_t)(q_begin + q0 + (valid ? tok : 0)) * p.out_stride + (size_t)(kvh * g + hh) * D;
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + lane_addr + (uint32_t)c0, v);
+        tmem_wait(v);
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j + e]) * inv;
+          if (valid)
+            *reinterpret_cast<uint4*>(dst + c0 + j) = make_uint4(pk(f[0], f[1]), pk(f[2], f[3]), pk(f[4], f[5]), pk(f[6], f[7]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+}  // namespace
+
+// bfloat16, head size 64, nh/nkv <= 128; out rows and q rows 16-byte aligned.  err: device flag.
+KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const void* kcache, const void* vcache,
+                                             const int* block_tables, const int* qsl, const int* ctx_lens, int B,
+                                             int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
+                                             int nkv, int d, int block_size, float scale, int window, int* err,
+                                             cudaStream_t st) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (d != D || nkv <= 0 || nh % nkv != 0 || nh / nkv > BM || block_size <= 0) return (int)cudaErrorInvalidValue;
+  if ((q_stride & 7) || (out_stride & 7) || ((((uintptr_t)q) | ((uintptr_t)out)) & 15)) return (int)cudaErrorInvalidValue;
+  if ((unsigned)B > 65535u || (unsigned)nkv > 65535u) return (int)cudaErrorInvalidValue;
+  TcAttnParams p;
+  p.q = (const bf16*)q; p.out = (bf16*)out; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
+  p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens; p.err = err;
+  p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
+  p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == block_size) p.bs_shift = sh;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int g = nh / nkv, tq = BM / g;
+  constexpr size_t smem = Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES + 128;
+  cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  return launch(attn_tcgen05_kernel, dim3((max_q_len + tq - 1) / tq, B, nkv), dim3(THREADS), smem, st, p);
+}

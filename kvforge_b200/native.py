@@ -30,7 +30,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # name -> (sources, extra flags).  One shared library per entry.
 LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     "core": (
-        ["elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "attention_mma.cu", "gemm_skinny_bf16.cu", "gemm_tcgen05_bf16.cu", "sampling.cu"],
+        ["elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny_bf16.cu", "gemm_tcgen05_bf16.cu", "sampling.cu"],
         [],
     ),
     # one entry point that allocates nothing (csrc/kvforge_noalloc.h); a library of its own, so
@@ -142,9 +142,17 @@ def build(name: str, verbose: bool = True) -> Path:
             os.replace(tmp, out)
             if verbose:
                 _say(f"built {out.name} in {time.time() - t0:.0f} s")
+            _prune_stale(name, out.parent)
             return out
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _prune_stale(name: str, keep: Path) -> None:
+    """Builds of ``name`` from sources that have changed since are of no use to anyone."""
+    for old in keep.parent.glob(f"{name}-*"):
+        if old != keep and old.is_dir():
+            shutil.rmtree(old, ignore_errors=True)
 
 
 def load(name: str = "core") -> ctypes.CDLL:

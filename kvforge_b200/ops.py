@@ -26,6 +26,7 @@ _SIGNATURES = {
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
+    "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiifipp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
@@ -353,6 +354,12 @@ def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decod
     return dtype == torch.bfloat16 and d in (64, 128) and g <= (16 if decode_form else 64)
 
 
+def tcgen05_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:
+    """Whether the tcgen05 kernel (``csrc/attention_tcgen05.cu``) takes this shape: many queries
+    (not the decode form), bfloat16, head size 64."""
+    return dtype == torch.bfloat16 and d == 64 and not decode_form and nh // max(nkv, 1) <= 128
+
+
 def paged_attention(
     q: torch.Tensor,
     out: torch.Tensor,
@@ -373,6 +380,7 @@ def paged_attention(
     max_context: int | None = None,
     split_size: int = 256,
     kernel: str = "auto",
+    err: torch.Tensor | None = None,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
@@ -380,9 +388,10 @@ def paged_attention(
     ``q``: rows of ``q_stride`` elements whose first ``nh*d`` are the query heads; ``out``:
     ``[N, nh*d]``.  With ``scratch`` (and every sequence holding one query) the decode form
     runs: key ranges of ``split_size`` in parallel, then a merge; ``max_context`` bounds the
-    contexts.  ``kernel``: ``"auto"`` takes the tensor-core kernel where it applies
-    (bfloat16, head size 64 or 128) and the FP32-pipe kernel elsewhere; ``"generic"`` and
-    ``"mma"`` force one (tests).
+    contexts.  ``kernel``: ``"auto"`` takes, for bfloat16, the tcgen05 kernel (many queries, head
+    size 64) or the mma.sync kernel (decode form; head size 128) and the FP32-pipe kernel
+    elsewhere; ``"generic"``, ``"mma"`` and ``"tcgen05"`` force one (tests).  ``err``: the device
+    error flag (a bounded wait inside the tcgen05 kernel raises it).
     """
     s = _suffix(q.dtype)
     check_head_dim(d)
@@ -417,11 +426,30 @@ def paged_attention(
         grid_splits = max(1, -(-max_context // split))
         if grid_splits > MAX_ATTN_SPLITS:
             raise ValueError("paged_attention: too many key ranges; use a larger split_size")
-    use_mma = mma_attention_supported(q.dtype, nh, nkv, d, scratch is not None)
+    decode_form = scratch is not None
+    use_tc = tcgen05_attention_supported(q.dtype, nh, nkv, d, decode_form) and q_stride % 8 == 0 and out.shape[-1] % 8 == 0 and max_q_len > 1
+    use_mma = mma_attention_supported(q.dtype, nh, nkv, d, decode_form)
     if kernel == "generic":
-        use_mma = False
-    elif kernel == "mma" and not use_mma:
-        raise ValueError("the tensor-core attention kernel does not take this shape")
+        use_tc = use_mma = False
+    elif kernel == "mma":
+        if not use_mma:
+            raise ValueError("the mma.sync attention kernel does not take this shape")
+        use_tc = False
+    elif kernel == "tcgen05":
+        if not tcgen05_attention_supported(q.dtype, nh, nkv, d, decode_form):
+            raise ValueError("the tcgen05 attention kernel does not take this shape")
+        use_tc = True
+    if use_tc:
+        name = "kvf_paged_attention_tcgen05_bf16"
+        _check(
+            _fn(name)(
+                _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
+                num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
+                int(window), _ptr(err), _stream(),
+            ),
+            name,
+        )  # fmt: skip
+        return
     name = "kvf_paged_attention_mma_bf16" if use_mma else f"kvf_paged_attention_generic_{s}"
     _check(
         _fn(name)(

@@ -145,4 +145,5 @@ class PagedAttention(Mixer):
             q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens,
             ctx.num_seqs, ctx.max_query_len, self.nh, self.nkv, self.d, self.scale,
             window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound, split_size=split,
+            err=self.rt.err,
         )  # fmt: skip

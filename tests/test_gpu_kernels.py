@@ -398,6 +398,68 @@ def test_paged_attention_mma(ops, nh, nkv, d, bs, ctx_lens, q_lens):
     assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
 
 
+# ---- the tcgen05 kernel (bfloat16, head size 64, many queries)
+
+TC_SHAPES = [s for s in MMA_SHAPES if s[2] == 64] + [(4, 4, 64, 16), (16, 1, 64, 32)]
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs", TC_SHAPES)
+@pytest.mark.parametrize(
+    "ctx_lens,q_lens",
+    [([9, 16], [9, 16]), ([12, 30, 5], [4, 7, 5]), ([17, 3, 25, 130], [1, 3, 5, 67]), ([300, 64, 65], [300, 2, 65]), ([700, 129], [450, 128])],
+)
+def test_paged_attention_tcgen05(ops, nh, nkv, d, bs, ctx_lens, q_lens):
+    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx_lens, q_lens, kernel="tcgen05")
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
+
+
+def test_tcgen05_attention_finds_a_far_key_and_respects_the_window(ops):
+    for far in (0, 15, 16, 127, 128, 255, 256, 511, 640):
+
+        def craft(kv, qs, far=far):
+            k, v = kv[0]
+            k.mul_(0.01)
+            k[far, :, 0] = 40.0
+            qs[0][-1, :, 0] = 40.0
+
+        out, ref, kv = run_attention(ops, torch.bfloat16, 8, 2, 64, 16, [700], [5], craft=craft, kernel="tcgen05")
+        v_far = kv[0][1][far].float().repeat_interleave(4, dim=0).reshape(-1)
+        assert torch.allclose(out[-1], v_far, atol=2e-2), far
+    ctx = 300
+    for window in (1, 5, 128, 129, 200):
+        for offset, seen in ((window - 1, True), (window, False)):
+            far = ctx - 1 - offset
+
+            def craft(kv, qs, far=far):
+                k, v = kv[0]
+                k.mul_(0.01)
+                k[far, :, 0] = 40.0
+                qs[0][-1, :, 0] = 40.0
+
+            out, ref, kv = run_attention(ops, torch.bfloat16, 4, 1, 64, 8, [ctx], [9], window=window, craft=craft, kernel="tcgen05")
+            assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2), (window, offset)
+            v_far = kv[0][1][far].float().repeat(4, 1).reshape(-1)
+            assert torch.allclose(out[-1], v_far, atol=2e-2) == seen, (window, offset)
+
+
+def test_tcgen05_attention_rows_do_not_depend_on_the_cut(ops):
+    nh, nkv, d, bs, ctx = 8, 2, 64, 16, 297
+    whole, _, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, [ctx], [ctx], seed=4, kernel="tcgen05")
+    g = torch.Generator().manual_seed(4)
+    k = torch.randn(ctx, nkv, d, generator=g).bfloat16()
+    v = torch.randn(ctx, nkv, d, generator=g).bfloat16()
+    q = torch.randn(ctx, nh, d, generator=g).bfloat16()
+    for ql in (2, 30, 170):
+        kc, vc, tables = paged([(k, v)], nkv, d, bs, torch.bfloat16, seed=ql)
+        out = torch.empty(ql, nh * d, device="cuda", dtype=torch.bfloat16)
+        ops.paged_attention(
+            dev(q[ctx - ql :].reshape(ql, -1)), out, dev(kc), dev(vc), dev(tables), dev(torch.tensor([0, ql], dtype=torch.int32)),
+            dev(torch.tensor([ctx], dtype=torch.int32)), 1, ql, nh, nkv, d, 1.0 / math.sqrt(d), kernel="tcgen05",
+        )  # fmt: skip
+        assert torch.equal(out.float().cpu(), whole[ctx - ql :]), ql
+
+
 @pytest.mark.parametrize("nh,nkv,d,bs", [s for s in MMA_SHAPES if s[0] // s[1] <= 16])
 @pytest.mark.parametrize("split", [64, 128, 256])
 def test_paged_attention_mma_decode_form(ops, nh, nkv, d, bs, split):
