@@ -36,6 +36,7 @@ struct MmaParams {
   const int* ctx_lens;
   float* part_acc;  // split form: [B][nh][max_splits][D]
   float* part_ml;   // split form: [B][nh][max_splits][2]  (m in natural-log units, l)
+  int* tickets;     // split form: [B][nkv] counters, zero between launches; null: a merge kernel follows
   int q_stride, out_stride, bt_stride;
   int nh, nkv, block_size;
   int bs_shift;  // log2(block_size) if it is a power of two, else -1
@@ -347,11 +348,57 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
 }
 
 // ------------------------------------------------------------------ split form
+// The merge of the key ranges of one (sequence, head) by one warp, in range order whichever
+// CTA runs it: lanes over the ranges for the weights, then lanes over the output dims.
+// wgt: ns floats of shared memory of this warp.
+template <int D>
+__device__ __forceinline__ void merge_ranges_warp(const float* part_acc, const float* part_ml, size_t base, int ns,
+                                                  float* wgt, bf16* o, int lane) {
+  float mx = -INFINITY;
+  for (int s = lane; s < ns; s += 32) {
+    const float ms = __ldcg(part_ml + (base + s) * 2);
+    wgt[s] = ms;
+    mx = fmaxf(mx, ms);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float lsum = 0.f;
+  for (int s = lane; s < ns; s += 32) {
+    const float ms = wgt[s];
+    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+    wgt[s] = w;
+    lsum += w * __ldcg(part_ml + (base + s) * 2 + 1);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+  __syncwarp();
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  for (int j = 2 * lane; j < D; j += 64) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < ns; ++s) {
+      const float w = wgt[s];
+      if (w != 0.f) {  // an empty range wrote no sums
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(part_acc + (base + s) * D + j));
+        a0 += w * v.x;
+        a1 += w * v.y;
+      }
+    }
+    *reinterpret_cast<uint32_t*>(o + j) = pack_bf16(a0 * inv, a1 * inv);
+  }
+  __syncwarp();
+}
+
+// ------------------------------------------------------------------ split form
+// Of the keys a range holds, only the newest (position ctx-1, written by the kernel ahead of
+// this one in the stream) can change during a step; lengths and block tables were uploaded
+// before the step.  So a CTA whose range ends before that key starts fetching its tiles before
+// it waits for the kernel ahead.
 template <int D>
 __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaParams p) {
   pdl_launch();
-  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int s_last;
   constexpr int TILE_BYTES = BN * D * 2;
   const uint32_t smem = smem_u32(smem_raw);
 
@@ -359,25 +406,36 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   const int g = p.nh / p.nkv;  // <= 16
   const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
   const int ctx = p.ctx_lens[b];
-  if (q_len <= 0 || ctx <= 0) return;
   int kv_lo = split * p.split_size;
-  if (kv_lo >= ctx) return;  // past the context: the merge never reads this range
+  // dead: no query, or a range past the context (the merge never reads it)
+  const bool live = q_len > 0 && ctx > 0 && kv_lo < ctx;
   const int kv_hi = min(ctx, kv_lo + p.split_size);
   const int key_lo = kv_lo;
   if (p.window > 0) kv_lo = max(kv_lo, (max(0, ctx - p.window) / BN) * BN);
+  const bool empty = kv_lo >= kv_hi;  // wholly before the window
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* bt = p.block_tables + (size_t)b * p.bt_stride;
+  TileLoader<D> loader;
+  loader.init();
+  const int n_tiles = (live && !empty) ? (kv_hi - kv_lo + BN - 1) / BN : 0;
+  int issued = 0;
+  if (n_tiles > 0 && kv_hi < ctx) {
+    for (; issued < 2 && issued < n_tiles; ++issued) {
+      loader.load(p, bt, kvh, kv_hi, kv_lo + issued * BN, smem + issued * 2 * TILE_BYTES, smem + (issued * 2 + 1) * TILE_BYTES);
+      cp_async_commit();
+    }
+  }
+  pdl_wait();
+  if (!live) return;
   const size_t slot0 = ((size_t)b * p.nh + (size_t)kvh * g) * p.max_splits + split;  // + head * max_splits
-  if (kv_lo >= kv_hi) {  // wholly before the window: an empty range, and it says so
+  // ranges of this sequence that write a partial result
+  const int ns = min(min(p.max_splits, p.grid_splits), (ctx + p.split_size - 1) / p.split_size);
+  if (empty) {  // an empty range, and it says so
     for (int h = threadIdx.x; h < g; h += blockDim.x) {
       p.part_ml[(slot0 + (size_t)h * p.max_splits) * 2] = -INFINITY;
       p.part_ml[(slot0 + (size_t)h * p.max_splits) * 2 + 1] = 0.f;
     }
-    return;
-  }
-  const int* bt = p.block_tables + (size_t)b * p.bt_stride;
-  TileLoader<D> loader;
-  loader.init();
-
+  } else {
   // rows are the heads of the group: row r is head r of this kv head; rows >= g are zero
   uint32_t qf[D / 16][4];
 #pragma unroll
@@ -403,19 +461,23 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
   for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
-  loader.load(p, bt, kvh, kv_hi, kv_lo, smem, smem + TILE_BYTES);
-  cp_async_commit();
+  if (issued == 0) {
+    loader.load(p, bt, kvh, kv_hi, kv_lo, smem, smem + TILE_BYTES);
+    cp_async_commit();
+    issued = 1;
+  }
   for (int t = 0; t < n_tiles; ++t) {
     const int st = t & 1;
-    if (t + 1 < n_tiles) {
+    if (issued == t + 1 && t + 1 < n_tiles) {  // its stage was read in iteration t-1
       loader.load(p, bt, kvh, kv_hi, kv_lo + (t + 1) * BN, smem + (st ^ 1) * 2 * TILE_BYTES,
                   smem + ((st ^ 1) * 2 + 1) * TILE_BYTES);
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+      ++issued;
     }
+    if (issued > t + 1)
+      cp_async_wait<1>();
+    else
+      cp_async_wait<0>();
     __syncthreads();
     {
       const uint32_t ks = smem + st * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
@@ -470,6 +532,27 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
       p.part_ml[slot * 2 + 1] = L;
     }
   }
+  }  // a range with keys
+
+  if (p.tickets == nullptr) return;
+  // ---- the CTA that finishes last among the ranges of this (sequence, kv head) merges them
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ticket = p.tickets + (size_t)b * p.nkv + kvh;
+    const int t = atomicAdd(ticket, 1);
+    s_last = (t == ns - 1);
+    if (t == ns - 1) *ticket = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* wgt = reinterpret_cast<float*>(smem_raw) + warp * 1024;  // ns <= 1024
+  bf16* orow = p.out + (size_t)(q_begin + q_len - 1) * p.out_stride;
+  for (int h = warp; h < g; h += NWARPS) {
+    const int head = kvh * g + h;
+    merge_ranges_warp<D>(p.part_acc, p.part_ml, ((size_t)b * p.nh + head) * p.max_splits, ns, wgt, orow + (size_t)head * D, lane);
+  }
 }
 
 // Merge the partial results of the key ranges of one (sequence, head), in range order.
@@ -523,13 +606,14 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
   const int g = p.nh / p.nkv;
   if (p.split_size > 0) {
     auto kern = attn_mma_split_kernel<D>;
-    const size_t need = smem > (size_t)NWARPS * 16 * (D + 2) * 4 ? smem : (size_t)NWARPS * 16 * (D + 2) * 4;
+    size_t need = smem > (size_t)NWARPS * 16 * (D + 2) * 4 ? smem : (size_t)NWARPS * 16 * (D + 2) * 4;
+    if (p.tickets && need < (size_t)NWARPS * 1024 * 4) need = (size_t)NWARPS * 1024 * 4;  // the merge's weights
     if (need > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
       if (e != cudaSuccess) return (int)e;
     }
     int rc = launch(kern, dim3(p.grid_splits, B, p.nkv), dim3(NWARPS * 32), need, st, p);
-    if (rc) return rc;
+    if (rc || p.tickets) return rc;
     return launch(attn_mma_merge_kernel, dim3(p.nh, B), dim3(128), 0, st, (const float*)p.part_acc,
                   (const float*)p.part_ml, p.out, p.qsl, p.ctx_lens, p.nh, D, p.out_stride, p.split_size, p.max_splits);
   }
@@ -547,12 +631,10 @@ int launch_mma(const MmaParams& p, int B, int max_q_len, cudaStream_t st) {
 // bfloat16 only; d in {64, 128}; nh/nkv <= 64 (tile form) or <= 16 (split form, chosen by
 // split_size > 0: one query per sequence, split_size a multiple of 64).  Anything else is
 // refused with cudaErrorInvalidValue: the caller falls back to the generic kernel.
-KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* kcache, const void* vcache,
-                                         const int* block_tables, const int* qsl, const int* ctx_lens, int B,
-                                         int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
-                                         int nkv, int d, int block_size, float scale, int window, int split_size,
-                                         int max_splits, int grid_splits, float* part_acc, float* part_ml,
-                                         cudaStream_t st) {
+static int run_mma(const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables,
+                   const int* qsl, const int* ctx_lens, int B, int max_q_len, int q_stride, int out_stride,
+                   int bt_stride, int nh, int nkv, int d, int block_size, float scale, int window, int split_size,
+                   int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || block_size <= 0) return (int)cudaErrorInvalidValue;
   const int g = nh / nkv;
@@ -561,7 +643,7 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
   MmaParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
   p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens;
-  p.part_acc = part_acc; p.part_ml = part_ml;
+  p.part_acc = part_acc; p.part_ml = part_ml; p.tickets = split_size > 0 ? tickets : nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.bs_shift = -1;
@@ -575,4 +657,28 @@ KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* k
       return (int)cudaErrorInvalidValue;
   }
   return d == 64 ? launch_mma<64>(p, B, max_q_len, st) : launch_mma<128>(p, B, max_q_len, st);
+}
+
+KVF_API int kvf_paged_attention_mma_bf16(const void* q, void* out, const void* kcache, const void* vcache,
+                                         const int* block_tables, const int* qsl, const int* ctx_lens, int B,
+                                         int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
+                                         int nkv, int d, int block_size, float scale, int window, int split_size,
+                                         int max_splits, int grid_splits, float* part_acc, float* part_ml,
+                                         cudaStream_t st) {
+  return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, max_q_len, q_stride, out_stride, bt_stride, nh,
+                 nkv, d, block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, nullptr, st);
+}
+
+// The split form in one launch: `tickets` holds B * nkv counters that are zero before the first
+// launch (each launch leaves them zero); the CTA that finishes last among the ranges of a
+// (sequence, kv head) merges them.  Launches that share `tickets` must not overlap.
+KVF_API int kvf_paged_attention_decode_fused_bf16(const void* q, void* out, const void* kcache, const void* vcache,
+                                                  const int* block_tables, const int* qsl, const int* ctx_lens, int B,
+                                                  int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
+                                                  int block_size, float scale, int window, int split_size,
+                                                  int max_splits, int grid_splits, float* part_acc, float* part_ml,
+                                                  int* tickets, cudaStream_t st) {
+  if (!tickets || split_size <= 0) return (int)cudaErrorInvalidValue;
+  return run_mma(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 1, q_stride, out_stride, bt_stride, nh, nkv, d,
+                 block_size, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets, st);
 }

@@ -27,6 +27,7 @@ _SIGNATURES = {
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiifipp",
+    "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
@@ -376,7 +377,7 @@ def paged_attention(
     scale: float,
     window: int = 0,
     q_stride: int | None = None,
-    scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+    scratch: tuple[torch.Tensor, ...] | None = None,
     max_context: int | None = None,
     split_size: int = 256,
     kernel: str = "auto",
@@ -408,11 +409,16 @@ def paged_attention(
     if q_stride is None:
         q_stride = q.shape[-1]
     bt_stride = block_tables.shape[-1] if block_tables.dim() == 2 else block_tables.numel() // max(1, num_seqs)
-    split, max_splits, grid_splits, pa, pm = 0, 0, 0, None, None
+    split, max_splits, grid_splits, pa, pm, tickets = 0, 0, 0, None, None, None
     if scratch is not None:
-        pa, pm = scratch
+        pa, pm = scratch[:2]
         _need(pa, torch.float32, "scratch acc")
         _need(pm, torch.float32, "scratch ml")
+        if len(scratch) > 2:
+            tickets = scratch[2]
+            _need(tickets, torch.int32, "scratch tickets")
+            if tickets.numel() < num_seqs * nkv:
+                raise ValueError("paged_attention: too few tickets (one per sequence and kv head)")
         if max_q_len != 1:
             raise ValueError("the decode form needs one query per sequence")
         if split_size <= 0 or split_size % 64:
@@ -446,6 +452,17 @@ def paged_attention(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
                 int(window), _ptr(err), _stream(),
+            ),
+            name,
+        )  # fmt: skip
+        return
+    if use_mma and tickets is not None:
+        name = "kvf_paged_attention_decode_fused_bf16"
+        _check(
+            _fn(name)(
+                _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
+                num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _stream(),
             ),
             name,
         )  # fmt: skip

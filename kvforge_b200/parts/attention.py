@@ -84,6 +84,8 @@ class PagedAttention(Mixer):
         super().bind(weights, rt)
         self.w_qkv = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0).contiguous()
         self.w_o = weights["o_proj.weight"].contiguous()
+        # counters of finished key ranges per (sequence, kv head) for the decode form: zero between launches
+        self._tickets = torch.zeros(max(1, rt.max_seqs) * self.nkv, dtype=torch.int32, device=rt.device)
         if self.position_spec is not None and self.position is None:
             self.position = build_part("position", self.position_spec)
             self.position.bind({}, rt)
@@ -101,7 +103,11 @@ class PagedAttention(Mixer):
         sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)
         acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
         ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
-        return (acc, ml), bound, split
+        if self._tickets.numel() < sa[0] * self.nkv:
+            if rt.capturing or rt.graphs_captured:
+                raise RuntimeError("the attention tickets would have to grow after or during graph capture")
+            self._tickets = torch.zeros(sa[0] * self.nkv, dtype=torch.int32, device=rt.device)
+        return (acc, ml, self._tickets), bound, split
 
     def forward(self, ctx, x: torch.Tensor, cache) -> torch.Tensor:
         rt = self.rt

@@ -284,11 +284,17 @@ def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode
         bound = max(ctx_lens)
         sa, sm = ops.attention_scratch_shapes(len(ctx_lens), nh, d, bound, split)
         scratch = (torch.full(sa, float("nan"), device="cuda"), torch.full(sm, float("nan"), device="cuda"))
-    ops.paged_attention(
-        dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
-        len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
-        split_size=split, kernel=kernel,
-    )  # fmt: skip
+        if decode_form == "fused":  # one launch: the last CTA of a (sequence, kv head) merges
+            scratch += (torch.zeros(len(ctx_lens) * nkv, dtype=torch.int32, device="cuda"),)
+    for _ in range(2 if decode_form == "fused" else 1):  # the second launch finds the tickets as the first left them
+        out.fill_(float("nan"))
+        ops.paged_attention(
+            dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
+            len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
+            split_size=split, kernel=kernel,
+        )  # fmt: skip
+    if decode_form == "fused":
+        assert int(scratch[2].abs().sum()) == 0
     refs = []
     for (k, v), qq, c, ql in zip(kv, qs, ctx_lens, q_lens):
         full_q = torch.zeros(c, nh, d, dtype=dtype)
@@ -462,14 +468,15 @@ def test_tcgen05_attention_rows_do_not_depend_on_the_cut(ops):
 
 @pytest.mark.parametrize("nh,nkv,d,bs", [s for s in MMA_SHAPES if s[0] // s[1] <= 16])
 @pytest.mark.parametrize("split", [64, 128, 256])
-def test_paged_attention_mma_decode_form(ops, nh, nkv, d, bs, split):
+@pytest.mark.parametrize("form", [True, "fused"])
+def test_paged_attention_mma_decode_form(ops, nh, nkv, d, bs, split, form):
     ctx = [700, 1, 256, 257, 33, 64, 65]
-    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form=True, kernel="mma", split=split)
+    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form=form, kernel="mma", split=split)
     assert not torch.isnan(out).any()
     assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("decode_form", [False, True])
+@pytest.mark.parametrize("decode_form", [False, True, "fused"])
 def test_mma_attention_finds_a_far_key_and_respects_the_window(ops, decode_form):
     for far in (0, 15, 16, 63, 64, 255, 256, 511, 640):
 
