@@ -17,6 +17,7 @@
 //
 // Cache layout per layer: K and V each [num_blocks][nkv][block_size][D].
 #include "common.cuh"
+#include "attention_merge.cuh"
 
 using namespace kvf;
 
@@ -348,47 +349,6 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_tile_kernel(const MmaPar
 }
 
 // ------------------------------------------------------------------ split form
-// The merge of the key ranges of one (sequence, head) by one warp, in range order whichever
-// CTA runs it: lanes over the ranges for the weights, then lanes over the output dims.
-// wgt: ns floats of shared memory of this warp.
-template <int D>
-__device__ __forceinline__ void merge_ranges_warp(const float* part_acc, const float* part_ml, size_t base, int ns,
-                                                  float* wgt, bf16* o, int lane) {
-  float mx = -INFINITY;
-  for (int s = lane; s < ns; s += 32) {
-    const float ms = __ldcg(part_ml + (base + s) * 2);
-    wgt[s] = ms;
-    mx = fmaxf(mx, ms);
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  float lsum = 0.f;
-  for (int s = lane; s < ns; s += 32) {
-    const float ms = wgt[s];
-    const float w = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
-    wgt[s] = w;
-    lsum += w * __ldcg(part_ml + (base + s) * 2 + 1);
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
-  __syncwarp();
-  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-  for (int j = 2 * lane; j < D; j += 64) {
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < ns; ++s) {
-      const float w = wgt[s];
-      if (w != 0.f) {  // an empty range wrote no sums
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(part_acc + (base + s) * D + j));
-        a0 += w * v.x;
-        a1 += w * v.y;
-      }
-    }
-    *reinterpret_cast<uint32_t*>(o + j) = pack_bf16(a0 * inv, a1 * inv);
-  }
-  __syncwarp();
-}
-
 // ------------------------------------------------------------------ split form
 // Of the keys a range holds, only the newest (position ctx-1, written by the kernel ahead of
 // this one in the stream) can change during a step; lengths and block tables were uploaded
@@ -536,17 +496,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_mma_split_kernel(const MmaPa
 
   if (p.tickets == nullptr) return;
   // ---- the CTA that finishes last among the ranges of this (sequence, kv head) merges them
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int* ticket = p.tickets + (size_t)b * p.nkv + kvh;
-    const int t = atomicAdd(ticket, 1);
-    s_last = (t == ns - 1);
-    if (t == ns - 1) *ticket = 0;  // ready for the next launch
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
+  if (!last_of_ranges(p.tickets + (size_t)b * p.nkv + kvh, ns, &s_last)) return;
   float* wgt = reinterpret_cast<float*>(smem_raw) + warp * 1024;  // ns <= 1024
   bf16* orow = p.out + (size_t)(q_begin + q_len - 1) * p.out_stride;
   for (int h = warp; h < g; h += NWARPS) {

@@ -27,6 +27,10 @@ from ..cache.state_slots import StateSlotPool
 from .runtime import Runtime, StepContext
 
 
+# graphs for shorter contexts than this are not told apart
+MIN_GRAPH_CONTEXT = 1024
+
+
 @dataclass
 class BatchItem:
     """``logits``: ``"last"``, ``"all"``, ``"none"`` (continuous.py:24-32) or a list of places
@@ -116,8 +120,9 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs)
         self.pdl = bool(pdl)  # programmatic dependent launch between the kernels of a step
         self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
-        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
-        self.graph_kernels: dict[int, int] = {}  # kernels of this library inside each captured graph
+        # keyed by (batch bucket, longest context the graph reaches)
+        self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.graph_kernels: dict[tuple[int, int], int] = {}  # kernels of this library inside each captured graph
         self.num_kernel_launches = 0  # kernels of this library launched by steps, replays included
         self.num_graph_kernels = 0  # those of them that ran inside replayed graphs
         self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
@@ -300,19 +305,24 @@ class ModelRunner:
             host[o["slots"] + g * bucket : o["slots"] + (g + 1) * bucket] = -1
         n, _, r, max_q, max_ctx = self._fill(items, lay)
         self._upload(lay.total)
-        entry = self._graphs.get(bucket)
+        # A graph fixes its grids, so it is made for contexts up to a bound: the next power of two
+        # (kernels whose grid follows the longest context then launch at most twice what they need).
+        reach = min(self.max_model_len, max(MIN_GRAPH_CONTEXT, 1 << max(0, max_ctx - 1).bit_length()))
+        key = (bucket, reach)
+        entry = self._graphs.get(key)
         if entry is None:
-            entry = self._capture(bucket, lay)
+            entry = self._capture(key, lay)
         graph, logits = entry
         graph.replay()
-        self.num_kernel_launches += self.graph_kernels[bucket]
-        self.num_graph_kernels += self.graph_kernels[bucket]
+        self.num_kernel_launches += self.graph_kernels[key]
+        self.num_graph_kernels += self.graph_kernels[key]
         self.num_forward_passes += 1
         self.num_tokens_processed += n
         return logits[:r]
 
-    def _capture(self, bucket: int, lay: _Layout):
-        ctx = self._context(lay, bucket, bucket, bucket, 1, self.max_model_len, bound=self.max_model_len)
+    def _capture(self, key: tuple[int, int], lay: _Layout):
+        bucket, reach = key
+        ctx = self._context(lay, bucket, bucket, bucket, 1, reach, bound=reach)
         # one eager run first: sizes every buffer and loads every kernel outside the capture
         self.model.forward(ctx)
         torch.cuda.synchronize()
@@ -324,7 +334,7 @@ class ModelRunner:
                 logits = self.model.forward(ctx)
         finally:
             self.rt.capturing = False
-        self.graph_kernels[bucket] = ops.launch_count - before
+        self.graph_kernels[key] = ops.launch_count - before
         self.rt.graphs_captured = True
-        self._graphs[bucket] = (graph, logits)
-        return self._graphs[bucket]
+        self._graphs[key] = (graph, logits)
+        return self._graphs[key]

@@ -30,7 +30,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # name -> (sources, extra flags).  One shared library per entry.
 LIBRARIES: dict[str, tuple[list[str], list[str]]] = {
     "core": (
-        ["elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny_bf16.cu", "gemm_tcgen05_bf16.cu", "sampling.cu"],
+        ["elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "attention_mma.cu", "attention_decode_tma.cu", "attention_tcgen05.cu", "gemm_skinny_bf16.cu", "gemm_tcgen05_bf16.cu", "sampling.cu"],
         [],
     ),
     # one entry point that allocates nothing (csrc/kvforge_noalloc.h); a library of its own, so

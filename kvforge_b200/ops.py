@@ -28,6 +28,7 @@ _SIGNATURES = {
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiifipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
+    "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppp",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
@@ -328,11 +329,13 @@ MAX_ATTN_SPLITS = 1024  # ranges per (sequence, head) the merge kernel takes
 
 
 def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
-    """Keys per range of the decode form: smaller ranges when few (sequence, kv head) pairs
-    would leave SMs idle, larger ones when the context is so long that there would be more
-    than ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of it, whatever the batch."""
+    """Keys per range of the decode form.  A range is a CTA, and a CTA has a fixed cost of a few
+    microseconds (its chain of dependent reads, its share of the merge), so ranges are long:
+    shorter only when few (sequence, kv head) pairs would leave SMs idle, longer when the
+    context is so long that there would be more than ``MAX_ATTN_SPLITS`` of them.  Ranges start
+    at multiples of it, whatever the batch."""
     pairs = num_seqs * nkv
-    split = 512 if pairs >= 256 else 256 if pairs >= 32 else 128
+    split = 1024 if pairs >= 256 else 512 if pairs >= 32 else 256
     while -(-max_context // split) > MAX_ATTN_SPLITS:
         split *= 2
     return split
@@ -359,6 +362,14 @@ def tcgen05_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, d
     """Whether the tcgen05 kernel (``csrc/attention_tcgen05.cu``) takes this shape: many queries
     (not the decode form), bfloat16, head size 64."""
     return dtype == torch.bfloat16 and d == 64 and not decode_form and nh // max(nkv, 1) <= 128
+
+
+def tma_decode_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, block_size: int, num_blocks: int) -> bool:
+    """Whether the TMA decode kernel (``csrc/attention_decode_tma.cu``) takes this shape."""
+    return (
+        dtype == torch.bfloat16 and d in (64, 128) and nh // max(nkv, 1) <= 8 and block_size % 16 == 0
+        and num_blocks * nkv * block_size < 2**31 - 16
+    )  # fmt: skip
 
 
 def paged_attention(
@@ -437,6 +448,8 @@ def paged_attention(
     use_mma = mma_attention_supported(q.dtype, nh, nkv, d, decode_form)
     if kernel == "generic":
         use_tc = use_mma = False
+    elif kernel == "tma":
+        pass
     elif kernel == "mma":
         if not use_mma:
             raise ValueError("the mma.sync attention kernel does not take this shape")
@@ -452,6 +465,20 @@ def paged_attention(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
                 int(window), _ptr(err), _stream(),
+            ),
+            name,
+        )  # fmt: skip
+        return
+    use_tma = tickets is not None and tma_decode_supported(q.dtype, nh, nkv, d, block_size, kcache.shape[0])
+    if kernel == "tma" and not use_tma:
+        raise ValueError("the TMA decode kernel does not take this shape (or no tickets were given)")
+    if use_tma and kernel in ("auto", "tma"):
+        name = "kvf_paged_attention_decode_tma_bf16"
+        _check(
+            _fn(name)(
+                _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
+                num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]), float(scale),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), _stream(),
             ),
             name,
         )  # fmt: skip

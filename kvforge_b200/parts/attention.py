@@ -96,7 +96,10 @@ class PagedAttention(Mixer):
 
     def _scratch(self, ctx):
         rt = self.rt
+        # buffers are made for the longest context the engine takes; the grid follows the longest
+        # context of this step (of this graph, when the step is captured)
         bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
+        reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
         split = ops.attention_split_size(ctx.num_seqs, self.nkv, bound)
         # made for the smallest range size, so that one buffer serves every batch size
         smallest = ops.attention_split_size(1, 1, bound)
@@ -107,7 +110,7 @@ class PagedAttention(Mixer):
             if rt.capturing or rt.graphs_captured:
                 raise RuntimeError("the attention tickets would have to grow after or during graph capture")
             self._tickets = torch.zeros(sa[0] * self.nkv, dtype=torch.int32, device=rt.device)
-        return (acc, ml, self._tickets), bound, split
+        return (acc, ml, self._tickets), reach, split
 
     def forward(self, ctx, x: torch.Tensor, cache) -> torch.Tensor:
         rt = self.rt

@@ -28,6 +28,17 @@ def ops():
     return o
 
 
+_ERR = None
+
+
+def err_flag():
+    """The device error flag that kernels with bounded waits raise."""
+    global _ERR
+    if _ERR is None:
+        _ERR = torch.zeros(4, dtype=torch.int32, device="cuda")
+    return _ERR
+
+
 def dev(t, dtype=None):
     return t.to(device="cuda", dtype=dtype or t.dtype).contiguous()
 
@@ -246,15 +257,15 @@ def test_norm_and_rope_sum_the_slices_of_a_split_product(ops, dtype):
 # ------------------------------------------------------------------ attention
 
 
-def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5):
+def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5, junk=(1e4, -1e4)):
     """Scatter per-sequence [ctx, nkv, d] keys/values into shuffled pages; stale pages hold junk."""
     rng = random.Random(seed)
     need = [-(-k.shape[0] // bs) for k, _ in kv_per_seq]
     nb = sum(need) + extra_blocks
     order = list(range(nb))
     rng.shuffle(order)
-    kc = torch.full((nb, nkv, bs, d), 1e4).to(dtype)  # junk that would show if it were read
-    vc = torch.full((nb, nkv, bs, d), -1e4).to(dtype)
+    kc = torch.full((nb, nkv, bs, d), junk[0]).to(dtype)  # junk that would show if it were read
+    vc = torch.full((nb, nkv, bs, d), junk[1]).to(dtype)
     width = max(need)
     tables = torch.zeros(len(kv_per_seq), width, dtype=torch.int32)
     for s, (k, v) in enumerate(kv_per_seq):
@@ -268,13 +279,13 @@ def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5):
     return kc, vc, tables
 
 
-def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256):
+def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256, junk=(1e4, -1e4)):
     g = torch.Generator().manual_seed(seed)
     kv = [(torch.randn(c, nkv, d, generator=g).to(dtype), torch.randn(c, nkv, d, generator=g).to(dtype)) for c in ctx_lens]
     qs = [torch.randn(ql, nh, d, generator=g).to(dtype) for ql in q_lens]
     if craft:
         craft(kv, qs)
-    kc, vc, tables = paged(kv, nkv, d, bs, dtype, seed)
+    kc, vc, tables = paged(kv, nkv, d, bs, dtype, seed, junk=junk)
     q = torch.cat(qs, 0).reshape(-1, nh * d)
     qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
     out = torch.full((q.shape[0], nh * d), float("nan"), device="cuda", dtype=dtype)
@@ -291,7 +302,7 @@ def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode
         ops.paged_attention(
             dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
             len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
-            split_size=split, kernel=kernel,
+            split_size=split, kernel=kernel, err=err_flag(),
         )  # fmt: skip
     if decode_form == "fused":
         assert int(scratch[2].abs().sum()) == 0
@@ -474,6 +485,79 @@ def test_paged_attention_mma_decode_form(ops, nh, nkv, d, bs, split, form):
     out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form=form, kernel="mma", split=split)
     assert not torch.isnan(out).any()
     assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
+
+
+# ---- the TMA decode kernel (bfloat16, head size 64 or 128, up to 8 heads per kv head, pages of 16 n tokens)
+
+TMA_SHAPES = [(8, 2, 64, 16), (32, 8, 64, 16), (3, 1, 64, 32), (24, 8, 128, 32), (5, 5, 64, 48), (14, 2, 128, 16), (8, 1, 64, 16)]
+
+
+@pytest.mark.parametrize("nh,nkv,d,bs", TMA_SHAPES)
+@pytest.mark.parametrize("split", [64, 128, 256, 1024])
+def test_paged_attention_tma_decode(ops, nh, nkv, d, bs, split):
+    ctx = [700, 1, 256, 257, 33, 64, 65, 1500, 16, 17]
+    err_flag().zero_()
+    # what lies past a context inside its last page must not reach the result, whatever it is
+    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form="fused", kernel="tma", split=split, junk=(float("nan"), float("nan")))
+    assert int(err_flag().sum()) == 0
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
+
+
+def test_tma_decode_finds_a_far_key_and_respects_the_window(ops):
+    err_flag().zero_()
+    for far in (0, 15, 16, 63, 64, 255, 256, 511, 640, 699):
+
+        def craft(kv, qs, far=far):
+            k, v = kv[0]
+            k.mul_(0.01)
+            k[far, :, 0] = 40.0
+            qs[0][-1, :, 0] = 40.0
+
+        out, ref, kv = run_attention(ops, torch.bfloat16, 8, 2, 64, 16, [700], [1], decode_form="fused", craft=craft, kernel="tma", split=128)
+        v_far = kv[0][1][far].float().repeat_interleave(4, dim=0).reshape(-1)
+        assert torch.allclose(out[-1], v_far, atol=2e-2), far
+    ctx = 300
+    for window in (1, 5, 16, 17, 64, 65, 100):
+        for offset, seen in ((window - 1, True), (window, False)):
+            far = ctx - 1 - offset
+
+            def craft(kv, qs, far=far):
+                k, v = kv[0]
+                k.mul_(0.01)
+                k[far, :, 0] = 40.0
+                qs[0][-1, :, 0] = 40.0
+
+            out, ref, kv = run_attention(ops, torch.bfloat16, 4, 1, 64, 16, [ctx], [1], window=window, decode_form="fused", craft=craft, kernel="tma", split=64)
+            assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2), (window, offset)
+            v_far = kv[0][1][far].float().repeat(4, 1).reshape(-1)
+            assert torch.allclose(out[-1], v_far, atol=2e-2) == seen, (window, offset)
+    assert int(err_flag().sum()) == 0
+
+
+def test_tma_decode_reads_zeros_for_pages_that_were_given_back(ops):
+    """A table entry of -1 (a page the window has passed) is read as zeros, not as page -1."""
+    nh, nkv, d, bs, ctx, window = 8, 2, 64, 16, 200, 40
+    g = torch.Generator().manual_seed(3)
+    k = torch.randn(ctx, nkv, d, generator=g).bfloat16()
+    v = torch.randn(ctx, nkv, d, generator=g).bfloat16()
+    q = torch.randn(1, nh, d, generator=g).bfloat16()
+    kc, vc, tables = paged([(k, v)], nkv, d, bs, torch.bfloat16, seed=1)
+    tables[0, : (ctx - window) // bs] = -1
+    out = torch.empty(1, nh * d, device="cuda", dtype=torch.bfloat16)
+    sa, sm = ops.attention_scratch_shapes(1, nh, d, ctx, 64)
+    scratch = (torch.empty(sa, device="cuda"), torch.empty(sm, device="cuda"), torch.zeros(nkv, dtype=torch.int32, device="cuda"))
+    err_flag().zero_()
+    ops.paged_attention(
+        dev(q.reshape(1, -1)), out, dev(kc), dev(vc), dev(tables), dev(torch.tensor([0, 1], dtype=torch.int32)),
+        dev(torch.tensor([ctx], dtype=torch.int32)), 1, 1, nh, nkv, d, 1.0 / math.sqrt(d), window=window, scratch=scratch,
+        max_context=ctx, split_size=64, kernel="tma", err=err_flag(),
+    )  # fmt: skip
+    full_q = torch.zeros(ctx, nh, d)
+    full_q[-1] = q[0].float()
+    ref = causal_attention(full_q, k.float(), v.float(), 1.0 / math.sqrt(d), window)[-1].reshape(-1)
+    assert int(err_flag().sum()) == 0
+    assert torch.allclose(out[0].float().cpu(), ref, rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("decode_form", [False, True, "fused"])
