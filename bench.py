@@ -382,7 +382,7 @@ def run_kernel_only(args, cfg) -> dict:
         cl = torch.full((b,), ctx, device=dev, dtype=torch.int32)
         split = args.split or ops.attention_split_size(b, nkv, ctx)
         sa, sm = ops.attention_scratch_shapes(b, nh, d, ctx, split)
-        scratch = (torch.empty(sa, device=dev), torch.empty(sm, device=dev))
+        scratch = (torch.empty(sa, device=dev), torch.empty(sm, device=dev), torch.zeros(b * nkv, dtype=torch.int32, device=dev))
         sec = _graph_time(
             lambda i: ops.paged_attention(q, out, kcs[i % copies], vcs[i % copies], tables, qsl, cl, b, 1, nh, nkv, d,
                                           d**-0.5, scratch=scratch, max_context=ctx, split_size=split),
@@ -391,6 +391,27 @@ def run_kernel_only(args, cfg) -> dict:
         nbytes = b * ctx * 2 * nkv * d * 2
         return {"only": "attention", "batch": b, "context": ctx, "split": split, "us": round(sec * 1e6, 2),
                 "GB/s": round(nbytes / sec / 1e9, 1), "frac_of_hbm_peak": round(nbytes / sec / 1e9 / pk["hbm_gbs"], 3)}  # fmt: skip
+    if args.only == "attention-prefill":
+        # one prompt of `context` tokens, all of them queries (the kernel of prompts and mixed batches)
+        ctx = args.context
+        nblk = -(-ctx // bs)
+        kc = torch.randn(nblk, nkv, bs, d, device=dev).bfloat16()
+        vc = torch.randn(nblk, nkv, bs, d, device=dev).bfloat16()
+        tables = torch.randperm(nblk, device=dev).int().view(1, -1).contiguous()
+        q = torch.randn(ctx, nh * d, device=dev).bfloat16()
+        out = torch.empty(ctx, nh * d, device=dev, dtype=torch.bfloat16)
+        qsl = torch.tensor([0, ctx], device=dev, dtype=torch.int32)
+        cl = torch.tensor([ctx], device=dev, dtype=torch.int32)
+        err = torch.zeros(4, device=dev, dtype=torch.int32)
+        sec = _graph_time(
+            lambda i: ops.paged_attention(q, out, kc, vc, tables, qsl, cl, 1, ctx, nh, nkv, d, d**-0.5, err=err),
+            calls=max(2, args.steps), reps=3,
+        )  # fmt: skip
+        if int(err.sum()):
+            raise SystemExit("the attention kernel raised its error flag")
+        flops = 4 * nh * d * ctx * (ctx + 1) // 2
+        return {"only": "attention-prefill", "tokens": ctx, "us": round(sec * 1e6, 2), "TFLOP/s": round(flops / sec / 1e12, 1),
+                "frac_of_bf16_peak": round(flops / sec / 1e12 / pk["bf16_tflops"], 3)}  # fmt: skip
     shapes = {"qkv": ((nh + 2 * nkv) * d, cfg.hidden_size), "o": (cfg.hidden_size, nh * d),
               "gate_up": (2 * cfg.intermediate_size, cfg.hidden_size), "down": (cfg.hidden_size, cfg.intermediate_size),
               "lm_head": (cfg.vocab_size, cfg.hidden_size)}  # fmt: skip
@@ -412,7 +433,7 @@ def run_only(args) -> dict:
     from kvforge_b200 import PRESETS
 
     cfg = PRESETS["llama-3.2-1b"]
-    if args.only in ("attention", "gemm"):
+    if args.only in ("attention", "attention-prefill", "gemm"):
         return run_kernel_only(args, cfg)
     ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
     core = make_core(cfg, max(args.batch, 1), PREFILL_TOKENS, ctx_cap, cuda_graphs=not args.no_graphs)
@@ -439,7 +460,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "attention", "gemm"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm"], help="run one part alone and print a short line (for profiling)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")

@@ -113,8 +113,11 @@ __device__ __forceinline__ uint32_t unit_off(int row, int c) {
   return (uint32_t)((c >> 3) * 2048 + row * 128 + (((c & 7) ^ (row & 7)) << 4));
 }
 
-template <int D> struct Shape {
-  static constexpr int STAGES = D == 64 ? 4 : 2;       // units in flight per warp
+// ST: units in flight per warp.  Four of 4 KB (head size 64) keep a warp's whole share of a
+// short range in flight; two leave room for seven CTAs on an SM, which suits grids of
+// several waves.
+template <int D, int ST> struct Shape {
+  static constexpr int STAGES = ST;
   static constexpr uint32_t TENSOR_BYTES = UNIT * D * 2;  // K (or V) of one unit
   static constexpr uint32_t STAGE_BYTES = 2 * TENSOR_BYTES;
   static constexpr uint32_t WARP_BYTES = STAGES * STAGE_BYTES;
@@ -123,11 +126,11 @@ template <int D> struct Shape {
   static constexpr uint32_t SMEM_BYTES = FLAG_OFFSET + 16;
 };
 
-template <int D>
+template <int D, int ST>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const DecParams p) {
-  using S = Shape<D>;
+  using S = Shape<D, ST>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];  // nothing static beside it: it starts the CTA's window
   pdl_launch();
@@ -383,11 +386,11 @@ int cache_map(CUtensorMap* map, const void* ptr, long long rows, int d) {
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int D>
+template <int D, int ST>
 int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int B, cudaStream_t st) {
-  auto kern = attn_decode_tma_kernel<D>;
-  size_t smem = Shape<D>::SMEM_BYTES;
-  static_assert(Shape<D>::FLAG_OFFSET >= NWARPS * 1024 * 4, "the range merge's weights lie in the tile area");
+  auto kern = attn_decode_tma_kernel<D, ST>;
+  size_t smem = Shape<D, ST>::SMEM_BYTES;
+  static_assert(Shape<D, ST>::FLAG_OFFSET >= NWARPS * 1024 * 4, "the range merge's weights lie in the tile area");
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   return launch(kern, dim3(p.grid_splits, B, p.nkv), dim3(NWARPS * 32), smem, st, mk, mv, p);
@@ -429,5 +432,14 @@ KVF_API int kvf_paged_attention_decode_tma_bf16(const void* q, void* out, const 
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.total_rows = (int)rows;
   p.scale_log2 = scale * 1.4426950408889634f;
-  return d == 64 ? launch_dec<64>(mk, mv, p, B, st) : launch_dec<128>(mk, mv, p, B, st);
+  // more CTAs than fit at four stages: two stages, so that they run in fewer waves
+  const long long ctas = (long long)p.grid_splits * B * nkv;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  if (d == 64) return ctas > 3ll * sms ? launch_dec<64, 2>(mk, mv, p, B, st) : launch_dec<64, 4>(mk, mv, p, B, st);
+  return launch_dec<128, 2>(mk, mv, p, B, st);
 }

@@ -330,12 +330,13 @@ MAX_ATTN_SPLITS = 1024  # ranges per (sequence, head) the merge kernel takes
 
 def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
     """Keys per range of the decode form.  A range is a CTA, and a CTA has a fixed cost of a few
-    microseconds (its chain of dependent reads, its share of the merge), so ranges are long:
-    shorter only when few (sequence, kv head) pairs would leave SMs idle, longer when the
-    context is so long that there would be more than ``MAX_ATTN_SPLITS`` of them.  Ranges start
+    microseconds (its chain of dependent reads, its share of the merge), so ranges are not
+    short: 256 keys, 512 with many (sequence, kv head) pairs (measured inside the decode step at
+    1, 8 and 64 sequences), and more when the context is so long that there would be more than
+    ``MAX_ATTN_SPLITS`` of them.  Ranges start
     at multiples of it, whatever the batch."""
     pairs = num_seqs * nkv
-    split = 1024 if pairs >= 256 else 512 if pairs >= 32 else 256
+    split = 512 if pairs >= 256 else 256
     while -(-max_context // split) > MAX_ATTN_SPLITS:
         split *= 2
     return split
