@@ -147,6 +147,51 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
+// The same for many rows: a warp per row keeps the row in registers (VPT float4 per lane, H <=
+// 128 * VPT), so a row costs one trip to memory with all its loads in flight and no block-wide
+// barrier.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(128) add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                                               const float* __restrict__ weight, T* __restrict__ out,
+                                                               const int* __restrict__ rows, int n_rows, int H, float eps) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const int src = rows ? rows[r] : r;
+  float* h = resid + (size_t)src * H;
+  const T* dl = delta ? delta + (size_t)src * H : nullptr;
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = (k * 32 + lane) * 4;
+    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < H) {
+      v[k] = *reinterpret_cast<const float4*>(h + i);
+      if (dl) {
+        const float4 d = Vec4<T>::load(dl + i);
+        v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  const bool write_back = dl != nullptr && rows == nullptr;
+  T* o = out + (size_t)r * H;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = (k * 32 + lane) * 4;
+    if (i < H) {
+      if (write_back) *reinterpret_cast<float4*>(h + i) = v[k];
+      const float4 w = *reinterpret_cast<const float4*>(weight + i);
+      Vec4<T>::store(o + i, make_float4(v[k].x * inv * w.x, v[k].y * inv * w.y, v[k].z * inv * w.z, v[k].w * inv * w.w));
+    }
+  }
+}
+
 // resid[r,:] += float(delta[r,:]) without a norm (used after the last layer when the
 // final norm reads gathered rows).
 template <typename T>
@@ -333,9 +378,16 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restri
                                       T* __restrict__ vcache, int nh, int nkv, int d, int block_size,
                                       long long num_slots, int* __restrict__ err) {
   pdl_launch();
-  pdl_wait();
+  extern __shared__ __align__(16) float cs_sn[];  // cos then sin of this token's d/2 angles
   const int n = blockIdx.x;
   const int half = d >> 1, cph = half >> 3;  // chunks of 8 pairs per head
+  {
+    // the angles depend on the position alone: once per token, not once per head
+    const float pos0 = (float)positions[n];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos0 * inv_freq[j], &cs_sn[half + j], &cs_sn[j]);
+  }
+  pdl_wait();
+  __syncthreads();
   const int stride = (nh + 2 * nkv) * d;
   T* row = qkv ? qkv + (size_t)n * stride : nullptr;
   const float* prow = partials ? partials + (size_t)n * stride : nullptr;
@@ -359,7 +411,6 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restri
     slot = -1;
   }
   const size_t cache_row = slot >= 0 ? ((size_t)(slot / block_size) * nkv) * block_size + (slot % block_size) : 0;
-  const float pos = (float)positions[n];
   T* qdst = q_out ? q_out + (size_t)n * nh * d : row;
   // rotated heads (q then k): one item = 8 pairs of one head
   const int rot_items = (nh + nkv) * cph;
@@ -370,8 +421,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restri
     load8(head * d + half + j0, x2);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      float sn, cs;
-      sincosf(pos * inv_freq[j0 + e], &sn, &cs);
+      const float cs = cs_sn[j0 + e], sn = cs_sn[half + j0 + e];
       y1[e] = x1[e] * cs - x2[e] * sn;
       y2[e] = x2[e] * cs + x1[e] * sn;
     }
@@ -493,6 +543,14 @@ static inline int norm_threads(int H) {
                                     long long split_stride, const float* weight, void* out,              \
                                     const int* rows, int n_rows, int H, float eps, cudaStream_t st) {    \
     if (n_rows <= 0) return 0;                                                                           \
+    if ((H & 3) == 0 && H <= 4096 && !partials && n_rows >= 64) {                                        \
+      const unsigned blocks = (unsigned)((n_rows + 3) / 4);                                              \
+      if (H <= 2048)                                                                                     \
+        return launch(add_rmsnorm_warp_kernel<T, 16>, dim3(blocks), dim3(128), 0, st, resid,              \
+                      (const T*)delta, weight, (T*)out, rows, n_rows, H, eps);                           \
+      return launch(add_rmsnorm_warp_kernel<T, 32>, dim3(blocks), dim3(128), 0, st, resid,                \
+                    (const T*)delta, weight, (T*)out, rows, n_rows, H, eps);                             \
+    }                                                                                                    \
     if ((H & 3) == 0 && H <= 32768 && (split_stride & 3) == 0) {                                         \
       int t = 32;                                                                                        \
       while (t < 1024 && t * 4 < H) t <<= 1;                                                             \
@@ -523,7 +581,7 @@ static inline int norm_threads(int H) {
     if (rot < 0 || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;                              \
     if (!qkv && !(partials && q_out)) return (int)cudaErrorInvalidValue;                                 \
     if (rot == d && (d & 15) == 0 && N > 16 && (split_stride & 3) == 0) {                                \
-      return launch(rope_cache_vec_kernel<T>, dim3(N), dim3(256), 0, st, (T*)qkv, partials, nsplit,      \
+      return launch(rope_cache_vec_kernel<T>, dim3(N), dim3(256), (size_t)d * sizeof(float), st, (T*)qkv, partials, nsplit, \
                     (size_t)split_stride, (T*)q_out, positions, inv_freq, slots, (T*)kcache, (T*)vcache, \
                     nh, nkv, d, block_size, num_slots, err);                                             \
     }                                                                                                    \
