@@ -543,7 +543,7 @@ static inline int norm_threads(int H) {
                                     long long split_stride, const float* weight, void* out,              \
                                     const int* rows, int n_rows, int H, float eps, cudaStream_t st) {    \
     if (n_rows <= 0) return 0;                                                                           \
-    if ((H & 3) == 0 && H <= 4096 && !partials && n_rows >= 64) {                                        \
+    if ((H & 3) == 0 && H <= 4096 && !partials && n_rows >= 1024) {                                       \
       const unsigned blocks = (unsigned)((n_rows + 3) / 4);                                              \
       if (H <= 2048)                                                                                     \
         return launch(add_rmsnorm_warp_kernel<T, 16>, dim3(blocks), dim3(128), 0, st, resid,              \
