@@ -27,6 +27,9 @@
 //
 // Every mbarrier wait is bounded; if one runs out the kernel raises bit 4 of the error flag and
 // winds down.  No cluster launch, no multicast.
+#include <cuda.h>
+#include <string.h>
+
 #include "common.cuh"
 
 using namespace kvf;
@@ -36,7 +39,9 @@ namespace {
 constexpr int D = 64;
 constexpr int BM = 128;  // rows per CTA
 constexpr int BN = 64;   // keys per tile
-constexpr int THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8;                    // two groups of four: even and odd key tiles
+constexpr int LOADER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr int KV_STAGES = 4;
 constexpr int LOOKAHEAD = 2;                 // tiles in flight behind the one being handed over
 constexpr uint32_t Q_BYTES = BM * 128;       // [128 rows][64] bfloat16
@@ -58,6 +63,8 @@ struct TcAttnParams {
   int nh, nkv, block_size, bs_shift;
   int window;
   float scale_log2;
+  int use_tma;     // pages are multiples of 16 keys: K and V tiles come as tensor-map boxes of [16][64]
+  int total_rows;  // rows of the cache seen as [rows][64]: a box from this row reads zeros
 };
 
 __device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -66,6 +73,15 @@ __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void bar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, int* err) {
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
@@ -214,7 +230,8 @@ __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)
   return sum0 + sum1;
 }
 
-__global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnParams p) {
+__global__ void __launch_bounds__(THREADS, 2)
+attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // no slack for rounding up (two CTAs have to fit an SM): the base must be 1024-byte aligned
   // as declared, else the kernel refuses (bit 8 of the error flag) rather than compute garbage
@@ -235,12 +252,14 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnPa
     return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.y, kvh = blockIdx.z;
+  // grid (kv heads, sequences, row blocks): CTAs start in the order of their index with x
+  // fastest, so all heads of the longest walk start first, then the next longest, ...
+  const int b = blockIdx.y, kvh = blockIdx.x;
   const int g = p.nh / p.nkv;
   const int tq = BM / g;
   const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
   const int ctx = p.ctx_lens[b];
-  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tq;  // the longest walks first
+  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * tq;  // the longest walks first
   const bool live = q_len > 0 && ctx > 0 && q0 < q_len;  // uniform over the CTA
   const int n_tok = live ? min(tq, q_len - q0) : 0;
   const int p_first = ctx - q_len + q0;
@@ -261,7 +280,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnPa
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -269,11 +288,12 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnPa
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;  // S buffers: columns 0..63, 64..127; O: 128..191
+  // S of even and odd tiles: columns 0..63, 64..127; their O accumulators: 128..191, 192..255
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;
 
   pdl_wait();
 
-  if (live && warp == 4) {
+  if (live && warp == LOADER_WARP) {
     // ---- loader: Q, then a K and a V tile per stage; 16-byte chunks into the swizzled layout
     const bf16* qg = p.q + (size_t)(q_begin + q0) * p.q_stride + (size_t)(kvh * g) * D;
     for (int idx = lane; idx < BM * 8; idx += 32) {
@@ -317,31 +337,88 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnPa
         cpa16(vs + sw128(key, c), p.vcache + at, valid);
       }
     };
+    if (p.use_tma) {
+      // A tile is four pages' worth of keys: eight boxes requested by one lane, which the copy
+      // engine lands in the swizzled layout and counts on the stage's barrier.  Only a tile that
+      // reaches past the context inside a live page (whatever lies there must not be read: the
+      // last tile of the sequence, at most) goes the slow way, which zero-fills by key.
+      cpa_commit();  // Q
+      bool ok = true, q_handed = false;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int s = t % KV_STAGES;
+        if (t >= KV_STAGES) ok = __all_sync(0xffffffffu, bar_wait(kv_empty0 + 8 * s, ((t / KV_STAGES) - 1) & 1, p.err));
+        if (!ok) break;
+        const int t0 = kv_lo + t * BN;
+        const bool ragged = t0 + BN > ctx && (ctx & 15) != 0;
+        if (!ragged) {
+          // lane j brings page j of the tile (its K box and its V box)
+          const uint32_t bar = kv_full0 + 8 * s, ks = kv_s + s * 2 * KV_BYTES, vs = ks + KV_BYTES;
+          if (lane == 0) bar_expect_tx(bar, 2 * KV_BYTES);
+          __syncwarp();
+          if (lane < BN / 16) {
+            const int key0 = t0 + 16 * lane;
+            int blk = -1, off = 0;
+            if (key0 < ctx) {
+              if (p.bs_shift >= 0) {
+                blk = bt[key0 >> p.bs_shift];
+                off = key0 & (p.block_size - 1);
+              } else {
+                blk = bt[key0 / p.block_size];
+                off = key0 % p.block_size;
+              }
+            }
+            const int row = blk >= 0 ? (blk * p.nkv + kvh) * p.block_size + off : p.total_rows;
+            tma_load_2d(ks + lane * 2048, &map_k, 0, row, bar);
+            tma_load_2d(vs + lane * 2048, &map_v, 0, row, bar);
+          }
+        } else {
+          issue_tile(t);
+          cpa_commit();
+          cpa_wait<0>();
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (!q_handed) bar_arrive(q_full);
+            bar_arrive(kv_full0 + 8 * s);
+          }
+          q_handed = true;
+        }
+        if (!q_handed && (t + 1 >= KV_STAGES || t + 1 == n_tiles)) {
+          // the first tiles are on their way: now wait for Q
+          cpa_wait<0>();
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) bar_arrive(q_full);
+          q_handed = true;
+        }
+      }
+    } else {
     // groups: {Q, tile 0}, {tile 1}, ...; an empty group stands for a tile past the end
 #pragma unroll
-    for (int t = 0; t < LOOKAHEAD; ++t) {
-      if (t < n_tiles) issue_tile(t);
-      cpa_commit();
-    }
-    bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      // tile t (and, the first time, Q) has landed: hand it to the tensor core
-      cpa_wait<LOOKAHEAD - 1>();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (t == 0) bar_arrive(q_full);
-        bar_arrive(kv_full0 + 8 * (t % KV_STAGES));
+      for (int t = 0; t < LOOKAHEAD; ++t) {
+        if (t < n_tiles) issue_tile(t);
+        cpa_commit();
       }
-      const int nx = t + LOOKAHEAD;
-      if (nx < n_tiles) {
-        if (nx >= KV_STAGES) ok = bar_wait(kv_empty0 + 8 * (nx % KV_STAGES), ((nx / KV_STAGES) - 1) & 1, p.err);
-        if (ok) issue_tile(nx);
+      bool ok = true;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        // tile t (and, the first time, Q) has landed: hand it to the tensor core
+        cpa_wait<LOOKAHEAD - 1>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (t == 0) bar_arrive(q_full);
+          bar_arrive(kv_full0 + 8 * (t % KV_STAGES));
+        }
+        const int nx = t + LOOKAHEAD;
+        if (nx < n_tiles) {
+          if (nx >= KV_STAGES) ok = bar_wait(kv_empty0 + 8 * (nx % KV_STAGES), ((nx / KV_STAGES) - 1) & 1, p.err);
+          if (ok) issue_tile(nx);
+        }
+        cpa_commit();
       }
-      cpa_commit();
+      cpa_wait<0>();
     }
-    cpa_wait<0>();
-  } else if (live && warp == 5) {
+  } else if (live && warp == MMA_WARP) {
     if (lane == 0) {
       // ---- MMA issuer: S(t+1) goes out before P(t) V(t), so the softmax never waits for it
       constexpr uint32_t id_s = idesc(BN, 0), id_o = idesc(D, 1);
@@ -375,80 +452,100 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnPa
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           // A: 16 keys of P = 32 bytes along the row; B: 16 keys of V = 16 rows of 128 bytes
-          umma(tmem_o, pd + 2 * kk, sdesc(vs + kk * 16 * 128), id_o, (t > 0 || kk > 0) ? 1u : 0u);
+          umma(tmem_o + (uint32_t)((t & 1) * D), pd + 2 * kk, sdesc(vs + kk * 16 * 128), id_o, (t > 1 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(pv_done0 + 8 * (t & 1));         // O holds tiles 0..t; P buffer t&1 may be rewritten
+        umma_commit(pv_done0 + 8 * (t & 1));         // O[t&1] holds tiles t&1, .., t; P buffer t&1 may be rewritten
         umma_commit(kv_empty0 + 8 * (t % KV_STAGES));  // and the stage may be refilled
       }
     }
-  } else if (live && warp < 4) {
-    // ---- softmax and output: thread r owns row r
-    const int r = threadIdx.x;
+  } else if (live && warp < SOFTMAX_WARPS) {
+    // ---- softmax and output: thread r of each group owns row r; group 0 takes the even key tiles,
+    // group 1 the odd ones, each with its S buffer, P buffer, O accumulator, maximum and sum
+    const int grp = warp >> 2;
+    const int r = threadIdx.x & 127;
     const int tok = r / g, hh = r - tok * g;
     const bool valid = tok < n_tok;
     const int pos = valid ? p_first + tok : -1;
     const int lo = p.window > 0 ? pos - p.window + 1 : 0;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t my_s = tmem_s + lane_addr + (uint32_t)(grp * BN), my_o = tmem_o + lane_addr + (uint32_t)(grp * D);
+    const uint32_t s_bar = s_full0 + 8 * grp, p_bar = p_full0 + 8 * grp, pv_bar = pv_done0 + 8 * grp;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
+    int i = 0;  // index among this group's tiles
+    for (int t = grp; t < n_tiles && ok; t += 2, ++i) {
       const int key0 = kv_lo + t * BN;
       // (tcgen05.ld and st are warp-wide: the lanes of a warp leave the loop together)
-      ok = __all_sync(0xffffffffu, bar_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1, p.err));
+      ok = __all_sync(0xffffffffu, bar_wait(s_bar, i & 1, p.err));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t va[32], vb[32];
-      tmem_ld32(tmem_s + lane_addr + (uint32_t)((t & 1) * BN), va);
-      tmem_ld32(tmem_s + lane_addr + (uint32_t)((t & 1) * BN + 32), vb);
-      // the P buffer of this tile was the A operand of P(t-2) V
-      if (t >= 2) ok = bar_wait(pv_done0 + 8 * (t & 1), ((t >> 1) - 1) & 1, p.err);
+      tmem_ld32(my_s, va);
+      tmem_ld32(my_s + 32, vb);
+      // the group's last P V is done: its P buffer may be rewritten and its O may be rescaled
+      if (i >= 1) ok = bar_wait(pv_bar, (i - 1) & 1, p.err);
       tmem_wait(va);
       tmem_wait(vb);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (key0 + BN - 1 > pos) || (key0 < lo);
-      const uint32_t p_row = p_s + (uint32_t)(t & 1) * P_BYTES + (uint32_t)r * 128u;
+      const uint32_t p_row = p_s + (uint32_t)grp * P_BYTES + (uint32_t)r * 128u;
       float corr, sum;
       if (__any_sync(0xffffffffu, need_mask))
         sum = softmax_tile<true>(va, vb, m_ref, corr, p.scale_log2, max(lo, key0) - key0, min(pos, key0 + BN - 1) - key0, p_row, r & 7);
       else
         sum = softmax_tile<false>(va, vb, m_ref, corr, p.scale_log2, 0, BN - 1, p_row, r & 7);
       l = l * corr + sum;
-      if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-        // O *= corr, once every earlier P V has been added to it
-        ok = __all_sync(0xffffffffu, bar_wait(pv_done0 + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, p.err));
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32(tmem_o + lane_addr + (uint32_t)c0, v);
+          tmem_ld32(my_o + (uint32_t)c0, v);
           tmem_wait(v);
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
-          tmem_st32(tmem_o + lane_addr + (uint32_t)c0, v);
+          tmem_st32(my_o + (uint32_t)c0, v);
         }
         tmem_wait_st();
       }
       fence_async_smem();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      bar_arrive(p_full0 + 8 * (t & 1));
+      bar_arrive(p_bar);
     }
-    if (ok) ok = __all_sync(0xffffffffu, bar_wait(pv_done0 + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.err));
-    if (ok) {
+    if (ok && i > 0) ok = __all_sync(0xffffffffu, bar_wait(pv_bar, (i - 1) & 1, p.err));
+    // ---- the two groups' results become one: group 1 hands its maximum and sum over (through its P
+    // buffer, which its last P V has read), group 0 reads both accumulators
+    float2* xch = reinterpret_cast<float2*>(smem_raw + (p_s + P_BYTES - base));
+    if (grp == 1) xch[r] = make_float2(ok ? m_ref : -INFINITY, ok ? l : 0.f);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+    if (grp == 0 && ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float2 other = xch[r];
+      const float m_all = fmaxf(m_ref, other.x);
+      const float w0 = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - m_all), w1 = (other.x == -INFINITY) ? 0.f : ex2(other.x - m_all);
+      const float l_all = l * w0 + other.y * w1;
+      const float f0 = l_all > 0.f ? w0 / l_all : 0.f, f1 = l_all > 0.f ? w1 / l_all : 0.f;
+      const bool use1 = __any_sync(0xffffffffu, other.y > 0.f);  // group 1 saw a tile (else its accumulator was never written)
       bf16* dst = p.out + (size_t)(q_begin + q0 + (valid ? tok : 0)) * p.out_stride + (size_t)(kvh * g + hh) * D;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_addr + (uint32_t)c0, v);
+        uint32_t v[32], u[32];
+        tmem_ld32(my_o + (uint32_t)c0, v);
         tmem_wait(v);
+        if (use1) {
+          tmem_ld32(my_o + (uint32_t)(D + c0), u);
+          tmem_wait(u);
+        }
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
           float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j + e]) * inv;
+          for (int e = 0; e < 8; ++e) {
+            f[e] = __uint_as_float(v[j + e]) * f0;
+            if (use1 && f1 != 0.f) f[e] += __uint_as_float(u[j + e]) * f1;
+          }
           if (valid)
             *reinterpret_cast<uint4*>(dst + c0 + j) = make_uint4(pk(f[0], f[1]), pk(f[2], f[3]), pk(f[4], f[5]), pk(f[6], f[7]));
         }
@@ -457,23 +554,58 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tcgen05_kernel(const TcAttnPa
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
 }  // namespace
 
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// The cache as [rows][64] bfloat16; boxes of [16][64], 128-byte swizzle, zeros past the end.
+int cache_map(CUtensorMap* map, const void* ptr, long long rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)D, 16u};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
 // bfloat16, head size 64, nh/nkv <= 128; out rows and q rows 16-byte aligned.  err: device flag.
+// kcache/vcache: [num_blocks][nkv][block_size][64].
 KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                              const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                              int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
-                                             int nkv, int d, int block_size, float scale, int window, int* err,
-                                             cudaStream_t st) {
+                                             int nkv, int d, int block_size, long long num_blocks, float scale,
+                                             int window, int* err, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (d != D || nkv <= 0 || nh % nkv != 0 || nh / nkv > BM || block_size <= 0) return (int)cudaErrorInvalidValue;
+  if (d != D || nkv <= 0 || nh % nkv != 0 || nh / nkv > BM || block_size <= 0 || num_blocks <= 0) return (int)cudaErrorInvalidValue;
   if ((q_stride & 7) || (out_stride & 7) || ((((uintptr_t)q) | ((uintptr_t)out)) & 15)) return (int)cudaErrorInvalidValue;
-  if ((unsigned)B > 65535u || (unsigned)nkv > 65535u) return (int)cudaErrorInvalidValue;
+  if ((unsigned)B > 65535u || (max_q_len + (BM / (nh / nkv)) - 1) / (BM / (nh / nkv)) > 65535) return (int)cudaErrorInvalidValue;
   TcAttnParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
   p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens; p.err = err;
@@ -483,9 +615,19 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
   for (int sh = 0; sh < 31; ++sh)
     if ((1 << sh) == block_size) p.bs_shift = sh;
   p.scale_log2 = scale * 1.4426950408889634f;
+  // pages of a multiple of 16 keys come in as tensor-map boxes; other page sizes key by key
+  const long long rows = num_blocks * nkv * block_size;
+  p.use_tma = (block_size % 16 == 0) && rows < (1ll << 31) - 16 && ((((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) == 0;
+  p.total_rows = (int)(p.use_tma ? rows : 0);
+  CUtensorMap mk, mv;
+  memset(&mk, 0, sizeof(mk));
+  memset(&mv, 0, sizeof(mv));
+  if (p.use_tma) {
+    if (cache_map(&mk, kcache, rows) || cache_map(&mv, vcache, rows)) p.use_tma = 0;
+  }
   const int g = nh / nkv, tq = BM / g;
   constexpr size_t smem = Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES + 128;
   cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return launch(attn_tcgen05_kernel, dim3((max_q_len + tq - 1) / tq, B, nkv), dim3(THREADS), smem, st, p);
+  return launch(attn_tcgen05_kernel, dim3(nkv, B, (max_q_len + tq - 1) / tq), dim3(THREADS), smem, st, mk, mv, p);
 }

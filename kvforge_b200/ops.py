@@ -26,7 +26,7 @@ _SIGNATURES = {
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
-    "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiifipp",
+    "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppp",
     "kvf_paged_attention_decode_rope_tma_bf16": "pilppp" "pppppp" "iiiiiii" "l" "f" "iiii" "ppppp",
@@ -465,8 +465,8 @@ def paged_attention(
         _check(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
-                num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, float(scale),
-                int(window), _ptr(err), _stream(),
+                num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]),
+                float(scale), int(window), _ptr(err), _stream(),
             ),
             name,
         )  # fmt: skip
