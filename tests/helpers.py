@@ -26,6 +26,16 @@ TINY = {
         ),
         block_size=4,
     ),
+    # head size 64 with four heads per kv head and pages of 16: in bfloat16 the tcgen05 kernel takes
+    # its prompts and mixed batches, the TMA kernel its decode steps
+    "tiny-d": dict(
+        cfg=ModelConfig(
+            vocab_size=211, hidden_size=96, num_layers=2, num_heads=8, num_kv_heads=2, head_dim=64,
+            intermediate_size=160, rms_norm_eps=2e-5, rope_theta=10000.0, tie_word_embeddings=True,
+            max_position_embeddings=512,
+        ),
+        block_size=16,
+    ),
 }  # fmt: skip
 
 
