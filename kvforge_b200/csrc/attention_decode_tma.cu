@@ -27,6 +27,13 @@
 // the new position turns the key, writes key and value to the cache, and puts them into its
 // tile in shared memory (the copy of that page may have read the slot before or after).
 //
+// With CLUSTER the CTAs of the ranges of one (sequence, kv head) are one thread-block cluster
+// (up to 16), and the merge goes through distributed shared memory: every CTA leaves its partial
+// result in its own shared memory, a cluster barrier, then CTA r merges a slice of the outputs by
+// reading all the others', in range order, and writes it out; a second barrier keeps every CTA's
+// shared memory alive until it has been read.  No partial results in global memory, no fence, no
+// ticket.  CTAs of ranges past the context stay for the barriers.
+//
 // Every mbarrier wait is bounded; if one runs out the kernel raises bit 4 of the error flag.
 #include <cuda.h>
 
@@ -123,6 +130,22 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// the address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t in_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+// every thread of every CTA of the cluster
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Byte offset of the 16-byte chunk c (0 .. D/8-1) of key `row` (0..15) inside a unit: one box of
 // [16][64] (2 KB, 128-byte swizzle) per 64 dims.
 __device__ __forceinline__ uint32_t unit_off(int row, int c) {
@@ -139,11 +162,15 @@ template <int D, int ST> struct Shape {
   static constexpr uint32_t WARP_BYTES = STAGES * STAGE_BYTES;
   static constexpr uint32_t TILES_BYTES = NWARPS * WARP_BYTES;
   static constexpr uint32_t FLAG_OFFSET = TILES_BYTES + NWARPS * STAGES * 8;  // one int: "this CTA merges"
+  // CLUSTER: this CTA's partial result [8 heads][D + 2] floats, after the four warps' [4][8][D + 2]
+  static constexpr uint32_t RED_BYTES = NWARPS * 8 * (D + 2) * 4;
+  static constexpr uint32_t CPART_OFFSET = RED_BYTES;
+  static_assert(CPART_OFFSET + 8 * (D + 2) * 4 <= TILES_BYTES, "the partial results lie in the tile area");
   static constexpr uint32_t ANGLE_OFFSET = FLAG_OFFSET + 16;  // ROPE: cos then sin of the token's D/2 angles
   static constexpr uint32_t SMEM_BYTES = ANGLE_OFFSET + NWARPS * D * 4;  // a copy per warp: no block-wide barrier
 };
 
-template <int D, int ST, bool ROPE>
+template <int D, int ST, bool ROPE, bool CLUSTER>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const DecParams p) {
@@ -161,7 +188,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // dead: no query, a range past the context (the merge never reads it), or shared memory that
   // does not start where the swizzle needs it (refused: bit 8 of the error flag)
   const bool aligned = (base & 1023u) == 0;
-  const bool live = q_len > 0 && ctx > 0 && range_lo < ctx && aligned;
+  const bool seq_live = q_len > 0 && ctx > 0;  // the same for all ranges of a sequence: for a whole cluster
+  const bool live = seq_live && range_lo < ctx && aligned;
   const int kv_hi = min(ctx, range_lo + p.split_size);
   const int first_seen = max(range_lo, p.window > 0 ? ctx - p.window : 0);  // first key this range may show
   const int kv_lo = (first_seen / UNIT) * UNIT;
@@ -171,7 +199,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int* bt = p.block_tables + (size_t)b * p.bt_stride;
   // A CTA with nothing to do leaves at once and frees its place for one that has; the first CTA
   // of the grid stays to the wait, so that the grid is never done before the kernel ahead of it.
-  if (!live && aligned && (blockIdx.x | blockIdx.y | blockIdx.z) != 0) return;
+  // With CLUSTER a CTA leaves early only if its whole cluster does (a sequence without query or context).
+  if ((CLUSTER ? !seq_live : (!live && aligned)) && (blockIdx.x | blockIdx.y | blockIdx.z) != 0) return;
 
   const uint32_t tiles = base + warp * S::WARP_BYTES;
   const uint32_t bars = base + S::TILES_BYTES + warp * STAGES * 8;
@@ -212,14 +241,20 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
   pdl_wait();
   if (!aligned && threadIdx.x == 0 && p.err) atomicOr(p.err, 8);
-  if (!live) return;
+  if (CLUSTER ? !seq_live : !live) return;
   const size_t slot0 = ((size_t)b * p.nh + (size_t)kvh * g) * p.max_splits + split;  // + head * max_splits
   const int ns = min(min(p.max_splits, p.grid_splits), (ctx + p.split_size - 1) / p.split_size);
 
-  if (empty) {
+  float* cpart = reinterpret_cast<float*>(smem_raw + S::CPART_OFFSET);  // CLUSTER: [8][D + 2]
+  if (empty || !live) {  // (not live: only with CLUSTER) nothing to add, and it says so
     for (int h = threadIdx.x; h < g; h += blockDim.x) {
-      p.part_ml[(slot0 + (size_t)h * p.max_splits) * 2] = -INFINITY;
-      p.part_ml[(slot0 + (size_t)h * p.max_splits) * 2 + 1] = 0.f;
+      if (CLUSTER) {
+        cpart[h * (D + 2) + D] = -INFINITY;
+        cpart[h * (D + 2) + D + 1] = 0.f;
+      } else {
+        p.part_ml[(slot0 + (size_t)h * p.max_splits) * 2] = -INFINITY;
+        p.part_ml[(slot0 + (size_t)h * p.max_splits) * 2 + 1] = 0.f;
+      }
     }
   } else {
     for (; issued < STAGES && issued < n_mine; ++issued) issue(issued);
@@ -426,6 +461,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         acc += f * red[((size_t)w * 8 + r) * LD + dcol];
         L += f * red[((size_t)w * 8 + r) * LD + D + 1];
       }
+      if (CLUSTER) {
+        cpart[r * LD + dcol] = acc;
+        if (dcol == 0) {
+          cpart[r * LD + D] = M;  // log2 units
+          cpart[r * LD + D + 1] = L;
+        }
+        continue;
+      }
       if (ns == 1) {  // the only range of its sequence: this is the result
         p.out[(size_t)(q_begin + q_len - 1) * p.out_stride + (size_t)(kvh * g + r) * D + dcol] =
             __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
@@ -438,7 +481,37 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         p.part_ml[slot * 2 + 1] = L;
       }
     }
-    if (ns == 1) return;
+    if (!CLUSTER && ns == 1) return;
+  }
+
+  if (CLUSTER) {
+    // ---- every CTA of the cluster merges a slice of the g * D outputs over the ns ranges, in range order
+    cluster_barrier();
+    uint32_t nranks;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
+    const int per = (g * D + (int)nranks - 1) / (int)nranks;
+    // (the cluster spans x: the rank is blockIdx.x)
+    for (int local = threadIdx.x; local < per; local += blockDim.x) {
+      const int idx = (int)blockIdx.x * per + local;
+      if (idx >= g * D) break;
+      const int r = idx / D, dcol = idx - r * D;
+      const uint32_t mine = sm32(cpart + r * (D + 2));
+      float M = -INFINITY;
+      for (int s2 = 0; s2 < ns; ++s2) M = fmaxf(M, ld_cluster(in_cta(mine + D * 4, (uint32_t)s2)));
+      float acc = 0.f, L = 0.f;
+      for (int s2 = 0; s2 < ns; ++s2) {
+        const uint32_t theirs = in_cta(mine, (uint32_t)s2);
+        const float ms = ld_cluster(theirs + D * 4);
+        if (ms == -INFINITY) continue;  // an empty range left no sums
+        const float w = ex2(ms - M);
+        acc += w * ld_cluster(theirs + dcol * 4);
+        L += w * ld_cluster(theirs + (D + 1) * 4);
+      }
+      p.out[(size_t)(q_begin + q_len - 1) * p.out_stride + (size_t)(kvh * g + r) * D + dcol] =
+          __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    cluster_barrier();  // nobody leaves while its shared memory may still be read
+    return;
   }
 
   // ---- the CTA that finishes last among the ranges of this (sequence, kv head) merges them
@@ -484,13 +557,39 @@ int cache_map(CUtensorMap* map, const void* ptr, long long rows, int d) {
 }
 
 template <int D, int ST, bool ROPE>
-int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int B, cudaStream_t st) {
-  auto kern = attn_decode_tma_kernel<D, ST, ROPE>;
+int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int B, bool cluster, cudaStream_t st) {
   size_t smem = Shape<D, ST>::SMEM_BYTES;
   static_assert(Shape<D, ST>::FLAG_OFFSET >= NWARPS * 1024 * 4, "the range merge's weights lie in the tile area");
+  const dim3 grid(p.grid_splits, B, p.nkv);
+  if (cluster) {
+    // the ranges of a (sequence, kv head) as one cluster; more than 8 CTAs need the non-portable size
+    auto kern = attn_decode_tma_kernel<D, ST, ROPE, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess && p.grid_splits > 8) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(NWARPS * 32);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = p.grid_splits;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = g_pdl_enabled ? 2 : 1;
+      e = cudaLaunchKernelEx(&cfg, kern, mk, mv, p);
+      if (e == cudaSuccess) return 0;
+    }
+    (void)cudaGetLastError();  // a cluster this size does not fit here: the ticket form does the same work
+  }
+  auto kern = attn_decode_tma_kernel<D, ST, ROPE, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return launch(kern, dim3(p.grid_splits, B, p.nkv), dim3(NWARPS * 32), smem, st, mk, mv, p);
+  return launch(kern, grid, dim3(NWARPS * 32), smem, st, mk, mv, p);
 }
 
 }  // namespace
@@ -510,7 +609,7 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
             const int* block_tables, const int* qsl, const int* ctx_lens, int B, int q_stride, int out_stride,
             int bt_stride, int nh, int nkv, int d, int block_size, long long num_blocks, float scale, int window,
             int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, int* err,
-            cudaStream_t st) {
+            int cluster, cudaStream_t st) {
   if (B <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh / nkv > 8) return (int)cudaErrorInvalidValue;
   if (block_size <= 0 || block_size % UNIT != 0 || num_blocks <= 0) return (int)cudaErrorInvalidValue;
@@ -551,12 +650,13 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
       sms = 148;
   }
   const bool small = ctas <= 3ll * sms;
+  const bool cl = cluster != 0 && p.grid_splits <= 16;
   if (rope) {
-    if (d == 64) return small ? launch_dec<64, 4, true>(mk, mv, p, B, st) : launch_dec<64, 2, true>(mk, mv, p, B, st);
-    return launch_dec<128, 2, true>(mk, mv, p, B, st);
+    if (d == 64) return small ? launch_dec<64, 4, true>(mk, mv, p, B, cl, st) : launch_dec<64, 2, true>(mk, mv, p, B, cl, st);
+    return launch_dec<128, 2, true>(mk, mv, p, B, cl, st);
   }
-  if (d == 64) return small ? launch_dec<64, 4, false>(mk, mv, p, B, st) : launch_dec<64, 2, false>(mk, mv, p, B, st);
-  return launch_dec<128, 2, false>(mk, mv, p, B, st);
+  if (d == 64) return small ? launch_dec<64, 4, false>(mk, mv, p, B, cl, st) : launch_dec<64, 2, false>(mk, mv, p, B, cl, st);
+  return launch_dec<128, 2, false>(mk, mv, p, B, cl, st);
 }
 
 }  // namespace
@@ -565,16 +665,18 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
 // aligned.  Takes d in {64, 128}, nh/nkv <= 8, block_size a multiple of 16, fewer than 2^31 - 16
 // cache rows; refuses anything else with cudaErrorInvalidValue (the caller has other kernels).
 // `tickets`: B * nkv counters, zero before the first launch and left zero by every launch;
-// launches that share them must not overlap.
+// launches that share them must not overlap.  cluster != 0: with at most 16 ranges, merge them
+// through a thread-block cluster's shared memory instead (scratch and tickets are then unused,
+// unless such a cluster cannot be launched here).
 KVF_API int kvf_paged_attention_decode_tma_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                                 const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                                 int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
                                                 int block_size, long long num_blocks, float scale, int window,
                                                 int split_size, int max_splits, int grid_splits, float* part_acc,
-                                                float* part_ml, int* tickets, int* err, cudaStream_t st) {
+                                                float* part_ml, int* tickets, int* err, int cluster, cudaStream_t st) {
   return run_dec(q, RopeSource(), out, kcache, vcache, block_tables, qsl, ctx_lens, B, q_stride, out_stride, bt_stride, nh,
                  nkv, d, block_size, num_blocks, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml,
-                 tickets, err, st);
+                 tickets, err, cluster, st);
 }
 
 // The same with the rotation and the cache write of the new token folded in.  qkv_part: float
@@ -589,12 +691,12 @@ KVF_API int kvf_paged_attention_decode_rope_tma_bf16(const float* qkv_part, int 
                                                      int bt_stride, int nh, int nkv, int d, int block_size,
                                                      long long num_blocks, float scale, int window, int split_size,
                                                      int max_splits, int grid_splits, float* part_acc, float* part_ml,
-                                                     int* tickets, int* err, cudaStream_t st) {
+                                                     int* tickets, int* err, int cluster, cudaStream_t st) {
   RopeSource rs;
   rs.qkv_part = qkv_part; rs.part_stride = part_stride; rs.nsplit = nsplit;
   rs.positions = positions; rs.inv_freq = inv_freq; rs.slots = slots;
   if (!qkv_part) return (int)cudaErrorInvalidValue;
   return run_dec(nullptr, rs, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 0, out_stride, bt_stride, nh, nkv, d,
                  block_size, num_blocks, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets,
-                 err, st);
+                 err, cluster, st);
 }

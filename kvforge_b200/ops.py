@@ -28,8 +28,8 @@ _SIGNATURES = {
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
-    "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppp",
-    "kvf_paged_attention_decode_rope_tma_bf16": "pilppp" "pppppp" "iiiiiii" "l" "f" "iiii" "ppppp",
+    "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppip",
+    "kvf_paged_attention_decode_rope_tma_bf16": "pilppp" "pppppp" "iiiiiii" "l" "f" "iiii" "ppppip",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
@@ -395,6 +395,7 @@ def paged_attention(
     split_size: int = 256,
     kernel: str = "auto",
     err: torch.Tensor | None = None,
+    cluster: bool = True,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
@@ -404,8 +405,10 @@ def paged_attention(
     runs: key ranges of ``split_size`` in parallel, then a merge; ``max_context`` bounds the
     contexts.  ``kernel``: ``"auto"`` takes, for bfloat16, the tcgen05 kernel (many queries, head
     size 64) or the mma.sync kernel (decode form; head size 128) and the FP32-pipe kernel
-    elsewhere; ``"generic"``, ``"mma"`` and ``"tcgen05"`` force one (tests).  ``err``: the device
-    error flag (a bounded wait inside the tcgen05 kernel raises it).
+    elsewhere; ``"generic"``, ``"mma"``, ``"tma"`` and ``"tcgen05"`` force one (tests).  ``err``: the
+    device error flag (a bounded wait inside a kernel raises it).  ``cluster``: the TMA decode kernel
+    merges up to 16 key ranges through a thread-block cluster's shared memory (else through the
+    scratch and the tickets).
     """
     s = _suffix(q.dtype)
     check_head_dim(d)
@@ -480,7 +483,7 @@ def paged_attention(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]), float(scale),
-                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), _stream(),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(cluster), _stream(),
             ),
             name,
         )  # fmt: skip
@@ -535,6 +538,7 @@ def paged_attention_decode_rope(
     window: int = 0,
     split_size: int = 256,
     err: torch.Tensor | None = None,
+    cluster: bool = True,
 ) -> None:
     """A decode step's rotation, cache write and attention in one kernel (bfloat16 caches).
 
@@ -580,7 +584,7 @@ def paged_attention_decode_rope(
             _ptr(qkv.t), qkv.nsplit, qkv.split_stride, _ptr(positions), _ptr(inv_freq), _ptr(slots),
             _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
             num_seqs, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]), float(scale),
-            int(window), split_size, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), _stream(),
+            int(window), split_size, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(cluster), _stream(),
         ),
         name,
     )  # fmt: skip

@@ -18,6 +18,12 @@ from .. import ops
 from .base import CacheNeed, Mixer, PartSpec, WeightDecl, build_part, register_mixer
 
 
+# Decode attention merges its key ranges through a thread-block cluster's shared memory only with
+# this few (sequence, kv head) pairs: measured inside the decode step it gains 2 % at one sequence
+# and loses at 8 and 64, where the ranges past the context (a captured graph's grid covers twice
+# the context at most) hold their places until their cluster is done.
+CLUSTER_MERGE_MAX_PAIRS = 16
+
 _PART_ROWS = ops.SKINNY_MAX_M * ops.SKINNY_MAX_SPLIT  # rows of the largest set of split-K slices
 
 
@@ -140,6 +146,7 @@ class PagedAttention(Mixer):
                     part, ctx.positions, self.inv_freq, slots, out, cache.k, cache.v, ctx.block_tables[cache.group],
                     ctx.query_start_loc, ctx.context_lens, ctx.num_seqs, self.nh, self.nkv, self.d, self.scale,
                     scratch, bound, window=int(self.window or 0), split_size=split, err=rt.err,
+                    cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
                 )  # fmt: skip
                 return _project(rt, "attn.proj", out, self.w_o)
             if splits > 1:
@@ -175,5 +182,5 @@ class PagedAttention(Mixer):
             q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens,
             ctx.num_seqs, ctx.max_query_len, self.nh, self.nkv, self.d, self.scale,
             window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound, split_size=split,
-            err=self.rt.err,
+            err=self.rt.err, cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
         )  # fmt: skip

@@ -279,7 +279,7 @@ def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5, junk=(1e4, -1e4
     return kc, vc, tables
 
 
-def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256, junk=(1e4, -1e4)):
+def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256, junk=(1e4, -1e4), cluster=True):
     g = torch.Generator().manual_seed(seed)
     kv = [(torch.randn(c, nkv, d, generator=g).to(dtype), torch.randn(c, nkv, d, generator=g).to(dtype)) for c in ctx_lens]
     qs = [torch.randn(ql, nh, d, generator=g).to(dtype) for ql in q_lens]
@@ -302,7 +302,7 @@ def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode
         ops.paged_attention(
             dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
             len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
-            split_size=split, kernel=kernel, err=err_flag(),
+            split_size=split, kernel=kernel, err=err_flag(), cluster=cluster,
         )  # fmt: skip
     if decode_form == "fused":
         assert int(scratch[2].abs().sum()) == 0
@@ -495,11 +495,12 @@ TMA_SHAPES = [(8, 2, 64, 16), (32, 8, 64, 16), (3, 1, 64, 32), (24, 8, 128, 32),
 
 @pytest.mark.parametrize("nh,nkv,d,bs", TMA_SHAPES)
 @pytest.mark.parametrize("split", [64, 128, 256, 1024])
-def test_paged_attention_tma_decode(ops, nh, nkv, d, bs, split):
+@pytest.mark.parametrize("cluster", [True, False])  # the ranges merged through a cluster's shared memory (up to 16), or by ticket
+def test_paged_attention_tma_decode(ops, nh, nkv, d, bs, split, cluster):
     ctx = [700, 1, 256, 257, 33, 64, 65, 1500, 16, 17]
     err_flag().zero_()
     # what lies past a context inside its last page must not reach the result, whatever it is
-    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form="fused", kernel="tma", split=split, junk=(float("nan"), float("nan")))
+    out, ref, _ = run_attention(ops, torch.bfloat16, nh, nkv, d, bs, ctx, [1] * len(ctx), decode_form="fused", kernel="tma", split=split, junk=(float("nan"), float("nan")), cluster=cluster)
     assert int(err_flag().sum()) == 0
     assert not torch.isnan(out).any()
     assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
