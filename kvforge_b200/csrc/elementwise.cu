@@ -108,11 +108,14 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int H, float eps) {
   pdl_launch();
-  pdl_wait();
   extern __shared__ __align__(16) float rowbuf[];  // H floats
   __shared__ float red[32];
   const int r = blockIdx.x;
+  // the norm's weight does not come from the kernel ahead: a thread's first four are fetched before the wait
+  const int i0 = threadIdx.x * 4;
+  const float4 w0 = i0 < H ? *reinterpret_cast<const float4*>(weight + i0) : make_float4(0.f, 0.f, 0.f, 0.f);
   const int src = rows ? rows[r] : r;
+  pdl_wait();
   float* h = resid + (size_t)src * H;
   const T* dl = delta ? delta + (size_t)src * H : nullptr;
   const float* pt = partials ? partials + (size_t)src * H : nullptr;
@@ -142,7 +145,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   T* o = out + (size_t)r * H;
   for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
     const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-    const float4 w = *reinterpret_cast<const float4*>(weight + i);
+    const float4 w = i == i0 ? w0 : *reinterpret_cast<const float4*>(weight + i);
     Vec4<T>::store(o + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
   }
 }
@@ -291,14 +294,23 @@ __global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __rest
                                         T* __restrict__ vcache, int nh, int nkv, int d, int block_size,
                                         long long num_slots, int heads_per_cta, int* __restrict__ err) {
   pdl_launch();
-  pdl_wait();
   const int n = blockIdx.x;
   const int half = d >> 1;
   const int total_heads = nh + 2 * nkv;
   const int stride = total_heads * d;
   const int head = blockIdx.y * heads_per_cta + threadIdx.x / half;
   const int j = threadIdx.x % half;
-  if (threadIdx.x >= heads_per_cta * half || head >= total_heads) return;
+  const bool mine = threadIdx.x < heads_per_cta * half && head < total_heads;
+  // positions, slots and frequencies come with the step, not from the kernel ahead: the angle is
+  // worked out before the wait
+  float sn = 0.f, cs = 1.f;
+  long long slot = -1;
+  if (mine) {
+    if (head < nh + nkv) sincosf((float)positions[n] * inv_freq[j], &sn, &cs);
+    slot = slots ? (long long)slots[n] : -1;
+  }
+  pdl_wait();
+  if (!mine) return;
   T* row = qkv ? qkv + (size_t)n * stride : nullptr;
   const float* prow = partials ? partials + (size_t)n * stride : nullptr;
   const int i1 = head * d + j, i2 = i1 + half;
@@ -314,15 +326,12 @@ __global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __rest
     x1 = to_float<T>(row[i1]);
     x2 = to_float<T>(row[i2]);
   }
-  long long slot = slots ? (long long)slots[n] : -1;
   if (slot >= num_slots) {
     if (j == 0 && err) atomicOr(err, 2);
     slot = -1;
   }
   T y1, y2;
   if (head < nh + nkv) {
-    float sn, cs;
-    sincosf((float)positions[n] * inv_freq[j], &sn, &cs);
     y1 = from_float<T>(x1 * cs - x2 * sn);
     y2 = from_float<T>(x2 * cs + x1 * sn);
   } else {
