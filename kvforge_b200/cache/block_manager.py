@@ -16,6 +16,8 @@ and tables of its own.  A ``full`` group keeps every key.  A ``window`` group ke
 
 from __future__ import annotations
 
+import numpy as np
+
 from collections.abc import Sequence
 from dataclasses import dataclass
 
@@ -120,14 +122,21 @@ class BlockManager:
         return b * self.block_size + position % self.block_size
 
     def slots(self, seq_id: str, start: int, end: int, group: int = 0) -> list[int]:
+        """Slots of positions ``start .. end-1``."""
+        return self.slots_array(seq_id, start, end, group).tolist()
+
+    def slots_array(self, seq_id: str, start: int, end: int, group: int = 0) -> np.ndarray:
+        """The same as an int32 array (a prompt portion has thousands of positions)."""
         table, bs = self._pools[group].tables[seq_id], self.block_size
-        out = []
-        for p in range(start, end):
-            b = table[p // bs]
-            if b < 0:
-                raise RuntimeError(f"position {p} of {seq_id} lies in a page that was given back")
-            out.append(b * bs + p % bs)
-        return out
+        if end <= start:
+            return np.empty(0, dtype=np.int32)
+        first, last = start // bs, (end - 1) // bs
+        pages = np.asarray(table[first : last + 1], dtype=np.int64)
+        if (pages < 0).any():
+            p = (first + int(np.argmax(pages < 0))) * bs
+            raise RuntimeError(f"position {max(p, start)} of {seq_id} lies in a page that was given back")
+        pos = np.arange(start, end, dtype=np.int64)
+        return (pages[pos // bs - first] * bs + pos % bs).astype(np.int32)
 
     # ------------------------------------------------------------------ sizing
     def _first_live_block(self, pool: _Pool, write_start: int) -> int:

@@ -29,6 +29,9 @@ from .runtime import Runtime, StepContext
 
 # graphs for shorter contexts than this are not told apart
 MIN_GRAPH_CONTEXT = 1024
+# steps of at least this many tokens are replayed as graphs too, padded to a multiple of GRAPH_TOKEN_STEP
+MIN_GRAPH_TOKENS = 512
+GRAPH_TOKEN_STEP = 256
 
 
 @dataclass
@@ -120,9 +123,9 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs)
         self.pdl = bool(pdl)  # programmatic dependent launch between the kernels of a step
         self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
-        # keyed by (batch bucket, longest context the graph reaches)
-        self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
-        self.graph_kernels: dict[tuple[int, int], int] = {}  # kernels of this library inside each captured graph
+        # keyed by (tokens, sequences, longest context the graph reaches)
+        self._graphs: dict[tuple[int, int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.graph_kernels: dict[tuple[int, int, int], int] = {}  # kernels of this library inside each captured graph
         self.num_kernel_launches = 0  # kernels of this library launched by steps, replays included
         self.num_graph_kernels = 0  # those of them that ran inside replayed graphs
         self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
@@ -191,7 +194,7 @@ class ModelRunner:
             host[o["positions"] + n : o["positions"] + n + k] = np.arange(item.start_pos, end, dtype=np.int32)
             for g in range(self.n_groups):
                 base = o["slots"] + g * lay.n_cap + n
-                host[base : base + k] = bm.slots(item.seq_id, item.start_pos, end, g)
+                host[base : base + k] = bm.slots_array(item.seq_id, item.start_pos, end, g)
                 table = bm.get_block_table(item.seq_id, g)
                 used = -(-end // bs)  # only the pages that cover the live context (continuous.py:67)
                 tb = o["tables"] + (g * lay.b_cap + b) * lay.width
@@ -261,7 +264,8 @@ class ModelRunner:
                 self._pool.clear_state_slots(fresh)
         single = all(len(it.token_ids) == 1 and it.wanted() == [0] for it in items)
         if self.cuda_graphs and single and len(items) <= self.graph_buckets[-1]:
-            return self._step_graph(items)
+            bucket = next(b for b in self.graph_buckets if b >= len(items))
+            return self._step_graph(items, bucket, bucket)
         n_tok = sum(len(it.token_ids) for it in items)
         if n_tok > self.rt.max_tokens or len(items) > self.rt.max_seqs:
             raise ValueError(
@@ -269,6 +273,14 @@ class ModelRunner:
                 f"({self.rt.max_tokens} tokens, {self.rt.max_seqs} requests)"
             )
         n_rows = sum(len(it.wanted()) for it in items)
+        if self.cuda_graphs and n_tok >= MIN_GRAPH_TOKENS and len(items) <= self.graph_buckets[-1]:
+            # A step of many tokens launches some 130 kernels; replayed as a graph they follow one
+            # another without the gaps of launches from Python.  Tokens are padded to a multiple of
+            # GRAPH_TOKEN_STEP, sequences to a bucket; the padding belongs to no sequence.
+            b_cap = next(b for b in self.graph_buckets if b >= len(items))
+            n_cap = min(self.rt.max_tokens, -(-n_tok // GRAPH_TOKEN_STEP) * GRAPH_TOKEN_STEP)
+            if n_rows <= b_cap and n_cap >= n_tok:
+                return self._step_graph(items, n_cap, b_cap)
         width = max(-(-(it.start_pos + len(it.token_ids)) // self.block_size) for it in items)
         lay = self._layout(n_tok, len(items), width, n_rows)
         self._ensure(lay.total)
@@ -288,27 +300,27 @@ class ModelRunner:
         self._pool = pool
         self.model.attach_cache(pool.caches)
 
-    def _step_graph(self, items: Sequence[BatchItem]) -> torch.Tensor:
-        nb = len(items)
-        bucket = next(b for b in self.graph_buckets if b >= nb)
-        lay = self._layout(bucket, bucket, self.max_width, bucket)
+    def _step_graph(self, items: Sequence[BatchItem], n_cap: int, b_cap: int) -> torch.Tensor:
+        """Replay the step as a graph made for ``n_cap`` tokens in ``b_cap`` sequences (``n_cap ==
+        b_cap``: one token each, the decode form)."""
+        lay = self._layout(n_cap, b_cap, self.max_width, b_cap)
         self._ensure(lay.total)
-        # padding tokens of the bucket: token 0 at position 0, written to no slot
+        # padding tokens: token 0 at position 0, written to no slot, part of no sequence
         if self._copy_done is not None:
             self._copy_done.synchronize()
         host, o = self._host.numpy(), lay.off
-        host[o["token_ids"] : o["token_ids"] + bucket] = 0
-        host[o["positions"] : o["positions"] + bucket] = 0
-        host[o["feedback_rows"] : o["feedback_rows"] + bucket] = -1
-        host[o["logit_rows"] : o["logit_rows"] + bucket] = 0
+        host[o["token_ids"] : o["token_ids"] + n_cap] = 0
+        host[o["positions"] : o["positions"] + n_cap] = 0
+        host[o["feedback_rows"] : o["feedback_rows"] + n_cap] = -1
+        host[o["logit_rows"] : o["logit_rows"] + b_cap] = 0
         for g in range(self.n_groups):
-            host[o["slots"] + g * bucket : o["slots"] + (g + 1) * bucket] = -1
+            host[o["slots"] + g * n_cap : o["slots"] + (g + 1) * n_cap] = -1
         n, _, r, max_q, max_ctx = self._fill(items, lay)
         self._upload(lay.total)
         # A graph fixes its grids, so it is made for contexts up to a bound: the next power of two
         # (kernels whose grid follows the longest context then launch at most twice what they need).
         reach = min(self.max_model_len, max(MIN_GRAPH_CONTEXT, 1 << max(0, max_ctx - 1).bit_length()))
-        key = (bucket, reach)
+        key = (n_cap, b_cap, reach)
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(key, lay)
@@ -320,9 +332,10 @@ class ModelRunner:
         self.num_tokens_processed += n
         return logits[:r]
 
-    def _capture(self, key: tuple[int, int], lay: _Layout):
-        bucket, reach = key
-        ctx = self._context(lay, bucket, bucket, bucket, 1, reach, bound=reach)
+    def _capture(self, key: tuple[int, int, int], lay: _Layout):
+        n_cap, b_cap, reach = key
+        # one token per sequence: the decode form; else a sequence may bring up to all the tokens
+        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if n_cap == b_cap else n_cap, reach, bound=reach)
         # one eager run first: sizes every buffer and loads every kernel outside the capture
         self.model.forward(ctx)
         torch.cuda.synchronize()
