@@ -75,3 +75,40 @@ def test_llama_1b_width_generation_uses_graphs_and_the_device_token_loop(big):
         outs[mode] = [o.output_token_ids for o in res]
         assert all(len(o) == 12 for o in outs[mode])
     assert outs["graphs+async"] == outs["plain"]
+
+
+def test_steps_of_many_tokens_replay_as_graphs_with_the_same_logits(big):
+    """A step of 512 tokens or more is replayed as a CUDA graph made for its token count rounded up
+    to 256 and its sequence count rounded up to a bucket; the padding must change nothing."""
+    from kvforge_b200 import CacheConfig
+    from kvforge_b200.engine.core import EngineCore
+    from kvforge_b200.engine.step import BatchItem
+
+    folder, reqs, ref = big
+    long, short = (reqs["a"] * 5)[:1300], reqs["b"]
+    rows = {}
+    for graphs in (False, True):
+        core = EngineCore.from_model_dir(
+            folder, dtype="bfloat16", cache=CacheConfig(block_size=16, num_blocks=100, watermark=0.0),
+            max_num_seqs=4, max_num_batched_tokens=1024, max_model_len=1536, cuda_graphs=graphs,
+        )  # fmt: skip
+        bm = core.block_manager
+        for rid, n in (("l", 650), ("s", len(short))):
+            bm.allocate(rid, n)
+            core.state_slots.allocate(rid)
+        # 650 tokens of a long prompt beside a whole short one; then the rest of the long one beside a decoded token
+        first = core.runner.step([BatchItem("l", long[:650], 0, "last"), BatchItem("s", short, 0, "last")]).float().cpu().clone()
+        bm.append_slots("l", 1300, 650)
+        bm.append_slots("s", len(short) + 1, len(short))
+        second = core.runner.step([BatchItem("l", long[650:], 650, "last"), BatchItem("s", [7], len(short), "last")]).float().cpu().clone()
+        rows[graphs] = (first, second)
+        if graphs:
+            assert core.runner.num_graph_kernels > 0 and len(core.runner.graph_kernels) >= 1
+        core.rt.check_error_flag()
+        del core
+        torch.cuda.empty_cache()
+    for a, b in zip(rows[False], rows[True]):
+        for i in range(a.shape[0]):
+            assert rel_err(b[i], a[i]) < 2e-2
+    # and the short prompt's last row is what the plain implementation says
+    assert rel_err(rows[True][0][1], ref["b"][len(short) - 1]) < 6e-2
