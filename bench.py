@@ -432,7 +432,7 @@ def run_only(args) -> dict:
     """One part alone on a small footing: what the profiler is pointed at."""
     from kvforge_b200 import PRESETS
 
-    cfg = PRESETS["llama-3.2-1b"]
+    cfg = PRESETS[args.preset]
     if args.only in ("attention", "attention-prefill", "gemm"):
         return run_kernel_only(args, cfg)
     ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
@@ -461,6 +461,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")

@@ -112,3 +112,25 @@ def test_steps_of_many_tokens_replay_as_graphs_with_the_same_logits(big):
             assert rel_err(b[i], a[i]) < 2e-2
     # and the short prompt's last row is what the plain implementation says
     assert rel_err(rows[True][0][1], ref["b"][len(short) - 1]) < 6e-2
+
+
+@pytest.mark.parametrize("preset", ["llama-3.2-3b", "llama-3.1-8b"])
+def test_wider_llamas_with_head_size_128(tmp_path_factory, preset):
+    """The widths of Llama-3.2-3B (24 heads of 128 over 8 kv heads, hidden 3072) and Llama-3.1-8B
+    (hidden 4096, intermediate 14336, untied head), two layers each: whole prompts, portions beside
+    decoded tokens, and the last tokens one by one, in bfloat16 against the plain implementation."""
+    from test_gpu_replay import check, replay_in_process
+
+    base = PRESETS[preset]
+    cfg = ModelConfig(**{**base.__dict__, "num_layers": 2, "max_position_embeddings": 4096})
+    folder = tmp_path_factory.mktemp("wide") / f"{preset}-width-2-layers"
+    write_random_model(folder, cfg, seed=6, store_dtype=torch.bfloat16, init_std=0.025, norm_std=0.05)
+    reqs = {"a": random_tokens(cfg.vocab_size, 210, seed=3), "b": random_tokens(cfg.vocab_size, 66, seed=4)}
+    plain = PlainLlama(folder, device="cuda")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = {rid: plain.logits(t).cpu() for rid, t in reqs.items()}
+    del plain
+    torch.cuda.empty_cache()
+    for steps in (traces.whole(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {"a": 190, "b": 50}, max_live=2, seed=2)):
+        outputs = replay_in_process(folder, "bfloat16", steps)
+        check(steps, outputs, ref, 6e-2)
