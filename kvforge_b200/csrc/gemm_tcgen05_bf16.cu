@@ -62,8 +62,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
         : "=r"(done)
         : "r"(bar), "r"(parity)
         : "memory");
-    if (done) return true;
-    __nanosleep(64);
+    if (done) return true;  // (try_wait itself suspends the thread for a while: no sleep between tries)
   }
   if (err) atomicOr(err, 4);
   return false;
