@@ -36,16 +36,26 @@ using namespace kvf;
 
 namespace {
 
-constexpr int D = 64;
+// D: head size, 64 or 128.  A [rows][128] tile lies in shared memory as two [rows][64] halves of 128-byte
+// swizzled rows; S = Q K^T then walks D/16 k-steps over the halves, and O += P V is one MMA of 64
+// output columns per half of V.
 constexpr int BM = 128;  // rows per CTA
 constexpr int BN = 64;   // keys per tile
 constexpr int SOFTMAX_WARPS = 8;                    // two groups of four: even and odd key tiles
 constexpr int LOADER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1;
 constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
-constexpr int KV_STAGES = 4;
+template <int D> struct Shape {
+  static constexpr int HALVES = D / 64;
+  static constexpr int KV_STAGES = D == 64 ? 4 : 5;
+  static constexpr int CTAS_PER_SM = D == 64 ? 2 : 1;  // 112 KB and 256 tensor-memory columns, or 224 KB and 512
+  static constexpr uint32_t Q_BYTES = HALVES * 128 * 128;     // [128 rows][D] bfloat16
+  static constexpr uint32_t KV_BYTES = HALVES * 64 * 128;     // a [64 keys][D] bfloat16 tile
+  static constexpr uint32_t TMEM_COLS = D == 64 ? 256u : 512u;  // S: 2 x 64, O: 2 x D
+  static constexpr size_t SMEM_BYTES = (size_t)Q_BYTES + (size_t)KV_STAGES * 2 * KV_BYTES + 2 * 128 * 128 + 256;
+};
 constexpr int LOOKAHEAD = 2;                 // tiles in flight behind the one being handed over
-constexpr uint32_t Q_BYTES = BM * 128;       // [128 rows][64] bfloat16
-constexpr uint32_t KV_BYTES = BN * 128;      // a [64 keys][64] bfloat16 tile
+constexpr uint32_t Q_HALF = BM * 128;        // [128 rows][64] bfloat16
+constexpr uint32_t KV_HALF = BN * 128;       // [64 keys][64] bfloat16
 constexpr uint32_t P_BYTES = BM * 128;       // [128 rows][64 keys] bfloat16
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 constexpr float RESCALE_STEP = 8.f;          // log2 units
@@ -229,8 +239,11 @@ __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)
   return sum0 + sum1;
 }
 
-__global__ void __launch_bounds__(THREADS, 2)
+template <int D>
+__global__ void __launch_bounds__(THREADS, Shape<D>::CTAS_PER_SM)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
+  constexpr int HALVES = Shape<D>::HALVES, KV_STAGES = Shape<D>::KV_STAGES;
+  constexpr uint32_t Q_BYTES = Shape<D>::Q_BYTES, KV_BYTES = Shape<D>::KV_BYTES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // no slack for rounding up (two CTAs have to fit an SM): the base must be 1024-byte aligned
   // as declared, else the kernel refuses (bit 8 of the error flag) rather than compute garbage
@@ -280,7 +293,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(Shape<D>::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -295,11 +308,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   if (live && warp == LOADER_WARP) {
     // ---- loader: Q, then a K and a V tile per stage; 16-byte chunks into the swizzled layout
     const bf16* qg = p.q + (size_t)(q_begin + q0) * p.q_stride + (size_t)(kvh * g) * D;
-    for (int idx = lane; idx < BM * 8; idx += 32) {
-      const int r = idx >> 3, c = idx & 7;
+    for (int idx = lane; idx < BM * (D / 8); idx += 32) {
+      const int r = idx / (D / 8), c = idx % (D / 8);
       const int tok = r / g, hh = r - tok * g;
       const bool valid = tok < n_tok;
-      cpa16(q_s + sw128(r, c), qg + (valid ? (size_t)tok * p.q_stride + (size_t)hh * D + c * 8 : 0), valid);
+      cpa16(q_s + (c >> 3) * Q_HALF + sw128(r, c & 7), qg + (valid ? (size_t)tok * p.q_stride + (size_t)hh * D + c * 8 : 0), valid);
     }
     const int* bt = p.block_tables + (size_t)b * p.bt_stride;
     // A tile's 64 keys sit in up to 64 pages: lane l looks up keys l and l+32 (independent table
@@ -331,9 +344,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const int key = 4 * i + sub;  // held by lane key % 32 in slot key / 32 = i / 8
         const long long src = __shfl_sync(0xffffffffu, row[i >> 3], 4 * (i & 7) + sub);
         const bool valid = src >= 0;
-        const long long at = valid ? src + c * 8 : 0;
-        cpa16(ks + sw128(key, c), p.kcache + at, valid);
-        cpa16(vs + sw128(key, c), p.vcache + at, valid);
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+          const long long at = valid ? src + h * 64 + c * 8 : 0;
+          cpa16(ks + h * KV_HALF + sw128(key, c), p.kcache + at, valid);
+          cpa16(vs + h * KV_HALF + sw128(key, c), p.vcache + at, valid);
+        }
       }
     };
     if (p.use_tma) {
@@ -367,8 +383,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
               }
             }
             const int row = blk >= 0 ? (blk * p.nkv + kvh) * p.block_size + off : p.total_rows;
-            tma_load_2d(ks + lane * 2048, &map_k, 0, row, bar);
-            tma_load_2d(vs + lane * 2048, &map_v, 0, row, bar);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+              tma_load_2d(ks + h * KV_HALF + lane * 2048, &map_k, 64 * h, row, bar);
+              tma_load_2d(vs + h * KV_HALF + lane * 2048, &map_v, 64 * h, row, bar);
+            }
           }
         } else {
           issue_tile(t);
@@ -420,13 +439,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   } else if (live && warp == MMA_WARP) {
     if (lane == 0) {
       // ---- MMA issuer: S(t+1) goes out before P(t) V(t), so the softmax never waits for it
-      constexpr uint32_t id_s = idesc(BN, 0), id_o = idesc(D, 1);
-      const uint64_t qd = sdesc(q_s);
+      constexpr uint32_t id_s = idesc(BN, 0), id_o = idesc(64, 1);
       auto issue_s = [&](int t) {
-        const uint64_t kd = sdesc(kv_s + (t % KV_STAGES) * 2 * KV_BYTES);
         const uint32_t dst = tmem_s + (uint32_t)((t & 1) * BN);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) umma(dst, qd + 2 * kk, kd + 2 * kk, id_s, kk > 0);
+        for (int kk = 0; kk < D / 16; ++kk)  // k-steps 0..3 in the first half of the tiles, 4..7 in the second
+          umma(dst, sdesc(q_s + (kk >> 2) * Q_HALF) + 2 * (kk & 3), sdesc(kv_s + (t % KV_STAGES) * 2 * KV_BYTES + (kk >> 2) * KV_HALF) + 2 * (kk & 3), id_s, kk > 0);
         umma_commit(s_full0 + 8 * (t & 1));
       };
       bool ok = bar_wait(q_full, 0, p.err);
@@ -449,9 +467,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const uint32_t vs = kv_s + (t % KV_STAGES) * 2 * KV_BYTES + KV_BYTES;
         const uint64_t pd = sdesc(p_s + (t & 1) * P_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          // A: 16 keys of P = 32 bytes along the row; B: 16 keys of V = 16 rows of 128 bytes
-          umma(tmem_o + (uint32_t)((t & 1) * D), pd + 2 * kk, sdesc(vs + kk * 16 * 128), id_o, (t > 1 || kk > 0) ? 1u : 0u);
+        for (int h = 0; h < HALVES; ++h) {  // 64 output dims per half of V
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            // A: 16 keys of P = 32 bytes along the row; B: 16 keys of V = 16 rows of 128 bytes
+            umma(tmem_o + (uint32_t)((t & 1) * D + 64 * h), pd + 2 * kk, sdesc(vs + h * KV_HALF + kk * 16 * 128), id_o, (t > 1 || kk > 0) ? 1u : 0u);
+          }
         }
         umma_commit(pv_done0 + 8 * (t & 1));         // O[t&1] holds tiles t&1, .., t; P buffer t&1 may be rewritten
         umma_commit(kv_empty0 + 8 * (t % KV_STAGES));  // and the stage may be refilled
@@ -554,7 +575,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == MMA_WARP) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Shape<D>::TMEM_COLS) : "memory");
   }
 }
 
@@ -578,13 +599,13 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// The cache as [rows][64] bfloat16; boxes of [16][64], 128-byte swizzle, zeros past the end.
-int cache_map(CUtensorMap* map, const void* ptr, long long rows) {
+// The cache as [rows][d] bfloat16; boxes of [16][64], 128-byte swizzle, zeros past the end.
+int cache_map(CUtensorMap* map, const void* ptr, long long rows, int d) {
   EncodeTiledFn fn = encode_tiled();
   if (!fn) return (int)cudaErrorNotSupported;
-  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)D, 16u};
+  const cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+  const cuuint32_t box[2] = {64u, 16u};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -592,17 +613,24 @@ int cache_map(CUtensorMap* map, const void* ptr, long long rows) {
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+template <int D>
+int launch_tc_attn(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape<D>::SMEM_BYTES);
+  if (e != cudaSuccess) return (int)e;
+  return launch(attn_tcgen05_kernel<D>, grid, dim3(THREADS), Shape<D>::SMEM_BYTES, st, mk, mv, p);
+}
+
 }  // namespace
 
-// bfloat16, head size 64, nh/nkv <= 128; out rows and q rows 16-byte aligned.  err: device flag.
-// kcache/vcache: [num_blocks][nkv][block_size][64].
+// bfloat16, head size 64 or 128, nh/nkv <= 128; out rows and q rows 16-byte aligned.  err: device flag.
+// kcache/vcache: [num_blocks][nkv][block_size][d].
 KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                              const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                              int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
                                              int nkv, int d, int block_size, long long num_blocks, float scale,
                                              int window, int* err, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
-  if (d != D || nkv <= 0 || nh % nkv != 0 || nh / nkv > BM || block_size <= 0 || num_blocks <= 0) return (int)cudaErrorInvalidValue;
+  if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || nh / nkv > BM || block_size <= 0 || num_blocks <= 0) return (int)cudaErrorInvalidValue;
   if ((q_stride & 7) || (out_stride & 7) || ((((uintptr_t)q) | ((uintptr_t)out)) & 15)) return (int)cudaErrorInvalidValue;
   if ((unsigned)B > 65535u || (max_q_len + (BM / (nh / nkv)) - 1) / (BM / (nh / nkv)) > 65535) return (int)cudaErrorInvalidValue;
   TcAttnParams p;
@@ -622,11 +650,9 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
   memset(&mk, 0, sizeof(mk));
   memset(&mv, 0, sizeof(mv));
   if (p.use_tma) {
-    if (cache_map(&mk, kcache, rows) || cache_map(&mv, vcache, rows)) p.use_tma = 0;
+    if (cache_map(&mk, kcache, rows, d) || cache_map(&mv, vcache, rows, d)) p.use_tma = 0;
   }
   const int g = nh / nkv, tq = BM / g;
-  constexpr size_t smem = Q_BYTES + KV_STAGES * 2 * KV_BYTES + 2 * P_BYTES + 128;
-  cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  return launch(attn_tcgen05_kernel, dim3(nkv, B, (max_q_len + tq - 1) / tq), dim3(THREADS), smem, st, mk, mv, p);
+  const dim3 grid(nkv, B, (max_q_len + tq - 1) / tq);
+  return d == 64 ? launch_tc_attn<64>(mk, mv, p, grid, st) : launch_tc_attn<128>(mk, mv, p, grid, st);
 }

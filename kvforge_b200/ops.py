@@ -370,8 +370,8 @@ def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decod
 
 def tcgen05_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:
     """Whether the tcgen05 kernel (``csrc/attention_tcgen05.cu``) takes this shape: many queries
-    (not the decode form), bfloat16, head size 64."""
-    return dtype == torch.bfloat16 and d == 64 and not decode_form and nh // max(nkv, 1) <= 128
+    (not the decode form), bfloat16, head size 64 or 128."""
+    return dtype == torch.bfloat16 and d in (64, 128) and not decode_form and nh // max(nkv, 1) <= 128
 
 
 def tma_decode_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, block_size: int, num_blocks: int) -> bool:

@@ -417,7 +417,7 @@ def test_paged_attention_mma(ops, nh, nkv, d, bs, ctx_lens, q_lens):
 
 # ---- the tcgen05 kernel (bfloat16, head size 64, many queries)
 
-TC_SHAPES = [s for s in MMA_SHAPES if s[2] == 64] + [(4, 4, 64, 16), (16, 1, 64, 32)]
+TC_SHAPES = MMA_SHAPES + [(4, 4, 64, 16), (16, 1, 64, 32), (4, 4, 128, 16), (8, 1, 128, 48)]
 
 
 @pytest.mark.parametrize("nh,nkv,d,bs", TC_SHAPES)
