@@ -428,11 +428,44 @@ def run_kernel_only(args, cfg) -> dict:
             "GB/s": round(nbytes / sec / 1e9, 1), "frac_of_hbm_peak": round(nbytes / sec / 1e9 / pk["hbm_gbs"], 3)}  # fmt: skip
 
 
+def run_load(args, cfg) -> dict:
+    """A serving load through the Python entry point: ``--batch`` requests (default 64 here) with
+    prompt lengths drawn uniformly from 128 to 2,048 and 256 greedy tokens each, under chunked
+    prefill with a 2,048-token budget."""
+    import random
+    import time
+
+    import torch
+
+    from kvforge_b200 import CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
+
+    nreq = args.batch if args.batch != 8 else 64
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(128, 2048))] for _ in range(nreq)]
+    engine = InferenceEngine(EngineConfig(
+        model=cfg, cache=CacheConfig(block_size=16, num_blocks=None, kv_cache_memory_gb=16.0),
+        scheduler=SchedulerConfig(max_num_seqs=64, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT), dtype="bfloat16",
+    ))  # fmt: skip
+    engine.generate(prompts[:4], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))  # graphs, kernels
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    n_in, n_out = sum(len(q) for q in prompts), sum(len(o.output_token_ids) for o in outs)
+    m = engine.stats()["metrics"]
+    return {"only": "load", "preset": args.preset, "requests": nreq, "prompt_tokens": n_in, "generated_tokens": n_out,
+            "seconds": round(dt, 3), "generated_tokens_per_s": round(n_out / dt, 1), "total_tokens_per_s": round((n_in + n_out) / dt, 1),
+            "tpot_p50_ms": round(m["tpot_p50_ms"], 3), "preemptions": engine.stats()["scheduler"]["num_preemptions"]}  # fmt: skip
+
+
 def run_only(args) -> dict:
     """One part alone on a small footing: what the profiler is pointed at."""
     from kvforge_b200 import PRESETS
 
     cfg = PRESETS[args.preset]
+    if args.only == "load":
+        return run_load(args, cfg)
     if args.only in ("attention", "attention-prefill", "gemm"):
         return run_kernel_only(args, cfg)
     ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
@@ -460,7 +493,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm", "load"], help="run one part alone and print a short line (for profiling)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
