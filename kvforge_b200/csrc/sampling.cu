@@ -50,12 +50,38 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
   return v;
 }
 
+constexpr int MAX_BLOCKS = 512;  // stretches of the vocabulary whose masses the draw keeps in shared memory
+
 struct Shared {
   unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass)
   unsigned long long red[NWARPS];
   unsigned long long bcast[3];
+  unsigned long long blk[MAX_BLOCKS];    // mass of each stretch, in index order
   float fred[32];
 };
+
+// f(i, row[i]) for every i < V, each thread taking its share.  Rows that start on a 16-byte boundary
+// are read four values at a time, and four such reads are in flight per thread: a pass over the
+// row is bound by L2 latency otherwise (one CTA reads a whole row).
+template <typename F>
+__device__ __forceinline__ void for_each(const float* __restrict__ row, int V, F f) {
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n4; i += THREADS) {
+      const float4 v = r4[i];
+      f(4 * i, v.x);
+      f(4 * i + 1, v.y);
+      f(4 * i + 2, v.z);
+      f(4 * i + 3, v.w);
+    }
+    for (int i = (n4 << 2) + threadIdx.x; i < V; i += THREADS) f(i, row[i]);
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < V; i += THREADS) f(i, row[i]);
+  }
+}
 
 // One level of the radix descent.  Among entries with key >= lo_key whose bits above
 // `shift + 8` equal `prefix`, histogram (count or mass) by the digit at `shift`, then walk
@@ -67,15 +93,23 @@ __device__ int radix_level(Shared& sh, const float* row, int V, float temp, floa
   const int warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < NWARPS * 256; i += THREADS) (&sh.hist[0][0])[i] = 0ull;
   __syncthreads();
-  for (int i = threadIdx.x; i < V; i += THREADS) {
-    const float x = row[i] / temp;
+  for_each(row, V, [&](int, float raw) {
+    const float x = raw / temp;
     const unsigned key = ordered_key(x);
-    if (key < lo_key) continue;
-    if (shift < 24 && (key >> (shift + 8)) != prefix) continue;
+    if (key < lo_key) return;
+    if (shift < 24 && (key >> (shift + 8)) != prefix) return;
     const unsigned digit = (key >> shift) & 255u;
     const unsigned long long w = BY_MASS ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 1ull;
-    atomicAdd(&sh.hist[warp][digit], w);
-  }
+    if (!BY_MASS && shift == 24) {
+      // Counting at the top level (sign and exponent), where nearly all values share a digit: the
+      // lanes with the same digit are counted at once and one of them adds to the histogram.
+      // (For masses the grouping costs more than the atomics it saves: measured.)
+      const unsigned peers = __match_any_sync(__activemask(), digit);
+      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&sh.hist[warp][digit], (unsigned long long)__popc(peers));
+    } else {
+      atomicAdd(&sh.hist[warp][digit], w);  // integer sums: the order does not matter
+    }
+  });
   __syncthreads();
   // fold the per-warp histograms: thread t < 256 owns digit t
   if (threadIdx.x < 256) {
@@ -114,7 +148,7 @@ __device__ int radix_level(Shared& sh, const float* row, int V, float temp, floa
   return chosen;
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temps,
               const int* __restrict__ top_ks, const float* __restrict__ top_ps,
               const unsigned long long* __restrict__ rand_keys, int* __restrict__ out_tokens,
@@ -131,10 +165,10 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   if (T == 0.f) {
     // ---- greedy: highest logit, lowest index among equals
     unsigned long long best = 0;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
-      const unsigned long long c = ((unsigned long long)ordered_key(row[i]) << 32) | (0xFFFFFFFFu - (unsigned)i);
+    for_each(row, V, [&](int i, float x) {
+      const unsigned long long c = ((unsigned long long)ordered_key(x) << 32) | (0xFFFFFFFFu - (unsigned)i);
       best = c > best ? c : best;
-    }
+    });
     best = warp_max_u64(best);
     if (lane == 0) sh.red[warp] = best;
     __syncthreads();
@@ -153,7 +187,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
 
   // ---- maximum of the scaled row
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += THREADS) mx = fmaxf(mx, row[i] / T);
+  for_each(row, V, [&](int, float x) { mx = fmaxf(mx, x / T); });
   mx = block_max(mx, sh.fred);
   __syncthreads();
 
@@ -174,10 +208,10 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   if (top_p < 1.f) {
     // mass of what top-k kept
     unsigned long long z = 0;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
-      const float x = row[i] / T;
+    for_each(row, V, [&](int, float raw) {
+      const float x = raw / T;
       if (ordered_key(x) >= lo_key) z += __float2ull_rz(expf(x - mx) * FIX_ONE);
-    }
+    });
     z = warp_sum_u64(z);
     if (lane == 0) sh.red[warp] = z;
     __syncthreads();
@@ -201,49 +235,53 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     lo_key = prefix > lo_key ? prefix : lo_key;
   }
 
-  // ---- draw: warp w owns the contiguous index range [w*seg, (w+1)*seg)
-  const int seg = (((V + NWARPS - 1) / NWARPS) + 31) / 32 * 32;
-  const int s_begin = warp * seg, s_end = min(V, s_begin + seg);
-  unsigned long long part = 0;
-  for (int i = s_begin + lane; i < s_end; i += 32) {
+  // ---- draw: the inverse CDF in index order.  The row is cut into stretches of `bs` entries (at
+  // most MAX_BLOCKS of them); warps sum the kept mass of each stretch, one thread finds the
+  // stretch the target falls into, one warp walks that stretch 32 entries at a time.
+  const int bs = 1024 * ((V + 1024 * MAX_BLOCKS - 1) / (1024 * MAX_BLOCKS));
+  const int nblk = (V + bs - 1) / bs;
+  auto mass_at = [&](int i) -> unsigned long long {
+    if (i >= V) return 0ull;
     const float x = row[i] / T;
-    if (ordered_key(x) >= lo_key) part += __float2ull_rz(expf(x - mx) * FIX_ONE);
+    return ordered_key(x) >= lo_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
+  };
+  for (int b = warp; b < nblk; b += NWARPS) {
+    unsigned long long part = 0;
+    for (int c0 = b * bs; c0 < (b + 1) * bs; c0 += 1024) {
+#pragma unroll 8
+      for (int j = 0; j < 32; ++j) part += mass_at(c0 + 32 * j + lane);
+    }
+    part = warp_sum_u64(part);
+    if (lane == 0) sh.blk[b] = part;
   }
-  part = warp_sum_u64(part);
-  if (lane == 0) sh.red[warp] = part;
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned long long total = 0;
-    for (int w = 0; w < NWARPS; ++w) total += sh.red[w];
+    for (int b = 0; b < nblk; ++b) total += sh.blk[b];
     const unsigned long long rnd = splitmix64(rand_keys ? rand_keys[r] : 0ull);
-    unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
-    int w_sel = NWARPS - 1;
+    const unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
+    int b_sel = nblk - 1;
     unsigned long long before = 0;
-    for (int w = 0; w < NWARPS; ++w) {
-      if (target < before + sh.red[w]) {
-        w_sel = w;
+    for (int b = 0; b < nblk; ++b) {
+      if (target < before + sh.blk[b]) {
+        b_sel = b;
         break;
       }
-      before += sh.red[w];
+      before += sh.blk[b];
     }
     sh.bcast[0] = target - before;
     sh.bcast[1] = total;
-    sh.bcast[2] = (unsigned long long)w_sel;
+    sh.bcast[2] = (unsigned long long)b_sel;
   }
   __syncthreads();
-  const int w_sel = (int)sh.bcast[2];
-  unsigned long long rem = sh.bcast[0];
+  const int b_sel = (int)sh.bcast[2];
   const unsigned long long total = sh.bcast[1];
-  if (warp == w_sel) {
-    int tok = -1;
-    int last_kept = -1;
+  if (warp == 0) {
+    unsigned long long rem = sh.bcast[0];
+    int tok = -1, last_kept = -1;
+    const int s_begin = b_sel * bs, s_end = min(V, s_begin + bs);
     for (int base = s_begin; base < s_end && tok < 0; base += 32) {
-      const int i = base + lane;
-      unsigned long long w = 0;
-      if (i < s_end) {
-        const float x = row[i] / T;
-        if (ordered_key(x) >= lo_key) w = __float2ull_rz(expf(x - mx) * FIX_ONE);
-      }
+      const unsigned long long w = mass_at(base + lane);
       unsigned long long incl = w;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
