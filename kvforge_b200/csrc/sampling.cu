@@ -1,4 +1,7 @@
-// Token sampling on the device: greedy, temperature, top-k and top-p, one CTA per row.
+// Token sampling on the device: greedy, temperature, top-k and top-p.  A row is shared by a
+// thread-block cluster of up to 8 CTAs (each takes a slice of the vocabulary); what the CTAs of a
+// row find (maximum, histograms, masses) meets through distributed shared memory, and every CTA
+// works out the same decisions from the same sums, so nothing has to be sent back.
 //
 // Meaning of the options (as in umarhassan-cloud/kvforge, src/tokenvault/sampling.py:40-66):
 // temperature 0 picks the argmax of the logits; otherwise logits are divided by the
@@ -51,49 +54,167 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
 }
 
 constexpr int MAX_BLOCKS = 512;  // stretches of the vocabulary whose masses the draw keeps in shared memory
+constexpr int MAX_CLUSTER = 8;
 
 struct Shared {
-  unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass)
+  unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass); [0] holds the CTA's fold
+  unsigned long long tot[256];           // the row's histogram (all CTAs of the cluster)
   unsigned long long red[NWARPS];
   unsigned long long bcast[3];
   unsigned long long blk[MAX_BLOCKS];    // mass of each stretch, in index order
+  unsigned long long xu;                 // what this CTA offers to the others (a sum or a maximum)
+  float xf;
   float fred[32];
 };
 
-// f(i, row[i]) for every i < V, each thread taking its share.  Rows that start on a 16-byte boundary
-// are read four values at a time, and four such reads are in flight per thread: a pass over the
-// row is bound by L2 latency otherwise (one CTA reads a whole row).
+__device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// the address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t in_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ unsigned long long ld_cluster_u64(uint32_t addr) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+// every thread of every CTA of the cluster
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The cluster's view of a row: CTA `rank` of `nranks` owns entries [lo, hi).
+struct Slice {
+  const float* row;
+  int V, lo, hi;
+  uint32_t rank, nranks;
+};
+
+// f(i, row[i]) for every i of the slice, each thread taking its share.  Slices start at multiples of
+// 4; rows that start on a 16-byte boundary are read four values at a time, and four such reads are
+// in flight per thread: a pass is bound by L2 latency otherwise.
 template <typename F>
-__device__ __forceinline__ void for_each(const float* __restrict__ row, int V, F f) {
-  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-    const float4* r4 = reinterpret_cast<const float4*>(row);
-    const int n4 = V >> 2;
+__device__ __forceinline__ void for_each(const Slice& s, F f) {
+  if ((reinterpret_cast<uintptr_t>(s.row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(s.row);
+    const int b4 = s.lo >> 2, e4 = s.hi >> 2;  // whole float4s inside the slice
 #pragma unroll 4
-    for (int i = threadIdx.x; i < n4; i += THREADS) {
+    for (int i = b4 + threadIdx.x; i < e4; i += THREADS) {
       const float4 v = r4[i];
       f(4 * i, v.x);
       f(4 * i + 1, v.y);
       f(4 * i + 2, v.z);
       f(4 * i + 3, v.w);
     }
-    for (int i = (n4 << 2) + threadIdx.x; i < V; i += THREADS) f(i, row[i]);
+    for (int i = (e4 << 2) + threadIdx.x; i < s.hi; i += THREADS) f(i, s.row[i]);
   } else {
 #pragma unroll 4
-    for (int i = threadIdx.x; i < V; i += THREADS) f(i, row[i]);
+    for (int i = s.lo + threadIdx.x; i < s.hi; i += THREADS) f(i, s.row[i]);
   }
+}
+
+// Sums / maxima over the cluster: each CTA offers its value, all read all.  Two barriers: one before
+// the reads, one after (the slot may be written again).
+__device__ __forceinline__ unsigned long long cluster_sum_u64(Shared& sh, const Slice& s, unsigned long long mine) {
+  if (threadIdx.x == 0) sh.xu = mine;
+  cluster_barrier();
+  unsigned long long total = 0;
+  for (uint32_t c = 0; c < s.nranks; ++c) total += ld_cluster_u64(in_cta(sm32(&sh.xu), c));
+  cluster_barrier();
+  return total;
+}
+__device__ __forceinline__ unsigned long long cluster_max_u64(Shared& sh, const Slice& s, unsigned long long mine) {
+  if (threadIdx.x == 0) sh.xu = mine;
+  cluster_barrier();
+  unsigned long long best = 0;
+  for (uint32_t c = 0; c < s.nranks; ++c) {
+    const unsigned long long v = ld_cluster_u64(in_cta(sm32(&sh.xu), c));
+    best = v > best ? v : best;
+  }
+  cluster_barrier();
+  return best;
+}
+__device__ __forceinline__ float cluster_max_f32(Shared& sh, const Slice& s, float mine) {
+  if (threadIdx.x == 0) sh.xf = mine;
+  cluster_barrier();
+  float best = -INFINITY;
+  for (uint32_t c = 0; c < s.nranks; ++c) best = fmaxf(best, ld_cluster_f32(in_cta(sm32(&sh.xf), c)));
+  cluster_barrier();
+  return best;
+}
+// the CTA's sum of a per-thread value
+__device__ __forceinline__ unsigned long long block_sum_u64(Shared& sh, unsigned long long v) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  v = warp_sum_u64(v);
+  __syncthreads();
+  if (lane == 0) sh.red[warp] = v;
+  __syncthreads();
+  unsigned long long s = 0;
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) s += sh.red[w];
+  return s;
+}
+
+// The first position (in walking order) at which the running total of a[.] reaches (REACH: >=) or
+// passes (!REACH: >) `want`, found by one warp: lane l sums the positions l*per .. l*per+per-1 of the
+// walk, a scan over the lanes finds the lane, the lane walks its own stretch.  a(i) gives the value
+// at walk position i.  Returns the position, or -1 if the total never gets there; `before` is the
+// total ahead of the returned position.
+template <bool REACH, typename A>
+__device__ __forceinline__ int warp_find(int n, A a, unsigned long long want, unsigned long long& before) {
+  const int lane = threadIdx.x & 31;
+  const int per = (n + 31) / 32;
+  unsigned long long mine = 0;
+  for (int j = 0; j < per; ++j) {
+    const int i = lane * per + j;
+    if (i < n) mine += a(i);
+  }
+  unsigned long long incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const bool got = REACH ? incl >= want : incl > want;
+  const unsigned hit = __ballot_sync(0xffffffffu, got && mine > 0);
+  if (!hit) return -1;
+  const int src = __ffs(hit) - 1;
+  int pos = -1;
+  unsigned long long cum = incl - mine;  // ahead of this lane's stretch
+  if (lane == src) {
+    for (int j = 0; j < per; ++j) {
+      const int i = lane * per + j;
+      const unsigned long long v = i < n ? a(i) : 0ull;
+      if (v > 0 && (REACH ? cum + v >= want : cum + v > want)) {
+        pos = i;
+        break;
+      }
+      cum += v;
+    }
+  }
+  pos = __shfl_sync(0xffffffffu, pos, src);
+  before = __shfl_sync(0xffffffffu, cum, src);
+  return pos;
 }
 
 // One level of the radix descent.  Among entries with key >= lo_key whose bits above
 // `shift + 8` equal `prefix`, histogram (count or mass) by the digit at `shift`, then walk
 // digits from 255 down until the running total reaches `remaining`.  Returns the digit and
-// updates `remaining` to what is still wanted inside that digit.
+// updates `remaining` to what is still wanted inside that digit.  Every CTA of the cluster
+// histograms its slice, sums all the CTAs' histograms and takes the same walk.
 template <bool BY_MASS>
-__device__ int radix_level(Shared& sh, const float* row, int V, float temp, float mx, unsigned lo_key,
-                           unsigned prefix, int shift, unsigned long long& remaining) {
+__device__ int radix_level(Shared& sh, const Slice& sl, float temp, float mx, unsigned lo_key, unsigned prefix, int shift,
+                           unsigned long long& remaining) {
   const int warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < NWARPS * 256; i += THREADS) (&sh.hist[0][0])[i] = 0ull;
   __syncthreads();
-  for_each(row, V, [&](int, float raw) {
+  for_each(sl, [&](int, float raw) {
     const float x = raw / temp;
     const unsigned key = ordered_key(x);
     if (key < lo_key) return;
@@ -118,28 +239,22 @@ __device__ int radix_level(Shared& sh, const float* row, int V, float temp, floa
     for (int w = 0; w < NWARPS; ++w) s += sh.hist[w][threadIdx.x];
     sh.hist[0][threadIdx.x] = s;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned long long cum = 0;
-    int chosen = 0;
-    unsigned long long rem = remaining;
-    bool found = false;
-    for (int dgt = 255; dgt >= 0; --dgt) {
-      const unsigned long long c = sh.hist[0][dgt];
-      if (cum + c >= remaining) {
-        chosen = dgt;
-        rem = remaining - cum;
-        found = true;
-        break;
-      }
-      cum += c;
+  cluster_barrier();  // every CTA's fold is there
+  if (threadIdx.x < 256) {
+    unsigned long long s = 0;
+    for (uint32_t c = 0; c < sl.nranks; ++c) s += ld_cluster_u64(in_cta(sm32(&sh.hist[0][threadIdx.x]), c));
+    sh.tot[threadIdx.x] = s;
+  }
+  cluster_barrier();  // the folds have been read: the histograms may be cleared again
+  if (threadIdx.x < 32) {
+    // walk the digits from 255 down until the running total reaches what is wanted
+    unsigned long long before = 0;
+    const int at = warp_find<true>(256, [&](int i) { return sh.tot[255 - i]; }, remaining, before);
+    if (threadIdx.x == 0) {
+      // (fewer than wanted exist under this prefix: take everything)
+      sh.bcast[0] = at >= 0 ? (unsigned long long)(255 - at) : 0ull;
+      sh.bcast[1] = at >= 0 ? remaining - before : 0ull;
     }
-    if (!found) {  // fewer than wanted exist under this prefix: take everything
-      chosen = 0;
-      rem = 0;
-    }
-    sh.bcast[0] = (unsigned long long)chosen;
-    sh.bcast[1] = rem;
   }
   __syncthreads();
   remaining = sh.bcast[1];
@@ -148,6 +263,7 @@ __device__ int radix_level(Shared& sh, const float* row, int V, float temp, floa
   return chosen;
 }
 
+// grid (cluster size, rows); the cluster spans x
 __global__ void __launch_bounds__(THREADS, 2)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temps,
               const int* __restrict__ top_ks, const float* __restrict__ top_ps,
@@ -156,40 +272,48 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   __shared__ Shared sh;
   pdl_launch();
   pdl_wait();
-  const int r = blockIdx.x;
+  const int r = blockIdx.y;
   const float* row = logits + (size_t)r * ld;
   float* prow = probs_out ? probs_out + (size_t)r * V : nullptr;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float T = temps ? temps[r] : 0.f;
+  Slice sl;
+  sl.row = row;
+  sl.V = V;
+  sl.rank = blockIdx.x;
+  sl.nranks = gridDim.x;
+  {
+    const int per = (((V + (int)gridDim.x - 1) / (int)gridDim.x) + 3) & ~3;  // a multiple of 4
+    sl.lo = min(V, (int)blockIdx.x * per);
+    sl.hi = min(V, sl.lo + per);
+  }
 
   if (T == 0.f) {
     // ---- greedy: highest logit, lowest index among equals
     unsigned long long best = 0;
-    for_each(row, V, [&](int i, float x) {
+    for_each(sl, [&](int i, float x) {
       const unsigned long long c = ((unsigned long long)ordered_key(x) << 32) | (0xFFFFFFFFu - (unsigned)i);
       best = c > best ? c : best;
     });
     best = warp_max_u64(best);
     if (lane == 0) sh.red[warp] = best;
     __syncthreads();
-    if (warp == 0) {
-      unsigned long long v = lane < NWARPS ? sh.red[lane] : 0ull;
-      v = warp_max_u64(v);
-      if (lane == 0) sh.bcast[0] = v;
-    }
-    __syncthreads();
-    const int tok = (int)(0xFFFFFFFFu - (unsigned)(sh.bcast[0] & 0xFFFFFFFFull));
-    if (threadIdx.x == 0) out_tokens[r] = tok;
+    unsigned long long v = 0;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) v = sh.red[w] > v ? sh.red[w] : v;
+    v = cluster_max_u64(sh, sl, v);
+    const int tok = (int)(0xFFFFFFFFu - (unsigned)(v & 0xFFFFFFFFull));
+    if (threadIdx.x == 0 && sl.rank == 0) out_tokens[r] = tok;
     if (prow)
-      for (int i = threadIdx.x; i < V; i += THREADS) prow[i] = (i == tok) ? 1.f : 0.f;
+      for (int i = sl.lo + threadIdx.x; i < sl.hi; i += THREADS) prow[i] = (i == tok) ? 1.f : 0.f;
     return;
   }
 
   // ---- maximum of the scaled row
   float mx = -INFINITY;
-  for_each(row, V, [&](int, float x) { mx = fmaxf(mx, x / T); });
+  for_each(sl, [&](int, float x) { mx = fmaxf(mx, x / T); });
   mx = block_max(mx, sh.fred);
-  __syncthreads();
+  mx = cluster_max_f32(sh, sl, mx);
 
   unsigned lo_key = 0u;  // entries with key >= lo_key are kept
   const int k = top_ks ? top_ks[r] : 0;
@@ -198,7 +322,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     unsigned long long remaining = (unsigned long long)k;
     for (int level = 0; level < 4; ++level) {
       const int shift = 24 - 8 * level;
-      const int dgt = radix_level<false>(sh, row, V, T, mx, 0u, prefix, shift, remaining);
+      const int dgt = radix_level<false>(sh, sl, T, mx, 0u, prefix, shift, remaining);
       prefix = (prefix << 8) | (unsigned)dgt;
     }
     lo_key = prefix;  // the k-th largest key
@@ -208,36 +332,27 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   if (top_p < 1.f) {
     // mass of what top-k kept
     unsigned long long z = 0;
-    for_each(row, V, [&](int, float raw) {
+    for_each(sl, [&](int, float raw) {
       const float x = raw / T;
       if (ordered_key(x) >= lo_key) z += __float2ull_rz(expf(x - mx) * FIX_ONE);
     });
-    z = warp_sum_u64(z);
-    if (lane == 0) sh.red[warp] = z;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long s = 0;
-      for (int w = 0; w < NWARPS; ++w) s += sh.red[w];
-      unsigned long long tgt = (unsigned long long)ceil((double)top_p * (double)s);
-      if (tgt < 1ull) tgt = 1ull;
-      if (tgt > s) tgt = s;
-      sh.bcast[0] = tgt;
-    }
-    __syncthreads();
-    unsigned long long remaining = sh.bcast[0];
-    __syncthreads();
+    const unsigned long long s = cluster_sum_u64(sh, sl, block_sum_u64(sh, z));
+    unsigned long long remaining = (unsigned long long)ceil((double)top_p * (double)s);
+    if (remaining < 1ull) remaining = 1ull;
+    if (remaining > s) remaining = s;
     unsigned prefix = 0u;
     for (int level = 0; level < 4; ++level) {
       const int shift = 24 - 8 * level;
-      const int dgt = radix_level<true>(sh, row, V, T, mx, lo_key, prefix, shift, remaining);
+      const int dgt = radix_level<true>(sh, sl, T, mx, lo_key, prefix, shift, remaining);
       prefix = (prefix << 8) | (unsigned)dgt;
     }
     lo_key = prefix > lo_key ? prefix : lo_key;
   }
 
   // ---- draw: the inverse CDF in index order.  The row is cut into stretches of `bs` entries (at
-  // most MAX_BLOCKS of them); warps sum the kept mass of each stretch, one thread finds the
-  // stretch the target falls into, one warp walks that stretch 32 entries at a time.
+  // most MAX_BLOCKS of them); stretch b belongs to CTA b % nranks, whose warps sum its kept mass;
+  // every CTA then gathers all the sums and finds the stretch the target falls into; the first CTA
+  // walks that stretch 32 entries at a time.
   const int bs = 1024 * ((V + 1024 * MAX_BLOCKS - 1) / (1024 * MAX_BLOCKS));
   const int nblk = (V + bs - 1) / bs;
   auto mass_at = [&](int i) -> unsigned long long {
@@ -245,7 +360,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     const float x = row[i] / T;
     return ordered_key(x) >= lo_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
   };
-  for (int b = warp; b < nblk; b += NWARPS) {
+  for (int b = (int)sl.rank + (int)sl.nranks * warp; b < nblk; b += (int)sl.nranks * NWARPS) {
     unsigned long long part = 0;
     for (int c0 = b * bs; c0 < (b + 1) * bs; c0 += 1024) {
 #pragma unroll 8
@@ -254,55 +369,71 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     part = warp_sum_u64(part);
     if (lane == 0) sh.blk[b] = part;
   }
+  cluster_barrier();  // every stretch's mass is with its owner
+  for (int b = threadIdx.x; b < nblk; b += THREADS) {
+    const uint32_t owner = (uint32_t)b % sl.nranks;
+    if (owner != sl.rank) sh.blk[b] = ld_cluster_u64(in_cta(sm32(&sh.blk[b]), owner));
+  }
+  cluster_barrier();  // gathered (and nobody reads this CTA's shared memory after this)
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
     unsigned long long total = 0;
-    for (int b = 0; b < nblk; ++b) total += sh.blk[b];
+    for (int b = threadIdx.x; b < nblk; b += 32) total += sh.blk[b];
+    total = warp_sum_u64(total);
     const unsigned long long rnd = splitmix64(rand_keys ? rand_keys[r] : 0ull);
     const unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
-    int b_sel = nblk - 1;
     unsigned long long before = 0;
-    for (int b = 0; b < nblk; ++b) {
-      if (target < before + sh.blk[b]) {
-        b_sel = b;
-        break;
-      }
-      before += sh.blk[b];
+    int b_sel = warp_find<false>(nblk, [&](int i) { return sh.blk[i]; }, target, before);
+    if (b_sel < 0) {  // (cannot happen: target < total)
+      b_sel = nblk - 1;
+      before = total - sh.blk[nblk - 1];
     }
-    sh.bcast[0] = target - before;
-    sh.bcast[1] = total;
-    sh.bcast[2] = (unsigned long long)b_sel;
+    if (threadIdx.x == 0) {
+      sh.bcast[0] = target - before;
+      sh.bcast[1] = total;
+      sh.bcast[2] = (unsigned long long)b_sel;
+    }
   }
   __syncthreads();
   const int b_sel = (int)sh.bcast[2];
   const unsigned long long total = sh.bcast[1];
-  if (warp == 0) {
+  if (sl.rank == 0) {
+    // the chosen stretch, 1,024 entries at a time: every thread works out two masses (all reads in
+    // flight at once), then one warp finds where the running mass passes what is left of the target
+    unsigned long long* sel = &sh.hist[0][0];  // 1,024 entries (the histograms are done with)
     unsigned long long rem = sh.bcast[0];
-    int tok = -1, last_kept = -1;
     const int s_begin = b_sel * bs, s_end = min(V, s_begin + bs);
-    for (int base = s_begin; base < s_end && tok < 0; base += 32) {
-      const unsigned long long w = mass_at(base + lane);
-      unsigned long long incl = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += t;
+    int tok = -1;
+    for (int c0 = s_begin; c0 < s_end && tok < 0; c0 += 1024) {
+      __syncthreads();
+      sel[threadIdx.x] = mass_at(c0 + threadIdx.x < s_end ? c0 + threadIdx.x : V);
+      sel[threadIdx.x + THREADS] = mass_at(c0 + THREADS + threadIdx.x < s_end ? c0 + THREADS + threadIdx.x : V);
+      __syncthreads();
+      if (warp == 0) {
+        unsigned long long before = 0;
+        const int at = warp_find<false>(1024, [&](int i) { return sel[i]; }, rem, before);
+        if (lane == 0) {
+          unsigned long long chunk = 0;
+          if (at < 0)
+            for (int i = 0; i < 1024; ++i) chunk += sel[i];  // (only a stretch longer than 1,024 gets here)
+          sh.bcast[0] = at >= 0 ? (unsigned long long)(c0 + at) : ~0ull;
+          sh.bcast[1] = rem - chunk;
+        }
       }
-      const unsigned hit = __ballot_sync(0xffffffffu, w > 0 && incl > rem);
-      const unsigned kept = __ballot_sync(0xffffffffu, w > 0);
-      if (kept) last_kept = base + 31 - __clz(kept);
-      if (hit) {
-        tok = base + __ffs(hit) - 1;
-      } else {
-        rem -= __shfl_sync(0xffffffffu, incl, 31);
-      }
+      __syncthreads();
+      if (sh.bcast[0] != ~0ull) tok = (int)sh.bcast[0];
+      rem = sh.bcast[1];
     }
-    if (tok < 0) tok = last_kept >= 0 ? last_kept : 0;
-    if (lane == 0) out_tokens[r] = tok;
+    if (tok < 0) {  // (cannot happen: the target is below the stretch's mass) the last kept entry of the stretch
+      for (int i = s_end - 1; i >= s_begin && tok < 0; --i)
+        if (mass_at(i) > 0) tok = i;
+      if (tok < 0) tok = 0;
+    }
+    if (threadIdx.x == 0) out_tokens[r] = tok;
   }
   if (prow) {
     const float inv = 1.f / (float)total;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
+    for (int i = sl.lo + threadIdx.x; i < sl.hi; i += THREADS) {
       const float x = row[i] / T;
       const unsigned long long w = ordered_key(x) >= lo_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
       prow[i] = (float)w * inv;
@@ -361,8 +492,31 @@ KVF_API int kvf_sample_f32(const float* logits, long long ld, int R, int V, cons
                            int* out_tokens, float* probs_out, cudaStream_t st) {
   if (R <= 0) return 0;
   if (V <= 0) return (int)cudaErrorInvalidValue;
-  return launch(sample_kernel, dim3(R), dim3(THREADS), 0, st, logits, ld, V, temps, top_ks, top_ps, rand_keys,
-                out_tokens, probs_out);
+  // a cluster per row: as many CTAs (a power of two up to 8) as the row has stretches of 8,192 entries
+  // ... as long as all the clusters fit the device at once (two CTAs per SM)
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  int c = 1;
+  while (c < MAX_CLUSTER && (long long)c * 8192 < V && (long long)2 * c * R <= 2ll * sms) c <<= 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(c, R);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = c;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, temps, top_ks, top_ps, rand_keys, out_tokens, probs_out);
 }
 
 // Greedy tokens of float logits [R, V] (row stride ld): the highest logit, the lowest index
