@@ -368,7 +368,7 @@ def run_kernel_only(args, cfg) -> dict:
 
     pk = peaks()
     dev = "cuda"
-    nh, nkv, d, bs = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, 16
+    nh, nkv, d, bs = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, args.block_size
     if args.only == "attention":
         b, ctx = args.batch, args.context
         nblk = b * (-(-ctx // bs))
@@ -496,6 +496,7 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm", "load"], help="run one part alone and print a short line (for profiling)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
+    ap.add_argument("--block-size", type=int, default=16, help="with --only attention / attention-prefill: tokens per page")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="with --only decode: tokens already in each cache")

@@ -73,7 +73,8 @@ struct TcAttnParams {
   int nh, nkv, block_size, bs_shift;
   int window;
   float scale_log2;
-  int use_tma;     // pages are multiples of 16 keys: K and V tiles come as tensor-map boxes of [16][64]
+  int use_tma;     // pages are multiples of 16 keys: K and V tiles come as tensor-map boxes of [box_rows][64]
+  int box_rows;    // 16, 32 or 64: the largest of them that divides the page
   int total_rows;  // rows of the cache seen as [rows][64]: a box from this row reads zeros
 };
 
@@ -138,6 +139,16 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "r"(accumulate)
+      : "memory");
+}
+// The same with the accumulate flag known when compiling (no predicate to set up at run time).
+template <int ACC>
+__device__ __forceinline__ void umma_c(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t id) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "n"(ACC)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -353,7 +364,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
     };
     if (p.use_tma) {
-      // A tile is four pages' worth of keys: eight boxes requested by one lane, which the copy
+      // A tile is 64 / box_rows boxes of K and as many of V, one pair per lane, which the copy
       // engine lands in the swizzled layout and counts on the stage's barrier.  Only a tile that
       // reaches past the context inside a live page (whatever lies there must not be read: the
       // last tile of the sequence, at most) goes the slow way, which zero-fills by key.
@@ -364,14 +375,14 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         if (t >= KV_STAGES) ok = __all_sync(0xffffffffu, bar_wait(kv_empty0 + 8 * s, ((t / KV_STAGES) - 1) & 1, p.err));
         if (!ok) break;
         const int t0 = kv_lo + t * BN;
-        const bool ragged = t0 + BN > ctx && (ctx & 15) != 0;
+        const bool ragged = t0 + BN > ctx && (ctx & (p.box_rows - 1)) != 0;
         if (!ragged) {
-          // lane j brings page j of the tile (its K box and its V box)
+          // lane j brings box j of the tile (box_rows keys of one page: a K box and a V box)
           const uint32_t bar = kv_full0 + 8 * s, ks = kv_s + s * 2 * KV_BYTES, vs = ks + KV_BYTES;
           if (lane == 0) bar_expect_tx(bar, 2 * KV_BYTES);
           __syncwarp();
-          if (lane < BN / 16) {
-            const int key0 = t0 + 16 * lane;
+          if (lane < BN / p.box_rows) {
+            const int key0 = t0 + p.box_rows * lane;
             int blk = -1, off = 0;
             if (key0 < ctx) {
               if (p.bs_shift >= 0) {
@@ -385,8 +396,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const int row = blk >= 0 ? (blk * p.nkv + kvh) * p.block_size + off : p.total_rows;
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
-              tma_load_2d(ks + h * KV_HALF + lane * 2048, &map_k, 64 * h, row, bar);
-              tma_load_2d(vs + h * KV_HALF + lane * 2048, &map_v, 64 * h, row, bar);
+              tma_load_2d(ks + h * KV_HALF + lane * p.box_rows * 128, &map_k, 64 * h, row, bar);
+              tma_load_2d(vs + h * KV_HALF + lane * p.box_rows * 128, &map_v, 64 * h, row, bar);
             }
           }
         } else {
@@ -438,44 +449,59 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
   } else if (live && warp == MMA_WARP) {
     if (lane == 0) {
-      // ---- MMA issuer: S(t+1) goes out before P(t) V(t), so the softmax never waits for it
+      // ---- MMA issuer.  When P(t) arrives its group waits for S(t+2) and for nothing else, so S(t+2)
+      // goes out first (its buffer was read before P(t) was written) and P(t) V(t) after it; whether
+      // K(t+2) has landed is asked while the softmax of tile t still runs.  Descriptors are made
+      // once; a tile's differ from them by its stage and k-step (the address field counts 16-byte
+      // units and cannot carry out of its 14 bits: shared memory ends below 256 KB).
       constexpr uint32_t id_s = idesc(BN, 0), id_o = idesc(64, 1);
-      auto issue_s = [&](int t) {
+      constexpr uint32_t STAGE_UNITS = (2 * KV_BYTES) >> 4;
+      const uint64_t q_d = sdesc(q_s), k_d = sdesc(kv_s), v_d = sdesc(kv_s + KV_BYTES), p_d = sdesc(p_s);
+      auto issue_s = [&](int t, int stage) {
         const uint32_t dst = tmem_s + (uint32_t)((t & 1) * BN);
+        const uint64_t kd = k_d + (uint32_t)stage * STAGE_UNITS;
+        umma_c<0>(dst, q_d, kd, id_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)  // k-steps 0..3 in the first half of the tiles, 4..7 in the second
-          umma(dst, sdesc(q_s + (kk >> 2) * Q_HALF) + 2 * (kk & 3), sdesc(kv_s + (t % KV_STAGES) * 2 * KV_BYTES + (kk >> 2) * KV_HALF) + 2 * (kk & 3), id_s, kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk)  // k-steps 0..3 in the first half of the tiles, 4..7 in the second
+          umma_c<1>(dst, q_d + (((kk >> 2) * Q_HALF) >> 4) + 2 * (kk & 3), kd + (((kk >> 2) * KV_HALF) >> 4) + 2 * (kk & 3), id_s);
         umma_commit(s_full0 + 8 * (t & 1));
       };
       bool ok = bar_wait(q_full, 0, p.err);
       if (ok) ok = bar_wait(kv_full0, 0, p.err);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        issue_s(0);
+        issue_s(0, 0);
       }
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        if (t + 1 < n_tiles) {
-          // the S buffer of tile t+1 was read by the softmax of tile t-1 (P(t-1) arrived before P(t-1) V)
-          ok = bar_wait(kv_full0 + 8 * ((t + 1) % KV_STAGES), ((t + 1) / KV_STAGES) & 1, p.err);
-          if (!ok) break;
+      if (ok && n_tiles > 1) {
+        ok = bar_wait(kv_full0 + 8, 0, p.err);
+        if (ok) {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(t + 1);
+          issue_s(1, 1);
         }
-        ok = bar_wait(p_full0 + 8 * (t & 1), (t >> 1) & 1, p.err);  // P(t) is in shared memory, O has been rescaled
+      }
+      int st_s = 2 % KV_STAGES, st_pv = 0;  // the stages of tile t+2 and of tile t
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const bool more = t + 2 < n_tiles;
+        if (more) ok = bar_wait(kv_full0 + 8 * st_s, ((t + 2) / KV_STAGES) & 1, p.err);
+        if (ok) ok = bar_wait(p_full0 + 8 * (t & 1), (t >> 1) & 1, p.err);  // P(t) is in shared memory, O has been rescaled
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t vs = kv_s + (t % KV_STAGES) * 2 * KV_BYTES + KV_BYTES;
-        const uint64_t pd = sdesc(p_s + (t & 1) * P_BYTES);
+        if (more) {
+          issue_s(t + 2, st_s);
+          st_s = st_s + 1 == KV_STAGES ? 0 : st_s + 1;
+        }
+        const uint64_t vd = v_d + (uint32_t)st_pv * STAGE_UNITS, pd = p_d + (uint32_t)(t & 1) * (P_BYTES >> 4);
+        const uint32_t od = tmem_o + (uint32_t)((t & 1) * D);
 #pragma unroll
         for (int h = 0; h < HALVES; ++h) {  // 64 output dims per half of V
+          // A: 16 keys of P = 32 bytes along the row; B: 16 keys of V = 16 rows of 128 bytes
+          umma(od + 64 * h, pd, vd + ((h * KV_HALF) >> 4), id_o, t > 1 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            // A: 16 keys of P = 32 bytes along the row; B: 16 keys of V = 16 rows of 128 bytes
-            umma(tmem_o + (uint32_t)((t & 1) * D + 64 * h), pd + 2 * kk, sdesc(vs + h * KV_HALF + kk * 16 * 128), id_o, (t > 1 || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 1; kk < BN / 16; ++kk) umma_c<1>(od + 64 * h, pd + 2 * kk, vd + ((h * KV_HALF + kk * 16 * 128) >> 4), id_o);
         }
-        umma_commit(pv_done0 + 8 * (t & 1));         // O[t&1] holds tiles t&1, .., t; P buffer t&1 may be rewritten
-        umma_commit(kv_empty0 + 8 * (t % KV_STAGES));  // and the stage may be refilled
+        umma_commit(pv_done0 + 8 * (t & 1));  // O[t&1] holds tiles t&1, .., t; P buffer t&1 may be rewritten
+        umma_commit(kv_empty0 + 8 * st_pv);   // and the stage may be refilled
+        st_pv = st_pv + 1 == KV_STAGES ? 0 : st_pv + 1;
       }
     }
   } else if (live && warp < SOFTMAX_WARPS) {
@@ -599,13 +625,13 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// The cache as [rows][d] bfloat16; boxes of [16][64], 128-byte swizzle, zeros past the end.
-int cache_map(CUtensorMap* map, const void* ptr, long long rows, int d) {
+// The cache as [rows][d] bfloat16; boxes of [box_rows][64], 128-byte swizzle, zeros past the end.
+int cache_map(CUtensorMap* map, const void* ptr, long long rows, int d, int box_rows) {
   EncodeTiledFn fn = encode_tiled();
   if (!fn) return (int)cudaErrorNotSupported;
   const cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)d * 2};
-  const cuuint32_t box[2] = {64u, 16u};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -644,13 +670,14 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
   p.scale_log2 = scale * 1.4426950408889634f;
   // pages of a multiple of 16 keys come in as tensor-map boxes; other page sizes key by key
   const long long rows = num_blocks * nkv * block_size;
-  p.use_tma = (block_size % 16 == 0) && rows < (1ll << 31) - 16 && ((((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) == 0;
+  p.use_tma = (block_size % 16 == 0) && rows < (1ll << 31) - 64 && ((((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) == 0;
   p.total_rows = (int)(p.use_tma ? rows : 0);
+  p.box_rows = block_size % 64 == 0 ? 64 : block_size % 32 == 0 ? 32 : 16;
   CUtensorMap mk, mv;
   memset(&mk, 0, sizeof(mk));
   memset(&mv, 0, sizeof(mv));
   if (p.use_tma) {
-    if (cache_map(&mk, kcache, rows, d) || cache_map(&mv, vcache, rows, d)) p.use_tma = 0;
+    if (cache_map(&mk, kcache, rows, d, p.box_rows) || cache_map(&mv, vcache, rows, d, p.box_rows)) p.use_tma = 0;
   }
   const int g = nh / nkv, tq = BM / g;
   const dim3 grid(nkv, B, (max_q_len + tq - 1) / tq);

@@ -417,7 +417,7 @@ def test_paged_attention_mma(ops, nh, nkv, d, bs, ctx_lens, q_lens):
 
 # ---- the tcgen05 kernel (bfloat16, head size 64, many queries)
 
-TC_SHAPES = MMA_SHAPES + [(4, 4, 64, 16), (16, 1, 64, 32), (4, 4, 128, 16), (8, 1, 128, 48)]
+TC_SHAPES = MMA_SHAPES + [(4, 4, 64, 16), (16, 1, 64, 32), (4, 4, 128, 16), (8, 1, 128, 48), (8, 2, 64, 64), (8, 2, 128, 64), (4, 2, 64, 128)]
 
 
 @pytest.mark.parametrize("nh,nkv,d,bs", TC_SHAPES)
