@@ -204,6 +204,24 @@ __device__ __forceinline__ uint32_t pk(float a, float b) {
 // MASK: some key of the tile may be hidden from some row of the warp.  Returns the tile's sum of
 // P and stores P (bfloat16) into the row of the A-operand tile at p_row (a shared address of
 // the row's first byte; chunk c of the row lies at p_row + ((c ^ (r & 7)) << 4)).
+// Two floats side by side in a 64-bit register, for the packed fma and add of sm_100.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 template <bool MASK>
 __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)[32], float& m_ref, float& corr,
                                               float scale_log2, int first, int last, uint32_t p_row, int r7) {
@@ -211,8 +229,9 @@ __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    if (!MASK || (j >= first && j <= last)) mx = fmaxf(mx, __uint_as_float(va[j]));
-    if (!MASK || (j + 32 >= first && j + 32 <= last)) mx = fmaxf(mx, __uint_as_float(vb[j]));
+    const float a = (!MASK || (j >= first && j <= last)) ? __uint_as_float(va[j]) : -INFINITY;
+    const float b = (!MASK || (j + 32 >= first && j + 32 <= last)) ? __uint_as_float(vb[j]) : -INFINITY;
+    mx = fmaxf(mx, fmaxf(a, b));  // (a three-input maximum)
   }
   mx *= scale_log2;  // scale > 0
   corr = 1.f;
@@ -221,7 +240,8 @@ __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)
     m_ref = mx;
   }
   const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-  float sum0 = 0.f, sum1 = 0.f;
+  const uint64_t scale2 = pack2(scale_log2, scale_log2), neg_m2 = pack2(-m_use, -m_use);
+  uint64_t sum_a = pack2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     uint32_t(&v)[32] = half ? vb : va;
@@ -229,14 +249,17 @@ __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)
 #pragma unroll
     for (int j = 0; j < 32; j += 2) {
       const int c = half * 32 + j;
-      float e0 = ex2(fmaf(__uint_as_float(v[j]), scale_log2, -m_use));
-      float e1 = ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, -m_use));
+      float x0, x1;
+      unpack2(fma2(pack2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), scale2, neg_m2), x0, x1);
+      float e0 = ex2(x0), e1 = ex2(x1);
       if (MASK) {
         if (c < first || c > last) e0 = 0.f;
         if (c + 1 < first || c + 1 > last) e1 = 0.f;
       }
-      sum0 += e0;
-      sum1 += e1;
+      if (j & 2)
+        sum_b = add2(sum_b, pack2(e0, e1));
+      else
+        sum_a = add2(sum_a, pack2(e0, e1));
       w[j >> 1] = pk(e0, e1);
     }
 #pragma unroll
@@ -247,7 +270,9 @@ __device__ __forceinline__ float softmax_tile(uint32_t (&va)[32], uint32_t (&vb)
                    : "memory");
     }
   }
-  return sum0 + sum1;
+  float s0, s1;
+  unpack2(add2(sum_a, sum_b), s0, s1);
+  return s0 + s1;
 }
 
 template <int D>
