@@ -68,6 +68,7 @@ struct TcAttnParams {
   const int* block_tables;
   const int* qsl;
   const int* ctx_lens;
+  const int* work;  // n_work pairs (sequence or -1, first query of the tile), or null: the grid's y and z say which
   int* err;
   int q_stride, out_stride, bt_stride;
   int nh, nkv, block_size, bs_shift;
@@ -302,13 +303,18 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // grid (kv heads, sequences, row blocks): CTAs start in the order of their index with x
   // fastest, so all heads of the longest walk start first, then the next longest, ...
-  const int b = blockIdx.y, kvh = blockIdx.x;
+  const int kvh = blockIdx.x;
   const int g = p.nh / p.nkv;
   const int tq = BM / g;
-  const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
-  const int ctx = p.ctx_lens[b];
-  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * tq;  // the longest walks first
+  // which tile of queries: from the list (made on the host, longest walk first), else from the grid
+  const int b = p.work ? p.work[2 * blockIdx.y] : (int)blockIdx.y;
+  const int q0 = p.work ? p.work[2 * blockIdx.y + 1] : (int)(gridDim.z - 1 - blockIdx.z) * tq;  // the longest walks first
+  const int q_begin = b >= 0 ? p.qsl[b] : 0, q_len = b >= 0 ? p.qsl[b + 1] - q_begin : 0;
+  const int ctx = b >= 0 ? p.ctx_lens[b] : 0;
   const bool live = q_len > 0 && ctx > 0 && q0 < q_len;  // uniform over the CTA
+  // A CTA without a tile leaves at once; the grid's first CTA stays for the dependency wait, so
+  // the grid does not complete before its predecessor.
+  if (!live && (blockIdx.x | blockIdx.y | blockIdx.z) != 0) return;
   const int n_tok = live ? min(tq, q_len - q0) : 0;
   const int p_first = ctx - q_len + q0;
   const int kv_hi = p_first + n_tok;
@@ -679,7 +685,7 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
                                              const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                              int max_q_len, int q_stride, int out_stride, int bt_stride, int nh,
                                              int nkv, int d, int block_size, long long num_blocks, float scale,
-                                             int window, int* err, cudaStream_t st) {
+                                             int window, const int* work, int n_work, int* err, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || nh / nkv > BM || block_size <= 0 || num_blocks <= 0) return (int)cudaErrorInvalidValue;
   if ((q_stride & 7) || (out_stride & 7) || ((((uintptr_t)q) | ((uintptr_t)out)) & 15)) return (int)cudaErrorInvalidValue;
@@ -687,6 +693,7 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
   TcAttnParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
   p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens; p.err = err;
+  p.work = work;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.bs_shift = -1;
@@ -705,6 +712,7 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
     if (cache_map(&mk, kcache, rows, d, p.box_rows) || cache_map(&mv, vcache, rows, d, p.box_rows)) p.use_tma = 0;
   }
   const int g = nh / nkv, tq = BM / g;
-  const dim3 grid(nkv, B, (max_q_len + tq - 1) / tq);
+  if (work && (n_work <= 0 || n_work > 65535)) return (int)cudaErrorInvalidValue;
+  const dim3 grid(nkv, work ? n_work : B, work ? 1 : (max_q_len + tq - 1) / tq);
   return d == 64 ? launch_tc_attn<64>(mk, mv, p, grid, st) : launch_tc_attn<128>(mk, mv, p, grid, st);
 }

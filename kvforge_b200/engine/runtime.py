@@ -26,6 +26,9 @@ class Runtime:
         self.lazy = bool(lazy)
         self._buffers: dict[tuple, torch.Tensor] = {}
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # Tile sizes (queries of one sequence per CTA) of kernels that want a list of query tiles with
+        # every step; parts add theirs in ``bind``, the step function fills ``StepContext.query_tiles``.
+        self.query_tile_sizes: set[int] = set()
         self.capturing = False
         self.graphs_captured = False  # captured graphs hold buffer addresses: no buffer may move afterwards
 
@@ -89,6 +92,9 @@ class StepContext:
     token_feedback: torch.Tensor | None = None
     # Upper bound on any context (fixes grid sizes of captured decode steps).
     context_bound: int = 0
+    # Per registered tile size: (int32 pairs (sequence or -1, first query of the tile), longest key
+    # walk first; how many of them a kernel has to launch).  Empty when every sequence brings one token.
+    query_tiles: dict = field(default_factory=dict)
     extras: dict = field(default_factory=dict)
 
     @property

@@ -77,6 +77,7 @@ class _Layout:
     width: int
     n_groups: int
     r_cap: int
+    tile_sizes: tuple[int, ...] = ()
     off: dict[str, int] = field(default_factory=dict)
     total: int = 0
 
@@ -95,7 +96,14 @@ class _Layout:
         ):
             self.off[name] = o
             o += _align(size)
+        for tq in self.tile_sizes:  # pairs (sequence, first query) per tile of tq queries
+            self.off[f"qtiles_{tq}"] = o
+            o += _align(2 * self.tile_cap(tq))
         self.total = o
+
+    def tile_cap(self, tq: int) -> int:
+        """The most tiles of ``tq`` queries that ``n_cap`` tokens in ``b_cap`` sequences can make."""
+        return self.n_cap // tq + self.b_cap
 
 
 class ModelRunner:
@@ -133,6 +141,7 @@ class ModelRunner:
         self._host: torch.Tensor | None = None
         self._dev: torch.Tensor | None = None
         self._copy_done: torch.cuda.Event | None = None
+        self._tile_counts: dict[int, int] = {}
         # made once for the widest step there can be, so its address never changes
         self._ensure(self._layout(rt.max_tokens, rt.max_seqs, self.max_width, rt.max_tokens).total)
         # tokens sampled on the device that may feed the next step (set by whoever samples)
@@ -142,7 +151,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ buffers
     def _layout(self, n_cap: int, b_cap: int, width: int, r_cap: int) -> _Layout:
-        return _Layout(n_cap, b_cap, max(1, width), self.n_groups, max(1, r_cap))
+        return _Layout(n_cap, b_cap, max(1, width), self.n_groups, max(1, r_cap), tuple(sorted(self.rt.query_tile_sizes)))
 
     def _ensure(self, total: int) -> None:
         if total <= self._cap:
@@ -215,10 +224,41 @@ class ModelRunner:
         if len(rows) > lay.r_cap:
             raise RuntimeError("more logit rows than the layout holds")
         host[o["logit_rows"] : o["logit_rows"] + len(rows)] = rows
+        self._tile_counts = self._fill_query_tiles(host, lay, nb) if max_q > 1 else {}
         return n, nb, len(rows), max_q, max_ctx
 
-    def _context(self, lay: _Layout, n: int, nb: int, r: int, max_q: int, max_ctx: int, bound: int) -> StepContext:
+    def _fill_query_tiles(self, host: np.ndarray, lay: _Layout, nb: int) -> dict[int, int]:
+        """For every registered tile size the step's tiles of queries as (sequence, first query),
+        the one with the longest walk over the keys first; returns how many there are."""
+        o = lay.off
+        starts = host[o["qsl"] : o["qsl"] + nb + 1].astype(np.int64)
+        q_lens = starts[1:] - starts[:-1]
+        ctx = host[o["ctx"] : o["ctx"] + nb].astype(np.int64)
+        counts: dict[int, int] = {}
+        for tq in lay.tile_sizes:
+            cap = lay.tile_cap(tq)
+            tiles = host[o[f"qtiles_{tq}"] : o[f"qtiles_{tq}"] + 2 * cap].reshape(cap, 2)
+            per_seq = -(-q_lens // tq)
+            total = int(per_seq.sum())
+            seq = np.repeat(np.arange(nb), per_seq)
+            q0 = (np.arange(total) - np.repeat(np.cumsum(per_seq) - per_seq, per_seq)) * tq
+            last_key = ctx[seq] - q_lens[seq] + np.minimum(q_lens[seq], q0 + tq)
+            order = np.argsort(-last_key, kind="stable")
+            tiles[:total, 0] = seq[order]
+            tiles[:total, 1] = q0[order]
+            tiles[total:, 0] = -1
+            tiles[total:, 1] = 0
+            counts[tq] = total
+        return counts
+
+    def _context(self, lay: _Layout, n: int, nb: int, r: int, max_q: int, max_ctx: int, bound: int, all_tiles: bool = False) -> StepContext:
         dev, host, o = self._dev, self._host.numpy(), lay.off
+        # a captured step launches every tile its layout can hold (the list says which are live)
+        tiles = {}
+        if max_q > 1:
+            for tq in lay.tile_sizes:
+                count = lay.tile_cap(tq) if all_tiles else self._tile_counts.get(tq, 0)
+                tiles[tq] = (dev[o[f"qtiles_{tq}"] : o[f"qtiles_{tq}"] + 2 * lay.tile_cap(tq)], count)
         view = lambda name, size: dev[o[name] : o[name] + size]  # noqa: E731
         tables, slots = [], []
         for g in range(self.n_groups):
@@ -248,6 +288,7 @@ class ModelRunner:
             h_context_lens=host[o["ctx"] : o["ctx"] + nb].copy(),
             h_state_slots=host[o["state_slots"] : o["state_slots"] + nb].copy(),
             context_bound=bound,
+            query_tiles=tiles,
         )
 
     # ------------------------------------------------------------------ running
@@ -335,7 +376,7 @@ class ModelRunner:
     def _capture(self, key: tuple[int, int, int], lay: _Layout):
         n_cap, b_cap, reach = key
         # one token per sequence: the decode form; else a sequence may bring up to all the tokens
-        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if n_cap == b_cap else n_cap, reach, bound=reach)
+        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if n_cap == b_cap else n_cap, reach, bound=reach, all_tiles=True)
         # one eager run first: sizes every buffer and loads every kernel outside the capture
         self.model.forward(ctx)
         torch.cuda.synchronize()

@@ -26,7 +26,7 @@ _SIGNATURES = {
     "kvf_cast_from_float_{s}": "pplp",
     "kvf_paged_attention_generic_{s}": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
-    "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipp",
+    "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppip",
     "kvf_paged_attention_decode_rope_tma_bf16": "pilppp" "pppppp" "iiiiiii" "l" "f" "iiii" "ppppip",
@@ -368,6 +368,14 @@ def mma_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decod
     return dtype == torch.bfloat16 and d in (64, 128) and g <= (16 if decode_form else 64)
 
 
+TC_ATTN_ROWS = 128  # (token, head of a group) rows of a CTA of the tcgen05 attention kernel
+
+
+def tcgen05_query_tile(nh: int, nkv: int) -> int:
+    """Queries of one sequence that a CTA of the tcgen05 attention kernel takes."""
+    return max(1, TC_ATTN_ROWS // max(1, nh // nkv))
+
+
 def tcgen05_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, decode_form: bool) -> bool:
     """Whether the tcgen05 kernel (``csrc/attention_tcgen05.cu``) takes this shape: many queries
     (not the decode form), bfloat16, head size 64 or 128."""
@@ -404,6 +412,7 @@ def paged_attention(
     kernel: str = "auto",
     err: torch.Tensor | None = None,
     cluster: bool = True,
+    query_tiles: tuple[torch.Tensor, int] | None = None,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
@@ -416,7 +425,9 @@ def paged_attention(
     elsewhere; ``"generic"``, ``"mma"``, ``"tma"`` and ``"tcgen05"`` force one (tests).  ``err``: the
     device error flag (a bounded wait inside a kernel raises it).  ``cluster``: the TMA decode kernel
     merges up to 16 key ranges through a thread-block cluster's shared memory (else through the
-    scratch and the tickets).
+    scratch and the tickets).  ``query_tiles``: for the tcgen05 kernel, an int32 array of (sequence or
+    -1, first query) pairs, one per tile of ``tcgen05_query_tile`` queries, and how many of them to
+    launch; without it the grid spans every sequence times the tiles of the longest query run.
     """
     s = _suffix(q.dtype)
     check_head_dim(d)
@@ -473,11 +484,17 @@ def paged_attention(
         use_tc = True
     if use_tc:
         name = "kvf_paged_attention_tcgen05_bf16"
+        tiles, n_tiles = None, 0
+        if query_tiles is not None and 0 < query_tiles[1] <= 65535:
+            tiles, n_tiles = query_tiles
+            _need(tiles, torch.int32, "query_tiles")
+            if tiles.numel() < 2 * n_tiles:
+                raise ValueError("paged_attention: the list of query tiles is shorter than the launch")
         _check(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, max_q_len, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]),
-                float(scale), int(window), _ptr(err), _stream(),
+                float(scale), int(window), _ptr(tiles), n_tiles, _ptr(err), _stream(),
             ),
             name,
         )  # fmt: skip

@@ -97,6 +97,11 @@ class PagedAttention(Mixer):
         self.w_o = weights["o_proj.weight"].contiguous()
         # counters of finished key ranges per (sequence, kv head) for the decode form: zero between launches
         self._tickets = torch.zeros(max(1, rt.max_seqs) * self.nkv, dtype=torch.int32, device=rt.device)
+        # the kernel of prompts and mixed batches takes its tiles of queries from a list made with the step
+        self._query_tile = None
+        if ops.tcgen05_attention_supported(rt.dtype, self.nh, self.nkv, self.d, False):
+            self._query_tile = ops.tcgen05_query_tile(self.nh, self.nkv)
+            rt.query_tile_sizes.add(self._query_tile)
         if self.position_spec is not None and self.position is None:
             self.position = build_part("position", self.position_spec)
             self.position.bind({}, rt)
@@ -183,4 +188,5 @@ class PagedAttention(Mixer):
             ctx.num_seqs, ctx.max_query_len, self.nh, self.nkv, self.d, self.scale,
             window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound, split_size=split,
             err=self.rt.err, cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
+            query_tiles=ctx.query_tiles.get(self._query_tile),
         )  # fmt: skip

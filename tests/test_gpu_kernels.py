@@ -432,6 +432,35 @@ def test_paged_attention_tcgen05(ops, nh, nkv, d, bs, ctx_lens, q_lens):
     assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
 
 
+def test_paged_attention_tcgen05_takes_its_tiles_from_a_list(ops):
+    # the same batch with the grid spanning sequences x tiles, and with a shuffled list of
+    # (sequence, first query) tiles that has dead entries in it
+    nh, nkv, d, bs = 8, 2, 64, 16
+    ctx_lens, q_lens = [300, 64, 65, 130], [300, 2, 65, 1]
+    torch.manual_seed(5)
+    dev = "cuda"
+    kv = [(torch.randn(c, nkv, d).bfloat16(), torch.randn(c, nkv, d).bfloat16()) for c in ctx_lens]
+    kc, vc, bt = (t.to(dev) for t in paged(kv, nkv, d, bs, torch.bfloat16))
+    q = torch.cat([torch.randn(n, nh, d).bfloat16() for n in q_lens]).reshape(-1, nh * d).contiguous().to(dev)
+    qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32).to(dev)
+    cl = torch.tensor(ctx_lens, dtype=torch.int32).to(dev)
+    outs = []
+    tq = ops.tcgen05_query_tile(nh, nkv)
+    pairs = [(b, j * tq) for b, n in enumerate(q_lens) for j in range(-(-n // tq))]
+    g = torch.Generator().manual_seed(1)
+    pairs = [pairs[i] for i in torch.randperm(len(pairs), generator=g).tolist()]
+    listed = pairs[:3] + [(-1, 0)] + pairs[3:] + [(-1, 0), (-1, 0)]
+    tiles = torch.tensor(listed, device=dev, dtype=torch.int32).reshape(-1).contiguous()
+    for query_tiles in (None, (tiles, len(listed))):
+        out = torch.full_like(q, float("nan"))
+        err = err_flag()
+        ops.paged_attention(q, out, kc, vc, bt, qsl, cl, len(q_lens), max(q_lens), nh, nkv, d, d**-0.5, kernel="tcgen05", err=err, query_tiles=query_tiles)
+        assert int(err.sum()) == 0
+        outs.append(out)
+    assert not torch.isnan(outs[1]).any()
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_tcgen05_attention_finds_a_far_key_and_respects_the_window(ops):
     for far in (0, 15, 16, 127, 128, 255, 256, 511, 640):
 
