@@ -62,6 +62,7 @@ struct DecParams {
   int q_stride, out_stride, bt_stride;
   int nh, nkv, block_size;
   int window;
+  int single_only;  // sequences that bring more than one query are left alone (another kernel's)
   int split_size, max_splits, grid_splits;
   int total_rows;  // rows of the cache seen as [rows][D]: a copy from this row reads zeros
   float scale_log2;
@@ -188,7 +189,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   // dead: no query, a range past the context (the merge never reads it), or shared memory that
   // does not start where the swizzle needs it (refused: bit 8 of the error flag)
   const bool aligned = (base & 1023u) == 0;
-  const bool seq_live = q_len > 0 && ctx > 0;  // the same for all ranges of a sequence: for a whole cluster
+  const bool seq_live = (p.single_only ? q_len == 1 : q_len > 0) && ctx > 0;  // the same for all ranges of a sequence: for a whole cluster
   const bool live = seq_live && range_lo < ctx && aligned;
   const int kv_hi = min(ctx, range_lo + p.split_size);
   const int first_seen = max(range_lo, p.window > 0 ? ctx - p.window : 0);  // first key this range may show
@@ -609,8 +610,9 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
             const int* block_tables, const int* qsl, const int* ctx_lens, int B, int q_stride, int out_stride,
             int bt_stride, int nh, int nkv, int d, int block_size, long long num_blocks, float scale, int window,
             int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, int* err,
-            int cluster, cudaStream_t st) {
+            int flags, cudaStream_t st) {
   if (B <= 0) return 0;
+  const int cluster = flags & 1;
   if ((d != 64 && d != 128) || nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh / nkv > 8) return (int)cudaErrorInvalidValue;
   if (block_size <= 0 || block_size % UNIT != 0 || num_blocks <= 0) return (int)cudaErrorInvalidValue;
   const long long rows = num_blocks * nkv * block_size;
@@ -633,6 +635,7 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
   p.part_acc = part_acc; p.part_ml = part_ml; p.tickets = tickets; p.err = err;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.single_only = (flags & 2) ? 1 : 0;
   p.split_size = split_size; p.max_splits = max_splits;
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.total_rows = (int)rows;
@@ -665,18 +668,19 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
 // aligned.  Takes d in {64, 128}, nh/nkv <= 8, block_size a multiple of 16, fewer than 2^31 - 16
 // cache rows; refuses anything else with cudaErrorInvalidValue (the caller has other kernels).
 // `tickets`: B * nkv counters, zero before the first launch and left zero by every launch;
-// launches that share them must not overlap.  cluster != 0: with at most 16 ranges, merge them
+// launches that share them must not overlap.  flags bit 0: with at most 16 ranges, merge them
 // through a thread-block cluster's shared memory instead (scratch and tickets are then unused,
-// unless such a cluster cannot be launched here).
+// unless such a cluster cannot be launched here).  flags bit 1: only sequences that bring exactly
+// one query are computed (the others of a mixed batch belong to the kernel of prompts).
 KVF_API int kvf_paged_attention_decode_tma_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                                 const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                                 int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
                                                 int block_size, long long num_blocks, float scale, int window,
                                                 int split_size, int max_splits, int grid_splits, float* part_acc,
-                                                float* part_ml, int* tickets, int* err, int cluster, cudaStream_t st) {
+                                                float* part_ml, int* tickets, int* err, int flags, cudaStream_t st) {
   return run_dec(q, RopeSource(), out, kcache, vcache, block_tables, qsl, ctx_lens, B, q_stride, out_stride, bt_stride, nh,
                  nkv, d, block_size, num_blocks, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml,
-                 tickets, err, cluster, st);
+                 tickets, err, flags, st);
 }
 
 // The same with the rotation and the cache write of the new token folded in.  qkv_part: float

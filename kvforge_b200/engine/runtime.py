@@ -65,6 +65,18 @@ class Runtime:
 
 
 @dataclass
+class QueryTiles:
+    """A step's tiles of queries for kernels that take ``size`` queries of one sequence per CTA:
+    int32 pairs (sequence or -1, first query of the tile), the longest walk over the keys first."""
+
+    tiles: torch.Tensor  # of all sequences
+    count: int  # how many of them to launch
+    multi: torch.Tensor  # of the sequences that bring more than one query
+    multi_count: int
+    num_single: int  # sequences that bring exactly one query (a captured step: as many as it has sequences)
+
+
+@dataclass
 class StepContext:
     """One step's batch as the parts see it.  All device arrays are int32."""
 
@@ -92,8 +104,7 @@ class StepContext:
     token_feedback: torch.Tensor | None = None
     # Upper bound on any context (fixes grid sizes of captured decode steps).
     context_bound: int = 0
-    # Per registered tile size: (int32 pairs (sequence or -1, first query of the tile), longest key
-    # walk first; how many of them a kernel has to launch).  Empty when every sequence brings one token.
+    # Per registered tile size a ``QueryTiles``.  Empty when every sequence brings one token.
     query_tiles: dict = field(default_factory=dict)
     extras: dict = field(default_factory=dict)
 

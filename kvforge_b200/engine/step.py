@@ -24,7 +24,7 @@ import torch
 from .. import ops
 from ..cache.block_manager import BlockManager
 from ..cache.state_slots import StateSlotPool
-from .runtime import Runtime, StepContext
+from .runtime import QueryTiles, Runtime, StepContext
 
 
 # graphs for shorter contexts than this are not told apart
@@ -96,9 +96,10 @@ class _Layout:
         ):
             self.off[name] = o
             o += _align(size)
-        for tq in self.tile_sizes:  # pairs (sequence, first query) per tile of tq queries
-            self.off[f"qtiles_{tq}"] = o
-            o += _align(2 * self.tile_cap(tq))
+        for tq in self.tile_sizes:  # pairs (sequence, first query) per tile of tq queries: all, and without single tokens
+            for name in (f"qtiles_{tq}", f"qtiles_multi_{tq}"):
+                self.off[name] = o
+                o += _align(2 * self.tile_cap(tq))
         self.total = o
 
     def tile_cap(self, tq: int) -> int:
@@ -141,7 +142,7 @@ class ModelRunner:
         self._host: torch.Tensor | None = None
         self._dev: torch.Tensor | None = None
         self._copy_done: torch.cuda.Event | None = None
-        self._tile_counts: dict[int, int] = {}
+        self._tile_counts: dict[int, tuple[int, int, int]] = {}
         # made once for the widest step there can be, so its address never changes
         self._ensure(self._layout(rt.max_tokens, rt.max_seqs, self.max_width, rt.max_tokens).total)
         # tokens sampled on the device that may feed the next step (set by whoever samples)
@@ -227,28 +228,34 @@ class ModelRunner:
         self._tile_counts = self._fill_query_tiles(host, lay, nb) if max_q > 1 else {}
         return n, nb, len(rows), max_q, max_ctx
 
-    def _fill_query_tiles(self, host: np.ndarray, lay: _Layout, nb: int) -> dict[int, int]:
+    def _fill_query_tiles(self, host: np.ndarray, lay: _Layout, nb: int) -> dict[int, tuple[int, int, int]]:
         """For every registered tile size the step's tiles of queries as (sequence, first query),
-        the one with the longest walk over the keys first; returns how many there are."""
+        the one with the longest walk over the keys first: once for all sequences, once without
+        those that bring a single token.  Returns (tiles, tiles without single tokens, sequences
+        with a single token) per size."""
         o = lay.off
         starts = host[o["qsl"] : o["qsl"] + nb + 1].astype(np.int64)
         q_lens = starts[1:] - starts[:-1]
         ctx = host[o["ctx"] : o["ctx"] + nb].astype(np.int64)
-        counts: dict[int, int] = {}
+        counts: dict[int, tuple[int, int, int]] = {}
         for tq in lay.tile_sizes:
             cap = lay.tile_cap(tq)
-            tiles = host[o[f"qtiles_{tq}"] : o[f"qtiles_{tq}"] + 2 * cap].reshape(cap, 2)
             per_seq = -(-q_lens // tq)
             total = int(per_seq.sum())
             seq = np.repeat(np.arange(nb), per_seq)
             q0 = (np.arange(total) - np.repeat(np.cumsum(per_seq) - per_seq, per_seq)) * tq
             last_key = ctx[seq] - q_lens[seq] + np.minimum(q_lens[seq], q0 + tq)
             order = np.argsort(-last_key, kind="stable")
-            tiles[:total, 0] = seq[order]
-            tiles[:total, 1] = q0[order]
-            tiles[total:, 0] = -1
-            tiles[total:, 1] = 0
-            counts[tq] = total
+            seq, q0 = seq[order], q0[order]
+            multi = q_lens[seq] > 1
+            n_multi = int(multi.sum())
+            for name, s_, q_, n_ in ((f"qtiles_{tq}", seq, q0, total), (f"qtiles_multi_{tq}", seq[multi], q0[multi], n_multi)):
+                tiles = host[o[name] : o[name] + 2 * cap].reshape(cap, 2)
+                tiles[:n_, 0] = s_
+                tiles[:n_, 1] = q_
+                tiles[n_:, 0] = -1
+                tiles[n_:, 1] = 0
+            counts[tq] = (total, n_multi, int((q_lens == 1).sum()))
         return counts
 
     def _context(self, lay: _Layout, n: int, nb: int, r: int, max_q: int, max_ctx: int, bound: int, all_tiles: bool = False) -> StepContext:
@@ -257,8 +264,10 @@ class ModelRunner:
         tiles = {}
         if max_q > 1:
             for tq in lay.tile_sizes:
-                count = lay.tile_cap(tq) if all_tiles else self._tile_counts.get(tq, 0)
-                tiles[tq] = (dev[o[f"qtiles_{tq}"] : o[f"qtiles_{tq}"] + 2 * lay.tile_cap(tq)], count)
+                cap = lay.tile_cap(tq)
+                total, n_multi, n_single = (cap, cap, nb) if all_tiles else self._tile_counts.get(tq, (0, 0, 0))
+                a, m = o[f"qtiles_{tq}"], o[f"qtiles_multi_{tq}"]
+                tiles[tq] = QueryTiles(dev[a : a + 2 * cap], total, dev[m : m + 2 * cap], n_multi, n_single)
         view = lambda name, size: dev[o[name] : o[name] + size]  # noqa: E731
         tables, slots = [], []
         for g in range(self.n_groups):

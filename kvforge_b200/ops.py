@@ -413,6 +413,7 @@ def paged_attention(
     err: torch.Tensor | None = None,
     cluster: bool = True,
     query_tiles: tuple[torch.Tensor, int] | None = None,
+    single_only: bool = False,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
@@ -428,6 +429,8 @@ def paged_attention(
     scratch and the tickets).  ``query_tiles``: for the tcgen05 kernel, an int32 array of (sequence or
     -1, first query) pairs, one per tile of ``tcgen05_query_tile`` queries, and how many of them to
     launch; without it the grid spans every sequence times the tiles of the longest query run.
+    ``single_only`` (TMA decode kernel): of a mixed batch only the sequences that bring exactly one
+    query are computed; the rows of the others are left untouched.
     """
     s = _suffix(q.dtype)
     check_head_dim(d)
@@ -500,7 +503,7 @@ def paged_attention(
         )  # fmt: skip
         return
     use_tma = tickets is not None and tma_decode_supported(q.dtype, nh, nkv, d, block_size, kcache.shape[0])
-    if kernel == "tma" and not use_tma:
+    if (kernel == "tma" or single_only) and not use_tma:
         raise ValueError("the TMA decode kernel does not take this shape (or no tickets were given)")
     if use_tma and kernel in ("auto", "tma"):
         name = "kvf_paged_attention_decode_tma_bf16"
@@ -508,7 +511,7 @@ def paged_attention(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]), float(scale),
-                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(cluster), _stream(),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(bool(cluster)) | (2 if single_only else 0), _stream(),
             ),
             name,
         )  # fmt: skip

@@ -181,12 +181,22 @@ class PagedAttention(Mixer):
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256
+        common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err)
+        args = (q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs)
+        shape = (self.nh, self.nkv, self.d, self.scale)
         if ctx.all_single_query:
             scratch, bound, split = self._scratch(ctx)
+        tiles = ctx.query_tiles.get(self._query_tile)
+        if tiles is not None and tiles.num_single > 0 and ops.tma_decode_supported(q.dtype, self.nh, self.nkv, self.d, ctx.block_size, cache.k.shape[0]):
+            # a mixed batch: the sequences that bring one token go to the decode kernel (key ranges in
+            # parallel), the portions of prompts to the kernel of prompts; each leaves the other's rows alone
+            scratch, bound, split = self._scratch(ctx)
+            ops.paged_attention(*args, 1, *shape, scratch=scratch, max_context=bound, split_size=split, kernel="tma", cluster=False, single_only=True, **common)
+            if tiles.multi_count > 0:
+                ops.paged_attention(*args, ctx.max_query_len, *shape, query_tiles=(tiles.multi, tiles.multi_count), **common)
+            return
         ops.paged_attention(
-            q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens,
-            ctx.num_seqs, ctx.max_query_len, self.nh, self.nkv, self.d, self.scale,
-            window=int(self.window or 0), q_stride=q_stride, scratch=scratch, max_context=bound, split_size=split,
-            err=self.rt.err, cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
-            query_tiles=ctx.query_tiles.get(self._query_tile),
+            *args, ctx.max_query_len, *shape, scratch=scratch, max_context=bound, split_size=split,
+            cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
+            query_tiles=(tiles.tiles, tiles.count) if tiles is not None else None, **common,
         )  # fmt: skip

@@ -566,6 +566,47 @@ def test_tma_decode_finds_a_far_key_and_respects_the_window(ops):
     assert int(err_flag().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,d,bs", [(8, 2, 64, 16), (24, 8, 128, 32)])
+def test_mixed_batch_split_between_the_decode_kernel_and_the_kernel_of_prompts(ops, nh, nkv, d, bs):
+    """Of a mixed batch the decode kernel computes the sequences that bring one token and leaves
+    the rows of the others alone; the kernel of prompts, given the tiles of the others, fills those."""
+    ctx_lens, q_lens = [300, 130, 64, 700, 5, 257], [1, 67, 1, 300, 5, 1]
+    g = torch.Generator().manual_seed(11)
+    kv = [(torch.randn(c, nkv, d, generator=g).bfloat16(), torch.randn(c, nkv, d, generator=g).bfloat16()) for c in ctx_lens]
+    qs = [torch.randn(n, nh, d, generator=g).bfloat16() for n in q_lens]
+    kc, vc, tables = paged(kv, nkv, d, bs, torch.bfloat16, seed=2, junk=(float("nan"), float("nan")))
+    q = dev(torch.cat(qs, 0).reshape(-1, nh * d))
+    starts = [0] + list(torch.tensor(q_lens).cumsum(0))
+    qsl, cl = dev(torch.tensor(starts, dtype=torch.int32)), dev(torch.tensor(ctx_lens, dtype=torch.int32))
+    out = torch.full((q.shape[0], nh * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    scale, split, nseq = 1.0 / math.sqrt(d), 128, len(ctx_lens)
+    sa, sm = ops.attention_scratch_shapes(nseq, nh, d, max(ctx_lens), split)
+    scratch = (torch.empty(sa, device="cuda"), torch.empty(sm, device="cuda"), torch.zeros(nseq * nkv, dtype=torch.int32, device="cuda"))
+    err_flag().zero_()
+    common = (q, out, dev(kc), dev(vc), dev(tables), qsl, cl, nseq)
+    ops.paged_attention(*common, 1, nh, nkv, d, scale, scratch=scratch, max_context=max(ctx_lens), split_size=split, kernel="tma", err=err_flag(), cluster=False, single_only=True)
+    single = [b for b, n in enumerate(q_lens) if n == 1]
+    rows_single = [int(starts[b]) for b in single]
+    rows_multi = [r for b, n in enumerate(q_lens) if n > 1 for r in range(int(starts[b]), int(starts[b + 1]))]
+    assert not torch.isnan(out[rows_single]).any()
+    assert torch.isnan(out[rows_multi]).all()
+    assert int(scratch[2].abs().sum()) == 0
+    tq = ops.tcgen05_query_tile(nh, nkv)
+    pairs = [(b, j * tq) for b, n in enumerate(q_lens) if n > 1 for j in range(-(-n // tq))] + [(-1, 0)]
+    tiles = dev(torch.tensor(pairs, dtype=torch.int32).reshape(-1))
+    before = out[rows_single].clone()
+    ops.paged_attention(*common, max(q_lens), nh, nkv, d, scale, kernel="tcgen05", err=err_flag(), query_tiles=(tiles, len(pairs)))
+    assert torch.equal(out[rows_single], before)
+    assert int(err_flag().sum()) == 0
+    refs = []
+    for (k, v), qq, c, ql in zip(kv, qs, ctx_lens, q_lens):
+        full_q = torch.zeros(c, nh, d)
+        full_q[c - ql :] = qq.float()
+        refs.append(causal_attention(full_q, k.float(), v.float(), scale, None)[c - ql :])
+    ref = torch.cat(refs, 0).reshape(-1, nh * d)
+    assert torch.allclose(out.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
 def test_tma_decode_reads_zeros_for_pages_that_were_given_back(ops):
     """A table entry of -1 (a page the window has passed) is read as zeros, not as page -1."""
     nh, nkv, d, bs, ctx, window = 8, 2, 64, 16, 200, 40
