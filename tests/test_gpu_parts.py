@@ -1,7 +1,8 @@
 """Each part alone against the plain function it stands for; a model whose execution list
-names a layer twice and lets a layer read another's cache; attention with a window; and a
-toy mixer with state of its own, defined here, registered, built and stepped without any
-change to the framework's files."""
+names a layer twice and lets a layer read another's cache; attention with a window; and toy
+parts defined here (a mixer with state of its own, a feed-forward that routes tokens to
+experts, a position encoding with its own frequency table), registered, built and stepped
+without any change to the framework's files."""
 
 from __future__ import annotations
 
@@ -319,3 +320,116 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             runner.core.state_slots.check_invariants()
     finally:
         unregister_architecture("ToyStateForCausalLM")
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped(tmp_path):
+    """A feed-forward that routes each token to two of four experts, and a position encoding
+    with a frequency table of its own, both written here and plugged in through the public
+    registries only; odd layers route, even layers keep the dense feed-forward."""
+    from kvforge_b200 import ModelConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.base import (
+        FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PartSpec, PositionEncoding, WeightDecl, register_feed_forward, register_position_encoding,
+    )  # fmt: skip
+    from kvforge_b200.replay import TraceRunner
+    from test_gpu_replay import check
+
+    n_experts, top, inter = 4, 2, 40
+
+    def routed(x, router, up, down):
+        """softmax over the chosen experts' router logits (32-bit), experts are x -> relu(x U^T) D^T"""
+        logits = x.float() @ router.float().t()
+        val, idx = logits.topk(top, dim=-1)
+        gate = torch.softmax(val, dim=-1)
+        out = torch.zeros_like(x, dtype=torch.float32)
+        for e in range(n_experts):
+            y = torch.relu(x.float() @ up[e].float().t()) @ down[e].float().t()
+            w = (gate * (idx == e)).sum(-1, keepdim=True)
+            out += w * y
+        return out
+
+    class Routed(FeedForward):
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+
+        @classmethod
+        def weight_decls(cls, params):
+            h = params["hidden_size"]
+            return {
+                "router.weight": WeightDecl((n_experts, h)),
+                "experts.up": WeightDecl((n_experts, inter, h)),
+                "experts.down": WeightDecl((n_experts, h, inter)),
+            }
+
+        def bind(self, weights, rt):
+            super().bind(weights, rt)
+            self.router, self.up, self.down = weights["router.weight"], weights["experts.up"], weights["experts.down"]
+
+        def forward(self, ctx, x):
+            return routed(x, self.router, self.up, self.down).to(x.dtype)
+
+    class LinearFrequencies(PositionEncoding):
+        """pair j turns by pos * base / (j + 1)"""
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.table_host = float(params["base"]) / torch.arange(1, int(params["head_dim"]) // 2 + 1, dtype=torch.float32)
+
+        def bind(self, weights, rt):
+            super().bind(weights, rt)
+            self.dev = self.table_host.to(rt.device).contiguous()
+
+        def table(self):
+            return self.dev
+
+    if "toy_routed" not in FEED_FORWARDS:
+        register_feed_forward("toy_routed")(Routed)
+    if "toy_linear_frequencies" not in POSITION_ENCODINGS:
+        register_position_encoding("toy_linear_frequencies")(LinearFrequencies)
+
+    def build(cfg):
+        spec = llama_spec(cfg)
+        position = PartSpec("toy_linear_frequencies", {"head_dim": cfg.head_dim, "base": 0.7})
+        for i, ls in enumerate(spec.layers):
+            mixer = ls.block.params["mixer"]
+            ls.block.params["mixer"] = PartSpec(mixer.kind, {**mixer.params, "position": position})
+            if i % 2 == 1:
+                ls.block.params["ffn"] = PartSpec("toy_routed", {"hidden_size": cfg.hidden_size})
+                ls.block.params["ffn_name"] = "moe"
+        return spec
+
+    register_architecture("ToyRoutedForCausalLM", ModelConfig.from_hf_dict, build)
+    try:
+        from kvforge_b200.parts.model import DecoderModel
+        from kvforge_b200.weights.random_init import write_model_dir
+
+        cfg = TINY["tiny-b"]["cfg"]
+        cj = cfg.to_hf_dict()
+        cj["architectures"] = ["ToyRoutedForCausalLM"]
+        model = DecoderModel(build(cfg))
+        folder = write_model_dir(tmp_path / "toy", cj, model.expected_weights(), seed=6, store_dtype=torch.float32, init_std=0.1, norm_std=0.1)
+
+        class ToyPlain(PlainLlama):
+            def __init__(self, *a, **k):
+                super().__init__(*a, **k)
+                self.inv_freq = 0.7 / torch.arange(1, self.d // 2 + 1, dtype=torch.float32)
+
+            def mlp(self, layer, x):
+                if layer % 2 == 0:
+                    return super().mlp(layer, x)
+                p = f"layers.{layer}.moe."
+                return routed(x, self.w[p + "router.weight"], self.w[p + "experts.up"], self.w[p + "experts.down"])
+
+        plain = ToyPlain(folder)
+        reqs = {f"r{i}": random_tokens(320, n, seed=10 + i) for i, n in enumerate([33, 5, 48, 20, 27])}
+        ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: len(t) - 6 for r, t in reqs.items()}, max_live=3, seed=2)):
+            runner = TraceRunner(str(folder), "float32", traces.tokens_needed(steps), max_live=3)
+            outs = []
+            for s in steps:
+                o = runner.step(s)
+                outs.append(None if o is None else o.clone())
+            check(steps, outs, ref, 2e-5)
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
