@@ -132,9 +132,9 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs)
         self.pdl = bool(pdl)  # programmatic dependent launch between the kernels of a step
         self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
-        # keyed by (tokens, sequences, longest context the graph reaches)
-        self._graphs: dict[tuple[int, int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
-        self.graph_kernels: dict[tuple[int, int, int], int] = {}  # kernels of this library inside each captured graph
+        # keyed by (tokens, sequences, longest context the graph reaches, single-token sequences in a step of many tokens)
+        self._graphs: dict[tuple[int, int, int, bool], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.graph_kernels: dict[tuple[int, int, int, bool], int] = {}  # kernels of this library inside each captured graph
         self.num_kernel_launches = 0  # kernels of this library launched by steps, replays included
         self.num_graph_kernels = 0  # those of them that ran inside replayed graphs
         self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
@@ -258,14 +258,14 @@ class ModelRunner:
             counts[tq] = (total, n_multi, int((q_lens == 1).sum()))
         return counts
 
-    def _context(self, lay: _Layout, n: int, nb: int, r: int, max_q: int, max_ctx: int, bound: int, all_tiles: bool = False) -> StepContext:
+    def _context(self, lay: _Layout, n: int, nb: int, r: int, max_q: int, max_ctx: int, bound: int, all_tiles: bool = False, singles: bool = True) -> StepContext:
         dev, host, o = self._dev, self._host.numpy(), lay.off
         # a captured step launches every tile its layout can hold (the list says which are live)
         tiles = {}
         if max_q > 1:
             for tq in lay.tile_sizes:
                 cap = lay.tile_cap(tq)
-                total, n_multi, n_single = (cap, cap, nb) if all_tiles else self._tile_counts.get(tq, (0, 0, 0))
+                total, n_multi, n_single = (cap, cap, nb if singles else 0) if all_tiles else self._tile_counts.get(tq, (0, 0, 0))
                 a, m = o[f"qtiles_{tq}"], o[f"qtiles_multi_{tq}"]
                 tiles[tq] = QueryTiles(dev[a : a + 2 * cap], total, dev[m : m + 2 * cap], n_multi, n_single)
         view = lambda name, size: dev[o[name] : o[name] + size]  # noqa: E731
@@ -370,7 +370,10 @@ class ModelRunner:
         # A graph fixes its grids, so it is made for contexts up to a bound: the next power of two
         # (kernels whose grid follows the longest context then launch at most twice what they need).
         reach = min(self.max_model_len, max(MIN_GRAPH_CONTEXT, 1 << max(0, max_ctx - 1).bit_length()))
-        key = (n_cap, b_cap, reach)
+        # a step of many tokens is captured once for batches with single-token sequences among them
+        # (those go to the decode kernel) and once for batches without
+        singles = n_cap != b_cap and any(len(it.token_ids) == 1 for it in items)
+        key = (n_cap, b_cap, reach, singles)
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(key, lay)
@@ -382,10 +385,10 @@ class ModelRunner:
         self.num_tokens_processed += n
         return logits[:r]
 
-    def _capture(self, key: tuple[int, int, int], lay: _Layout):
-        n_cap, b_cap, reach = key
+    def _capture(self, key: tuple[int, int, int, bool], lay: _Layout):
+        n_cap, b_cap, reach, singles = key
         # one token per sequence: the decode form; else a sequence may bring up to all the tokens
-        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if n_cap == b_cap else n_cap, reach, bound=reach, all_tiles=True)
+        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if n_cap == b_cap else n_cap, reach, bound=reach, all_tiles=True, singles=singles)
         # one eager run first: sizes every buffer and loads every kernel outside the capture
         self.model.forward(ctx)
         torch.cuda.synchronize()
