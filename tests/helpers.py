@@ -36,6 +36,16 @@ TINY = {
         ),
         block_size=16,
     ),
+    # head size 128 with two heads per kv head and pages of 32 (the sizes of the larger shapes in small):
+    # the same two kernels with tiles of two halves and boxes of 32 keys
+    "tiny-e": dict(
+        cfg=ModelConfig(
+            vocab_size=157, hidden_size=128, num_layers=3, num_heads=4, num_kv_heads=2, head_dim=128,
+            intermediate_size=96, rms_norm_eps=1e-5, rope_theta=50000.0, tie_word_embeddings=False,
+            max_position_embeddings=512,
+        ),
+        block_size=32,
+    ),
 }  # fmt: skip
 
 

@@ -63,11 +63,11 @@ def test_batched_greedy_generation_equals_plain(folders, name):
     engine.block_manager.check_invariants()
 
 
-def test_bfloat16_generation_with_and_without_graphs(folders):
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-d", "tiny-e"])
+def test_bfloat16_generation_with_and_without_graphs(folders, name):
     """The bfloat16 path generates the same tokens whether single-token steps are replayed
     as CUDA graphs or launched one kernel at a time, and they are the plain model's tokens
     wherever its top-2 margin is larger than bfloat16 rounding."""
-    name = "tiny-a"
     prompts = prompts_for(name, [5, 17, 33, 9], seed=40)
     a = engine_for(folders[name], name, "bfloat16", cuda_graphs=True).generate(prompts, greedy(12))
     b = engine_for(folders[name], name, "bfloat16", cuda_graphs=False).generate(prompts, greedy(12))

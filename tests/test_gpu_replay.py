@@ -20,7 +20,7 @@ from plain_llama import PlainLlama
 pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
-LENGTHS = {"tiny-a": [5, 17, 33, 70, 100], "tiny-b": [1, 9, 40, 71, 130], "tiny-c": [3, 64, 65, 97, 2], "tiny-d": [130, 70, 33, 200, 17]}
+LENGTHS = {"tiny-a": [5, 17, 33, 70, 100], "tiny-b": [1, 9, 40, 71, 130], "tiny-c": [3, 64, 65, 97, 2], "tiny-d": [130, 70, 33, 200, 17], "tiny-e": [66, 140, 9, 35, 101]}
 # Error of a logits row: largest difference over the row's largest magnitude.
 # float32: the engine's 32-bit kernels against 32-bit torch on the CPU (sums in other orders).
 # bfloat16: stored weights are bfloat16 in both, so what differs is the rounding of
