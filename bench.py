@@ -412,6 +412,20 @@ def run_kernel_only(args, cfg) -> dict:
         flops = 4 * nh * d * ctx * (ctx + 1) // 2
         return {"only": "attention-prefill", "tokens": ctx, "us": round(sec * 1e6, 2), "TFLOP/s": round(flops / sec / 1e12, 1),
                 "frac_of_bf16_peak": round(flops / sec / 1e12 / pk["bf16_tflops"], 3)}  # fmt: skip
+    if args.only == "sample":
+        # one token per row of float logits [batch, vocabulary]; copies are cycled so that rows come from HBM
+        r, v = args.batch, cfg.vocab_size
+        copies = max(2, min(16, int(4e8 // (r * v * 4)) + 1))
+        logits = [torch.randn(r, v, device=dev) * 3 for _ in range(copies)]
+        out = torch.empty(r, device=dev, dtype=torch.int32)
+        temps = torch.full((r,), args.temperature, device=dev)
+        ks = torch.full((r,), args.top_k, device=dev, dtype=torch.int32)
+        ps = torch.full((r,), args.top_p, device=dev)
+        keys = torch.arange(r, device=dev, dtype=torch.int64)
+        sec = _graph_time(lambda i: ops.sample(logits[i % copies], out, temps, ks, ps, keys), calls=max(2, args.steps), reps=3)
+        nbytes = r * v * 4
+        return {"only": "sample", "rows": r, "vocab": v, "temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p,
+                "us": round(sec * 1e6, 2), "GB/s_one_pass": round(nbytes / sec / 1e9, 1)}  # fmt: skip
     shapes = {"qkv": ((nh + 2 * nkv) * d, cfg.hidden_size), "o": (cfg.hidden_size, nh * d),
               "gate_up": (2 * cfg.intermediate_size, cfg.hidden_size), "down": (cfg.hidden_size, cfg.intermediate_size),
               "lm_head": (cfg.vocab_size, cfg.hidden_size)}  # fmt: skip
@@ -467,7 +481,7 @@ def run_only(args) -> dict:
     cfg = PRESETS[args.preset]
     if args.only == "load":
         return run_load(args, cfg)
-    if args.only in ("attention", "attention-prefill", "gemm"):
+    if args.only in ("attention", "attention-prefill", "gemm", "sample"):
         return run_kernel_only(args, cfg)
     ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
     core = make_core(cfg, max(args.batch, 1), PREFILL_TOKENS, ctx_cap, cuda_graphs=not args.no_graphs)
@@ -494,10 +508,13 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm", "load"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm", "sample", "load"], help="run one part alone and print a short line (for profiling)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--block-size", type=int, default=16, help="with --only attention / attention-prefill: tokens per page")
+    ap.add_argument("--temperature", type=float, default=0.8, help="with --only sample (0 = greedy)")
+    ap.add_argument("--top-k", type=int, default=50, help="with --only sample (0 = off)")
+    ap.add_argument("--top-p", type=float, default=0.9, help="with --only sample (1 = off)")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="with --only decode: tokens already in each cache")
