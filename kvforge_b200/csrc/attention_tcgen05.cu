@@ -1,29 +1,33 @@
 // Paged grouped-query attention for many queries (prompts, portions, mixed batches) on the
-// tcgen05 tensor cores; bfloat16, head size 64.  Same contract as attention_generic.cu.
+// tcgen05 tensor cores; bfloat16, head size 64 or 128.  Same contract as attention_generic.cu.
 //
 // One CTA serves 128 rows of one kv head of one sequence; a row is a (query token, head of the
-// group) pair, so 128/g tokens.  Keys are walked in tiles of 64 from position 0 (or from the
-// tile that holds the window's first key).  Per tile t:
-//   S = Q K^T      tcgen05.mma 128 x 64 x 64, Q and the K tile in 128-byte-swizzled shared memory
-//                  (K-major), S in tensor memory: two buffers of 64 float columns, so the tensor
-//                  core writes S(t+1) while the softmax reads S(t);
+// group) pair, so 128/g tokens.  Which tokens: an entry (sequence, first query) of a list made
+// on the host with the step, longest walk over the keys first; without a list, the grid's y and
+// z.  Keys are walked in tiles of 64 from position 0 (or from the tile that holds the window's
+// first key).  Per tile t:
+//   S = Q K^T      tcgen05.mma 128 x 64 x (head size), Q and the K tile in 128-byte-swizzled shared
+//                  memory (K-major; a 128-wide tile as two 64-wide halves), S in tensor memory;
 //   softmax        thread r owns row r (tensor-memory lane r): it reads the 64 scores once with
 //                  tcgen05.ld, keeps the running maximum and sum in registers, and writes
-//                  P = exp2(S * scale - m) as bfloat16 into shared memory (two buffers) in the
-//                  swizzled K-major layout of an A operand;
-//   O += P V       tcgen05.mma 128 x 64 x 64, the V tile [keys][64] as an MN-major B operand; O
-//                  stays in tensor memory (64 columns) over all tiles.
+//                  P = exp2(S * scale - m) as bfloat16 into shared memory in the swizzled K-major
+//                  layout of an A operand (packed f32x2 fma and add, a three-input maximum);
+//   O += P V       tcgen05.mma 128 x 64 x 64 per 64 output dims, the V tile [keys][64] as an
+//                  MN-major B operand; O stays in tensor memory over all tiles.
+// Two groups of four softmax warps take the even and the odd tiles, each with its own S buffer,
+// P buffer, O accumulator, maximum and sum; at the end group 0 merges the two.
 // The maximum m that P is scaled by follows the row's true maximum lazily: a thread raises it
 // only when the true maximum has grown by more than 8 (in log2 units), so P <= 256; then the
 // warp multiplies its rows of O by exp2(m_old - m_new) in tensor memory (tcgen05.ld / st) before
 // the next P V.  The sum l carries the same factor, so O / l is the exact softmax average.
 // Whether a thread rescales depends on its own row only: a row's result does not depend on the
 // rows beside it.
-// Warps 0-3 do the softmax, warp 4 brings Q and the K/V tiles in with cp.async (pages are not
-// contiguous, so no tensor-map copy; two tiles in flight) and hands them to the tensor core
-// through a proxy fence and mbarriers, one thread of warp 5 issues the MMAs.  Two CTAs fit an SM
-// (112 KB of shared memory and 256 tensor-memory columns each).  CTAs with the most keys to
-// walk (the last queries) come first in the grid.
+// Warps 0-7 do the softmax.  Warp 8 brings Q in with cp.async and the K/V tiles as tensor-map
+// boxes of a page's keys (16, 32 or 64 rows of 128 bytes; with pages that are no multiple of 16
+// keys, and for a last tile that ends inside a page, key by key with cp.async) through a ring of
+// 4 stages (5 at head size 128).  One thread of warp 9 issues the MMAs: when P(t) arrives, first
+// S(t+2), which is all its group waits for, then P(t) V(t).  Two CTAs fit an SM at head size 64
+// (112 KB of shared memory and 256 tensor-memory columns each), one at 128.
 //
 // Every mbarrier wait is bounded; if one runs out the kernel raises bit 4 of the error flag and
 // winds down.  No cluster launch, no multicast.
