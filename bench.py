@@ -202,6 +202,50 @@ def time_prefill(core, tokens: int, reps: int = 3):
     return min(times[1:])
 
 
+def time_mixed(core, decodes: int, context: int, chunk: int, reps: int = 5):
+    """A mixed step: ``decodes`` requests with ``context`` tokens in their caches bring one token
+    each, beside one request that brings a portion of ``chunk`` prompt tokens (from position 0).
+    Returns the seconds per step of ``reps`` steps run back to back (the host prepares a step
+    while the device runs the one before)."""
+    import torch
+
+    from kvforge_b200.engine.step import BatchItem
+
+    bm = core.block_manager
+    ids = [f"d{i}" for i in range(decodes)]
+    for rid in ids:
+        bm.allocate(rid, context)
+        core.state_slots.allocate(rid)
+    for t in core.pool.k + core.pool.v:  # synthetic cache contents
+        t.normal_(0.0, 0.5)
+    gen = torch.Generator().manual_seed(3)
+    vocab = core.spec.vocab_size
+    prompt = torch.randint(0, vocab, (chunk,), generator=gen).tolist()
+    pos = context
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(reps + 2):  # two untimed steps (the second replays what the first captured), then the timed ones back to back
+        if i == 2:
+            torch.cuda.synchronize()
+            start.record()
+        for rid in ids:
+            bm.append_slots(rid, pos + 1, pos)
+        bm.allocate("p", chunk)
+        core.state_slots.allocate("p")
+        items = [BatchItem(rid, [int(torch.randint(0, vocab, (1,), generator=gen))], pos, "last") for rid in ids]
+        items.append(BatchItem("p", prompt, 0, "last"))
+        core.runner.step(items)
+        bm.free("p")
+        core.state_slots.free("p")
+        pos += 1
+    end.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(end) / 1e3 / reps
+    for rid in ids:
+        bm.free(rid)
+        core.state_slots.free(rid)
+    return seconds
+
+
 def time_e2e(cfg, batch: int, steps: int, warmup: int):
     """The same decode steps through ``InferenceEngine``: prompts of 2,048 host token ids in,
     a token id per request out to the host every step."""
@@ -460,8 +504,10 @@ def run_load(args, cfg) -> dict:
         model=cfg, cache=CacheConfig(block_size=16, num_blocks=None, kv_cache_memory_gb=16.0),
         scheduler=SchedulerConfig(max_num_seqs=64, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT), dtype="bfloat16",
     ))  # fmt: skip
-    # the same load once untimed: every graph the timed pass replays exists by then
-    engine.generate(prompts, SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True))
+    # the same load twice untimed: every graph the timed pass replays exists by then (a shape of
+    # many tokens is captured at its second coming)
+    for _ in range(2):
+        engine.generate(prompts, SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = engine.generate(prompts, SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True))
@@ -484,11 +530,16 @@ def run_only(args) -> dict:
     if args.only in ("attention", "attention-prefill", "gemm", "sample"):
         return run_kernel_only(args, cfg)
     ctx_cap = max(CONTEXT, args.context + args.steps + args.warmup + 16)
-    core = make_core(cfg, max(args.batch, 1), PREFILL_TOKENS, ctx_cap, cuda_graphs=not args.no_graphs)
+    core = make_core(cfg, max(args.batch, 1) + (args.only == "mixed"), PREFILL_TOKENS, ctx_cap, cuda_graphs=not args.no_graphs)
     if args.only == "decode":
         seconds, launches, mean_ctx = time_decode(core, args.batch, args.context, args.steps, args.warmup)
         return {"only": "decode", "batch": args.batch, "context": mean_ctx, "ms_per_step": round(1e3 * seconds / args.steps, 4),
                 "tokens_per_s": round(args.batch * args.steps / seconds, 1), "gpu_launches": launches}  # fmt: skip
+    if args.only == "mixed":
+        chunk = 1024
+        seconds = time_mixed(core, args.batch, args.context, chunk)
+        return {"only": "mixed", "preset": args.preset, "decode_requests": args.batch, "context": args.context, "prompt_portion": chunk,
+                "ms": round(1e3 * seconds, 3), "tokens_per_s": round((args.batch + chunk) / seconds, 1)}  # fmt: skip
     seconds = time_prefill(core, PREFILL_TOKENS, reps=max(1, args.steps))
     return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(1e3 * seconds, 3), "tokens_per_s": round(PREFILL_TOKENS / seconds, 1)}
 
@@ -508,7 +559,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--only", choices=["decode", "prefill", "attention", "attention-prefill", "gemm", "sample", "load"], help="run one part alone and print a short line (for profiling)")
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "attention", "attention-prefill", "gemm", "sample", "load"], help="run one part alone and print a short line (for profiling)")
     ap.add_argument("--preset", default="llama-3.2-1b", help="with --only: the shape (llama-3.2-1b, llama-3.2-3b, llama-3.1-8b)")
     ap.add_argument("--split", type=int, default=0, help="with --only attention: keys per range (0 = the engine's choice)")
     ap.add_argument("--block-size", type=int, default=16, help="with --only attention / attention-prefill: tokens per page")

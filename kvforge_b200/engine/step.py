@@ -30,8 +30,9 @@ from .runtime import QueryTiles, Runtime, StepContext
 # graphs for shorter contexts than this are not told apart
 MIN_GRAPH_CONTEXT = 1024
 # steps of at least this many tokens are replayed as graphs too, padded to a multiple of GRAPH_TOKEN_STEP
+# (padding is work: 224 tokens beside 1,056 cost a fifth more); a shape is captured the second time it comes
 MIN_GRAPH_TOKENS = 512
-GRAPH_TOKEN_STEP = 256
+GRAPH_TOKEN_STEP = 64
 
 
 @dataclass
@@ -131,7 +132,8 @@ class ModelRunner:
         self.n_groups = block_manager.num_groups
         self.cuda_graphs = bool(cuda_graphs)
         self.pdl = bool(pdl)  # programmatic dependent launch between the kernels of a step
-        self.graph_buckets = sorted(b for b in graph_buckets if b <= rt.max_seqs) or [rt.max_seqs]
+        # the most sequences a step can hold is a bucket of its own, so that no batch size goes without a graph
+        self.graph_buckets = sorted({b for b in graph_buckets if b <= rt.max_seqs} | ({rt.max_seqs} if rt.max_seqs <= max(graph_buckets) else set())) or [rt.max_seqs]
         # keyed by (tokens, sequences, longest context the graph reaches, single-token sequences in a step of many tokens)
         self._graphs: dict[tuple[int, int, int, bool], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self.graph_kernels: dict[tuple[int, int, int, bool], int] = {}  # kernels of this library inside each captured graph
@@ -143,6 +145,8 @@ class ModelRunner:
         self._dev: torch.Tensor | None = None
         self._copy_done: torch.cuda.Event | None = None
         self._tile_counts: dict[int, tuple[int, int, int]] = {}
+        self._graph_seen: dict[tuple[int, int, int, bool], int] = {}  # how often a shape of many tokens has come
+        self.graph_after = 2  # ... and at which coming it is captured
         # made once for the widest step there can be, so its address never changes
         self._ensure(self._layout(rt.max_tokens, rt.max_seqs, self.max_width, rt.max_tokens).total)
         # tokens sampled on the device that may feed the next step (set by whoever samples)
@@ -330,7 +334,11 @@ class ModelRunner:
             b_cap = next(b for b in self.graph_buckets if b >= len(items))
             n_cap = min(self.rt.max_tokens, -(-n_tok // GRAPH_TOKEN_STEP) * GRAPH_TOKEN_STEP)
             if n_rows <= b_cap and n_cap >= n_tok:
-                return self._step_graph(items, n_cap, b_cap)
+                key = self._graph_key(items, n_cap, b_cap)
+                seen = self._graph_seen.get(key, 0) + 1
+                self._graph_seen[key] = seen
+                if seen >= self.graph_after:  # a shape that comes once is not worth a capture
+                    return self._step_graph(items, n_cap, b_cap)
         width = max(-(-(it.start_pos + len(it.token_ids)) // self.block_size) for it in items)
         lay = self._layout(n_tok, len(items), width, n_rows)
         self._ensure(lay.total)
@@ -350,6 +358,16 @@ class ModelRunner:
         self._pool = pool
         self.model.attach_cache(pool.caches)
 
+    def _graph_key(self, items: Sequence[BatchItem], n_cap: int, b_cap: int) -> tuple[int, int, int, bool]:
+        # A graph fixes its grids, so it is made for contexts up to a bound: the next power of two
+        # (kernels whose grid follows the longest context then launch at most twice what they need).
+        max_ctx = max(it.start_pos + len(it.token_ids) for it in items)
+        reach = min(self.max_model_len, max(MIN_GRAPH_CONTEXT, 1 << max(0, max_ctx - 1).bit_length()))
+        # a step of many tokens is captured once for batches with single-token sequences among them
+        # (those go to the decode kernel) and once for batches without
+        singles = n_cap != b_cap and any(len(it.token_ids) == 1 for it in items)
+        return (n_cap, b_cap, reach, singles)
+
     def _step_graph(self, items: Sequence[BatchItem], n_cap: int, b_cap: int) -> torch.Tensor:
         """Replay the step as a graph made for ``n_cap`` tokens in ``b_cap`` sequences (``n_cap ==
         b_cap``: one token each, the decode form)."""
@@ -367,13 +385,8 @@ class ModelRunner:
             host[o["slots"] + g * n_cap : o["slots"] + (g + 1) * n_cap] = -1
         n, _, r, max_q, max_ctx = self._fill(items, lay)
         self._upload(lay.total)
-        # A graph fixes its grids, so it is made for contexts up to a bound: the next power of two
-        # (kernels whose grid follows the longest context then launch at most twice what they need).
-        reach = min(self.max_model_len, max(MIN_GRAPH_CONTEXT, 1 << max(0, max_ctx - 1).bit_length()))
-        # a step of many tokens is captured once for batches with single-token sequences among them
-        # (those go to the decode kernel) and once for batches without
-        singles = n_cap != b_cap and any(len(it.token_ids) == 1 for it in items)
-        key = (n_cap, b_cap, reach, singles)
+        key = self._graph_key(items, n_cap, b_cap)
+        reach = key[2]
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(key, lay)

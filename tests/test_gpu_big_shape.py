@@ -79,7 +79,8 @@ def test_llama_1b_width_generation_uses_graphs_and_the_device_token_loop(big):
 
 def test_steps_of_many_tokens_replay_as_graphs_with_the_same_logits(big):
     """A step of 512 tokens or more is replayed as a CUDA graph made for its token count rounded up
-    to 256 and its sequence count rounded up to a bucket; the padding must change nothing."""
+    to 64 and its sequence count rounded up to a bucket (here at its first coming); the padding
+    must change nothing."""
     from kvforge_b200 import CacheConfig
     from kvforge_b200.engine.core import EngineCore
     from kvforge_b200.engine.step import BatchItem
@@ -92,6 +93,7 @@ def test_steps_of_many_tokens_replay_as_graphs_with_the_same_logits(big):
             folder, dtype="bfloat16", cache=CacheConfig(block_size=16, num_blocks=100, watermark=0.0),
             max_num_seqs=4, max_num_batched_tokens=1024, max_model_len=1536, cuda_graphs=graphs,
         )  # fmt: skip
+        core.runner.graph_after = 1
         bm = core.block_manager
         for rid, n in (("l", 650), ("s", len(short))):
             bm.allocate(rid, n)
