@@ -1,4 +1,3 @@
-#!/usr/bin/env python3
 """Generate tokens from a model folder or a random-weights preset.
 
 The options that umarhassan-cloud/kvforge's launcher has (scripts/serve.py:41-61) keep their
@@ -9,8 +8,8 @@ the fields of its ``SamplingParams``.  Prompts are token ids (``--prompt-ids "1,
 per use, or ``--prompt-file`` with one comma-separated prompt a line) or, with the byte
 tokenizer of the random-weight demos, text (``--prompt``).
 
-    python scripts/generate.py --preset tiny-a --prompt-ids 5,17,3 --max-tokens 8 --temperature 0
-    python scripts/generate.py --hf-model /path/to/Llama-3.2-1B --prompt-ids 128000,9906 --max-tokens 32
+    bin/generate --preset tiny-a --prompt-ids 5,17,3 --max-tokens 8 --temperature 0
+    bin/generate --hf-model /path/to/Llama-3.2-1B --prompt-ids 128000,9906 --max-tokens 32
 """
 
 from __future__ import annotations
@@ -20,11 +19,9 @@ import json
 import sys
 from pathlib import Path
 
-sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
-
 
 def main() -> int:
-    from kvforge_b200 import PRESETS, ByteTokenizer, CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
+    from . import PRESETS, ByteTokenizer, CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
 
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     src = p.add_mutually_exclusive_group()

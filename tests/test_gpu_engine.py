@@ -217,3 +217,26 @@ def test_random_weights_mode_needs_no_folder():
     assert a == b and len(a) == 5
     stats = InferenceEngine(cfg).stats()
     assert stats["kv_cache"]["num_free_blocks"] == 64
+
+
+def test_the_command_line_generates_the_plain_models_tokens(folders):
+    """bin/generate on a model folder, greedy, float32: the tokens of the plain implementation."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    name = "tiny-b"
+    prompts = prompts_for(name, [9, 3], seed=70)
+    root = Path(__file__).resolve().parent.parent
+    cmd = [sys.executable, str(root / "bin" / "generate"), "--hf-model", str(folders[name]), "--dtype", "float32", "--block-size", "8",
+           "--num-blocks", "64", "--max-model-len", "128", "--max-num-batched-tokens", "64", "--max-tokens", "6", "--temperature", "0", "--ignore-eos"]  # fmt: skip
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(str(t) for t in p)]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    outs = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    plain = PlainLlama(folders[name])
+    assert [o["prompt_token_ids"] for o in outs] == prompts
+    for p, o in zip(prompts, outs):
+        assert o["output_token_ids"] == plain.greedy(p, 6) and o["finish_reason"] == "length"
