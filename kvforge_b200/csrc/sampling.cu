@@ -15,7 +15,9 @@
 // summed as 64-bit integers, so every sum is exact and independent of the order of
 // addition: the same row, options and random key always give the same token.  Values tied
 // with the k-th largest all stay.  The draw is the inverse CDF in index order with a
-// uniform integer in [0, total mass).
+// uniform integer in [0, total mass).  When top-k leaves at most 256 entries they are gathered in
+// the first CTA's shared memory and the top-p cut and the draw are worked out there, by the same
+// rules, instead of by further passes over the row.
 #include "common.cuh"
 
 using namespace kvf;
@@ -55,6 +57,7 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
 
 constexpr int MAX_BLOCKS = 512;  // stretches of the vocabulary whose masses the draw keeps in shared memory
 constexpr int MAX_CLUSTER = 8;
+constexpr int CAND_MAX = 256;  // with top-k up to this, what passes it is gathered in the first CTA and finished there
 
 struct Shared {
   unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass); [0] holds the CTA's fold
@@ -63,6 +66,7 @@ struct Shared {
   unsigned long long bcast[3];
   unsigned long long blk[MAX_BLOCKS];    // mass of each stretch, in index order
   unsigned long long xu;                 // what this CTA offers to the others (a sum or a maximum)
+  unsigned n_cand;                       // the first CTA's: how many entries passed top-k
   float xf;
   float fred[32];
 };
@@ -83,6 +87,19 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
+}
+__device__ __forceinline__ unsigned ld_cluster_u32(uint32_t addr) {
+  unsigned v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, unsigned v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned atom_add_cluster_u32(uint32_t addr, unsigned v) {
+  unsigned old;
+  asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+  return old;
 }
 // every thread of every CTA of the cluster
 __device__ __forceinline__ void cluster_barrier() {
@@ -159,6 +176,19 @@ __device__ __forceinline__ unsigned long long block_sum_u64(Shared& sh, unsigned
 #pragma unroll
   for (int w = 0; w < NWARPS; ++w) s += sh.red[w];
   return s;
+}
+
+__device__ __forceinline__ unsigned block_max_u32(Shared& sh, unsigned v) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) sh.red[warp] = v;
+  __syncthreads();
+  unsigned m = 0;
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) m = max(m, (unsigned)sh.red[w]);
+  return m;
 }
 
 // The first position (in walking order) at which the running total of a[.] reaches (REACH: >=) or
@@ -329,6 +359,94 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   }
 
   const float top_p = top_ps ? top_ps[r] : 1.f;
+  if (k > 0 && k < V && k <= CAND_MAX) {
+    // ---- top-k left few entries: they are gathered in the first CTA's shared memory (over the
+    // histograms, which are done with) and top-p and the draw are finished there, with the same
+    // masses, the same cut and the same draw in index order as the passes over the row below.
+    unsigned* c_idx = reinterpret_cast<unsigned*>(&sh.hist[0][0]);
+    unsigned* c_key = c_idx + CAND_MAX;
+    float* c_val = reinterpret_cast<float*>(c_key + CAND_MAX);
+    unsigned long long* c_mass = reinterpret_cast<unsigned long long*>(c_val + CAND_MAX);
+    unsigned long long* c_kept = c_mass + CAND_MAX;
+    if (threadIdx.x == 0) sh.n_cand = 0u;
+    cluster_barrier();  // every CTA is done with the histograms; the counter is zero
+    const uint32_t a_cnt = in_cta(sm32(&sh.n_cand), 0), a_idx = in_cta(sm32(c_idx), 0), a_val = in_cta(sm32(c_val), 0);
+    for_each(sl, [&](int i, float raw) {
+      const float x = raw / T;
+      if (ordered_key(x) >= lo_key) {
+        const unsigned slot = atom_add_cluster_u32(a_cnt, 1u);
+        if (slot < (unsigned)CAND_MAX) {
+          st_cluster_u32(a_idx + 4u * slot, (unsigned)i);
+          st_cluster_u32(a_val + 4u * slot, __float_as_uint(x));
+        }
+      }
+    });
+    cluster_barrier();  // all of them are in the first CTA
+    const int n = (int)ld_cluster_u32(a_cnt);
+    if (n <= CAND_MAX) {  // (more: values tied with the k-th largest; the passes below take those)
+      if (sl.rank == 0) {
+        for (int i = threadIdx.x; i < n; i += THREADS) {
+          c_key[i] = ordered_key(c_val[i]);
+          c_mass[i] = __float2ull_rz(expf(c_val[i] - mx) * FIX_ONE);
+        }
+        __syncthreads();
+        unsigned cut_key = lo_key;
+        if (top_p < 1.f) {
+          unsigned long long z = 0;
+          for (int i = threadIdx.x; i < n; i += THREADS) z += c_mass[i];
+          const unsigned long long s = block_sum_u64(sh, z);
+          unsigned long long remaining = (unsigned long long)ceil((double)top_p * (double)s);
+          if (remaining < 1ull) remaining = 1ull;
+          if (remaining > s) remaining = s;
+          // an entry stays if the mass of the strictly larger ones is below the target
+          unsigned lowest = 0xFFFFFFFFu;
+          for (int i = threadIdx.x; i < n; i += THREADS) {
+            unsigned long long above = 0;
+            const unsigned mine = c_key[i];
+            for (int j = 0; j < n; ++j) above += c_key[j] > mine ? c_mass[j] : 0ull;
+            const bool keep = above < remaining;
+            c_kept[i] = keep ? c_mass[i] : 0ull;
+            if (keep) lowest = min(lowest, mine);
+          }
+          lowest = ~block_max_u32(sh, ~lowest);
+          cut_key = lowest > lo_key ? lowest : lo_key;
+        } else {
+          for (int i = threadIdx.x; i < n; i += THREADS) c_kept[i] = c_mass[i];
+        }
+        __syncthreads();
+        unsigned long long z = 0;
+        for (int i = threadIdx.x; i < n; i += THREADS) z += c_kept[i];
+        const unsigned long long total = block_sum_u64(sh, z);
+        const unsigned long long rnd = splitmix64(rand_keys ? rand_keys[r] : 0ull);
+        const unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
+        for (int i = threadIdx.x; i < n; i += THREADS) {
+          unsigned long long before = 0;
+          const unsigned mine = c_idx[i];
+          for (int j = 0; j < n; ++j) before += c_idx[j] < mine ? c_kept[j] : 0ull;
+          if (before <= target && target - before < c_kept[i]) out_tokens[r] = (int)mine;  // exactly one entry
+        }
+        if (threadIdx.x == 0) {
+          sh.bcast[0] = (unsigned long long)cut_key;
+          sh.bcast[1] = total;
+        }
+      }
+      if (!prow) {
+        cluster_barrier();  // nobody leaves while the first CTA's counter may still be read
+        return;
+      }
+      cluster_barrier();  // the cut and the total stand in the first CTA
+      const unsigned cut_key = (unsigned)ld_cluster_u64(in_cta(sm32(&sh.bcast[0]), 0));
+      const unsigned long long total = ld_cluster_u64(in_cta(sm32(&sh.bcast[1]), 0));
+      cluster_barrier();  // read by all
+      const float inv = 1.f / (float)total;
+      for (int i = sl.lo + threadIdx.x; i < sl.hi; i += THREADS) {
+        const float x = row[i] / T;
+        const unsigned long long w = ordered_key(x) >= cut_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
+        prow[i] = (float)w * inv;
+      }
+      return;
+    }
+  }
   if (top_p < 1.f) {
     // mass of what top-k kept
     unsigned long long z = 0;

@@ -795,6 +795,64 @@ def test_sampling_distribution_matches_the_formula(ops, v):
             assert min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (i, tok, want)
 
 
+def tie_keeping_probs(logits, t, k, p):
+    """What the sampling kernel defines: values tied with the k-th largest all stay, and top-p
+    treats equal values as one block (it stays if the mass of the strictly larger values is
+    below top_p of the mass that top-k kept).  float64."""
+    x = logits.double() / t
+    v = x.numel()
+    kept = torch.ones(v, dtype=torch.bool)
+    if 0 < k < v:
+        kept = x >= x.sort(descending=True).values[k - 1]
+    m = torch.exp(x - x.max()) * kept
+    if p < 1.0:
+        vals, inv = torch.unique(x, return_inverse=True)  # ascending
+        per = torch.zeros_like(vals).index_add_(0, inv, m)
+        above = per.flip(0).cumsum(0).flip(0) - per  # mass of the strictly larger values
+        m = m * (above < p * m.sum())[inv]
+    return m / m.sum()
+
+
+def test_sampling_with_few_and_with_many_entries_left_by_top_k(ops):
+    """Top-k up to 256 finishes in one CTA's shared memory on the entries that passed; more
+    entries than that (a larger k, or values tied with the k-th largest) take the passes over
+    the row.  Both must give the same distribution and the same draw."""
+    v = 5000
+    g = torch.Generator().manual_seed(3)
+    base = torch.randn(v, generator=g) * 2
+    tied = base.clone()
+    tied[torch.randperm(v, generator=g)[:400]] = 7.0  # 400 values tied at the top
+    edge = base.clone()
+    order = edge.argsort(descending=True)
+    edge[order[199:201]] = float(edge[order[199]])  # the 200th and the 201st largest are equal
+    many_edge = base.clone()
+    many_edge[order[255:258]] = float(many_edge[order[255]])  # 256th..258th equal: 258 entries pass k = 256
+    cases = [(base, 1.0, 256, 0.9), (base, 0.7, 300, 0.8), (tied, 1.0, 10, 0.9), (edge, 1.3, 200, 0.5), (many_edge, 1.0, 256, 0.95),
+             (base, 1.0, 1, 0.5), (base, 0.9, 40, 1.0), (tied, 0.8, 500, 0.3)]  # fmt: skip
+    logits = torch.stack([c[0] for c in cases])
+    temps = torch.tensor([c[1] for c in cases])
+    ks = torch.tensor([c[2] for c in cases], dtype=torch.int32)
+    ps = torch.tensor([c[3] for c in cases])
+    keys = torch.arange(len(cases), dtype=torch.int64) + 99
+    out = torch.empty(len(cases), dtype=torch.int32, device="cuda")
+    probs = torch.empty(len(cases), v, device="cuda")
+    ops.sample(dev(logits), out, dev(temps), dev(ks), dev(ps), dev(keys), probs)
+    probs = probs.cpu().double()
+    for i, (row, t, k, p) in enumerate(cases):
+        ref = tie_keeping_probs(row, t, k, p)
+        differ = (probs[i] > 0) != (ref > 0)
+        assert float(ref[differ].sum()) + float(probs[i][differ].sum()) < 1e-5, (i, int(differ.sum()))
+        assert torch.allclose(probs[i][~differ], ref[~differ], atol=2e-6, rtol=1e-4), i
+        u = ops.splitmix64(int(keys[i])) / 2.0**64
+        cdf = ref.cumsum(0)
+        want = int(torch.searchsorted(cdf, torch.tensor(u * float(cdf[-1]), dtype=torch.float64), right=True))
+        tok = int(out[i])
+        assert ref[tok] > 0
+        if tok != want:  # only a draw that lands within rounding of a CDF step may differ
+            lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+            assert min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (i, tok, want)
+
+
 def test_sampling_is_reproducible_and_follows_the_distribution(ops):
     logits = torch.tensor([[2.0, 1.0, 0.5, -1.0, 0.0]]).repeat(4000, 1)
     temps = torch.full((4000,), 0.8)
