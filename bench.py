@@ -460,7 +460,11 @@ def run_kernel_only(args, cfg) -> dict:
         # one token per row of float logits [batch, vocabulary]; copies are cycled so that rows come from HBM
         r, v = args.batch, cfg.vocab_size
         copies = max(2, min(16, int(4e8 // (r * v * 4)) + 1))
-        logits = [torch.randn(r, v, device=dev) * 3 for _ in range(copies)]
+        if args.peaked:  # a few likely tokens and a long tail (logit = -1.5 ln(rank) + noise), as a trained model's rows are
+            ranks = torch.stack([torch.randperm(v, device=dev) for _ in range(r)]).float()
+            logits = [-1.5 * torch.log1p(ranks) + 0.3 * torch.randn(r, v, device=dev) for _ in range(copies)]
+        else:
+            logits = [torch.randn(r, v, device=dev) * 3 for _ in range(copies)]
         out = torch.empty(r, device=dev, dtype=torch.int32)
         temps = torch.full((r,), args.temperature, device=dev)
         ks = torch.full((r,), args.top_k, device=dev, dtype=torch.int32)
@@ -566,6 +570,7 @@ def main() -> int:
     ap.add_argument("--temperature", type=float, default=0.8, help="with --only sample (0 = greedy)")
     ap.add_argument("--top-k", type=int, default=50, help="with --only sample (0 = off)")
     ap.add_argument("--top-p", type=float, default=0.9, help="with --only sample (1 = off)")
+    ap.add_argument("--peaked", action="store_true", help="with --only sample: rows with a few likely tokens and a long tail instead of normal noise")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="with --only decode: tokens already in each cache")

@@ -15,9 +15,11 @@
 // summed as 64-bit integers, so every sum is exact and independent of the order of
 // addition: the same row, options and random key always give the same token.  Values tied
 // with the k-th largest all stay.  The draw is the inverse CDF in index order with a
-// uniform integer in [0, total mass).  When top-k leaves at most 256 entries they are gathered in
-// the first CTA's shared memory and the top-p cut and the draw are worked out there, by the same
-// rules, instead of by further passes over the row.
+// uniform integer in [0, total mass).  A pass that puts the row into coarse buckets below its
+// maximum comes first: when the buckets down to the one with the cut (the k-th largest, or the
+// top-p share of the mass) hold at most 512 entries, those are gathered in the first CTA's
+// shared memory and the cuts and the draw are worked out there, by the same rules, instead of by
+// radix passes over the row (which remain for flat rows, many equal values and large k).
 #include "common.cuh"
 
 using namespace kvf;
@@ -57,7 +59,7 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
 
 constexpr int MAX_BLOCKS = 512;  // stretches of the vocabulary whose masses the draw keeps in shared memory
 constexpr int MAX_CLUSTER = 8;
-constexpr int CAND_MAX = 256;  // with top-k up to this, what passes it is gathered in the first CTA and finished there
+constexpr int CAND_MAX = 512;  // up to this many entries are gathered in the first CTA and finished there (7 arrays: 14 KB + 4 KB)
 
 struct Shared {
   unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass); [0] holds the CTA's fold
@@ -95,11 +97,6 @@ __device__ __forceinline__ unsigned ld_cluster_u32(uint32_t addr) {
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t addr, unsigned v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned atom_add_cluster_u32(uint32_t addr, unsigned v) {
-  unsigned old;
-  asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
-  return old;
 }
 // every thread of every CTA of the cluster
 __device__ __forceinline__ void cluster_barrier() {
@@ -293,6 +290,75 @@ __device__ int radix_level(Shared& sh, const Slice& sl, float temp, float mx, un
   return chosen;
 }
 
+// Buckets of an eighth of a nat below the row's maximum, 255 for the maximum itself down to 0 for
+// 32 nats or more below it: a coarse order of the values (a larger value never has a smaller
+// bucket) in which a peaked row's k largest, or its top-p part, fill a few sparse buckets.
+__device__ __forceinline__ unsigned linear_bucket(float x, float mx) { return 255u - min(255u, __float2uint_rz((mx - x) * 8.f)); }
+
+// Histogram (count or mass) of the whole row by linear_bucket, then the walk from bucket 255 down
+// until the running total reaches what is wanted: `want` itself (counts), or the share `top_p` of
+// the row's whole mass, which the histogram gives (masses).  Returns the bucket where that
+// happens; `upto` says how many entries lie in the buckets down to and including it (by mass: a
+// lower bound worked out from the masses), `all` is the total of the row.
+template <bool BY_MASS>
+__device__ int linear_level(Shared& sh, const Slice& sl, float temp, float mx, unsigned long long want, float top_p,
+                            unsigned long long& upto, unsigned long long& all) {
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < NWARPS * 256; i += THREADS) (&sh.hist[0][0])[i] = 0ull;
+  __syncthreads();
+  for_each(sl, [&](int, float raw) {
+    const float x = raw / temp;
+    const unsigned digit = linear_bucket(x, mx);
+    // (a row spreads over many buckets, so the lanes of a warp seldom meet in one)
+    atomicAdd(&sh.hist[warp][digit], BY_MASS ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 1ull);
+  });
+  __syncthreads();
+  if (threadIdx.x < 256) {
+    unsigned long long s = 0;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) s += sh.hist[w][threadIdx.x];
+    sh.hist[0][threadIdx.x] = s;
+  }
+  cluster_barrier();  // every CTA's fold is there
+  if (threadIdx.x < 256) {
+    unsigned long long s = 0;
+    for (uint32_t c = 0; c < sl.nranks; ++c) s += ld_cluster_u64(in_cta(sm32(&sh.hist[0][threadIdx.x]), c));
+    sh.tot[threadIdx.x] = s;
+  }
+  cluster_barrier();  // the folds have been read
+  if (threadIdx.x < 32) {
+    unsigned long long total = 0;
+    for (int i = threadIdx.x; i < 256; i += 32) total += sh.tot[i];
+    total = warp_sum_u64(total);
+    unsigned long long wanted = want;
+    if (BY_MASS) {
+      wanted = (unsigned long long)ceil((double)top_p * (double)total);
+      if (wanted < 1ull) wanted = 1ull;
+      if (wanted > total) wanted = total;
+    }
+    unsigned long long before = 0;
+    const int at = warp_find<true>(256, [&](int i) { return sh.tot[255 - i]; }, wanted, before);
+    if (threadIdx.x == 0) {
+      const int bucket = at >= 0 ? 255 - at : 0;  // (fewer than wanted exist: everything)
+      sh.bcast[0] = (unsigned long long)bucket;
+      sh.bcast[1] = at >= 0 ? before + sh.tot[bucket] : total;
+      sh.bcast[2] = total;
+      if (BY_MASS) {
+        // how many entries that is, at least: a bucket's entries weigh at most exp(-(255 - b) / 8) each
+        float least = 0.f;
+        for (int b = 255; b >= bucket; --b) least += (float)sh.tot[b] / (expf(-0.125f * (float)(255 - b)) * FIX_ONE);
+        sh.bcast[1] = bucket == 0 ? ~0ull : (unsigned long long)least;
+      }
+    }
+  }
+  __syncthreads();
+  const int bucket = (int)sh.bcast[0];
+  upto = sh.bcast[1];
+  all = sh.bcast[2];
+  __syncthreads();
+  return bucket;
+}
+
 // grid (cluster size, rows); the cluster spans x
 __global__ void __launch_bounds__(THREADS, 2)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temps,
@@ -345,9 +411,144 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   mx = block_max(mx, sh.fred);
   mx = cluster_max_f32(sh, sl, mx);
 
-  unsigned lo_key = 0u;  // entries with key >= lo_key are kept
   const int k = top_ks ? top_ks[r] : 0;
-  if (k > 0 && k < V) {
+  const float top_p = top_ps ? top_ps[r] : 1.f;
+  const bool by_count = k > 0 && k < V;
+  bool have_all = false;  // the row's whole mass is known (from the histogram by mass)
+  unsigned long long row_mass = 0;
+
+  // ---- the short way: one more pass puts the row into coarse buckets (by count for top-k, else by
+  // mass for top-p); the entries of the buckets down to the one that holds the cut are gathered in
+  // the first CTA's shared memory (over the histograms, which are done with), if they are few, and
+  // top-k, top-p and the draw are finished there on the exact values: the same masses, the same
+  // cuts and the same draw in index order as the passes over the row further down.
+  if ((by_count && k <= CAND_MAX) || (!by_count && top_p < 1.f)) {
+    unsigned long long upto = 0, all = 0;
+    const int bucket = by_count ? linear_level<false>(sh, sl, T, mx, (unsigned long long)k, 1.f, upto, all)
+                                : linear_level<true>(sh, sl, T, mx, 0ull, top_p, upto, all);
+    unsigned* c_idx = reinterpret_cast<unsigned*>(&sh.hist[0][0]);
+    unsigned* c_key = c_idx + CAND_MAX;
+    float* c_val = reinterpret_cast<float*>(c_key + CAND_MAX);
+    unsigned long long* c_mass = reinterpret_cast<unsigned long long*>(c_val + CAND_MAX);
+    unsigned long long* c_kept = c_mass + CAND_MAX;
+    have_all = !by_count;
+    row_mass = all;
+    if (upto <= (unsigned long long)CAND_MAX) {  // (by mass this is a lower bound: the true number shows when they are gathered)
+      // every CTA first collects what it finds in its own shared memory (it stops collecting when it
+      // has more than fit: a flat row would otherwise queue up on the counter), then the CTAs learn
+      // one another's numbers and, if all fit, put theirs into the first CTA's arrays one after another
+      unsigned* l_idx = reinterpret_cast<unsigned*>(&sh.hist[8][0]);  // 16 KB in: behind the first CTA's arrays (14 KB)
+      float* l_val = reinterpret_cast<float*>(l_idx + CAND_MAX);
+      if (threadIdx.x == 0) sh.n_cand = 0u;
+      __syncthreads();
+      for_each(sl, [&](int i, float raw) {
+        const float x = raw / T;
+        if (linear_bucket(x, mx) >= (unsigned)bucket && *(volatile unsigned*)&sh.n_cand <= (unsigned)CAND_MAX) {
+          const unsigned slot = atomicAdd(&sh.n_cand, 1u);
+          if (slot < (unsigned)CAND_MAX) {
+            l_idx[slot] = (unsigned)i;
+            l_val[slot] = x;
+          }
+        }
+      });
+      cluster_barrier();  // every CTA's number stands (and every CTA is done with the histograms)
+      int n = 0, offset = 0;
+      for (uint32_t c = 0; c < sl.nranks; ++c) {
+        const int theirs = (int)ld_cluster_u32(in_cta(sm32(&sh.n_cand), c));
+        if (c < sl.rank) offset += theirs;
+        n = theirs > CAND_MAX ? 2 * CAND_MAX : n + theirs;
+      }
+      if (n <= CAND_MAX) {
+        const int mine = (int)sh.n_cand;
+        const uint32_t a_idx = in_cta(sm32(c_idx), 0), a_val = in_cta(sm32(c_val), 0);
+        for (int i = threadIdx.x; i < mine; i += THREADS) {
+          st_cluster_u32(a_idx + 4u * (uint32_t)(offset + i), l_idx[i]);
+          st_cluster_u32(a_val + 4u * (uint32_t)(offset + i), __float_as_uint(l_val[i]));
+        }
+      }
+      cluster_barrier();  // all of them are in the first CTA (or nobody sent any)
+      if (n <= CAND_MAX) {
+        if (sl.rank == 0) {
+          for (int i = threadIdx.x; i < n; i += THREADS) {
+            c_key[i] = ordered_key(c_val[i]);
+            c_mass[i] = __float2ull_rz(expf(c_val[i] - mx) * FIX_ONE);
+          }
+          __syncthreads();
+          if (by_count) {
+            // top-k: an entry stays if fewer than k are strictly larger (values tied with the k-th stay)
+            for (int i = threadIdx.x; i < n; i += THREADS) {
+              int larger = 0;
+              const unsigned mine = c_key[i];
+              for (int j = 0; j < n; ++j) larger += c_key[j] > mine ? 1 : 0;
+              c_kept[i] = larger < k ? c_mass[i] : 0ull;
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < n; i += THREADS) c_mass[i] = c_kept[i];
+            __syncthreads();
+          }
+          if (top_p < 1.f) {
+            // top-p of the mass that top-k kept (of the whole row without top-k: the entries that were
+            // not gathered are all smaller than these): an entry stays if the mass of the strictly
+            // larger ones is below the target
+            unsigned long long s = all;
+            if (by_count) {
+              unsigned long long z = 0;
+              for (int i = threadIdx.x; i < n; i += THREADS) z += c_mass[i];
+              s = block_sum_u64(sh, z);
+            }
+            unsigned long long remaining = (unsigned long long)ceil((double)top_p * (double)s);
+            if (remaining < 1ull) remaining = 1ull;
+            if (remaining > s) remaining = s;
+            for (int i = threadIdx.x; i < n; i += THREADS) {
+              unsigned long long above = 0;
+              const unsigned mine = c_key[i];
+              for (int j = 0; j < n; ++j) above += c_key[j] > mine ? c_mass[j] : 0ull;
+              c_kept[i] = above < remaining ? c_mass[i] : 0ull;
+            }
+          } else {
+            for (int i = threadIdx.x; i < n; i += THREADS) c_kept[i] = c_mass[i];
+          }
+          __syncthreads();
+          unsigned long long z = 0;
+          unsigned lowest = 0xFFFFFFFFu;  // the smallest key that stays
+          for (int i = threadIdx.x; i < n; i += THREADS) {
+            z += c_kept[i];
+            if (c_kept[i] > 0ull) lowest = min(lowest, c_key[i]);
+          }
+          const unsigned long long total = block_sum_u64(sh, z);
+          lowest = ~block_max_u32(sh, ~lowest);
+          const unsigned long long rnd = splitmix64(rand_keys ? rand_keys[r] : 0ull);
+          const unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
+          for (int i = threadIdx.x; i < n; i += THREADS) {
+            unsigned long long before = 0;
+            const unsigned mine = c_idx[i];
+            for (int j = 0; j < n; ++j) before += c_idx[j] < mine ? c_kept[j] : 0ull;
+            if (before <= target && target - before < c_kept[i]) out_tokens[r] = (int)mine;  // exactly one entry
+          }
+          if (threadIdx.x == 0) {
+            sh.bcast[0] = (unsigned long long)lowest;
+            sh.bcast[1] = total;
+          }
+        }
+        if (!prow) return;
+        cluster_barrier();  // the cut and the total stand in the first CTA
+        const unsigned cut_key = (unsigned)ld_cluster_u64(in_cta(sm32(&sh.bcast[0]), 0));
+        const unsigned long long total = ld_cluster_u64(in_cta(sm32(&sh.bcast[1]), 0));
+        cluster_barrier();  // read by all
+        const float inv = 1.f / (float)total;
+        for (int i = sl.lo + threadIdx.x; i < sl.hi; i += THREADS) {
+          const float x = row[i] / T;
+          const unsigned long long w = ordered_key(x) >= cut_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
+          prow[i] = (float)w * inv;
+        }
+        return;
+      }
+    }
+  }
+
+  // ---- the long way (a flat row, many equal values, or a large k): exact radix descents over the row
+  unsigned lo_key = 0u;  // entries with key >= lo_key are kept
+  if (by_count) {
     unsigned prefix = 0u;
     unsigned long long remaining = (unsigned long long)k;
     for (int level = 0; level < 4; ++level) {
@@ -357,104 +558,17 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     }
     lo_key = prefix;  // the k-th largest key
   }
-
-  const float top_p = top_ps ? top_ps[r] : 1.f;
-  if (k > 0 && k < V && k <= CAND_MAX) {
-    // ---- top-k left few entries: they are gathered in the first CTA's shared memory (over the
-    // histograms, which are done with) and top-p and the draw are finished there, with the same
-    // masses, the same cut and the same draw in index order as the passes over the row below.
-    unsigned* c_idx = reinterpret_cast<unsigned*>(&sh.hist[0][0]);
-    unsigned* c_key = c_idx + CAND_MAX;
-    float* c_val = reinterpret_cast<float*>(c_key + CAND_MAX);
-    unsigned long long* c_mass = reinterpret_cast<unsigned long long*>(c_val + CAND_MAX);
-    unsigned long long* c_kept = c_mass + CAND_MAX;
-    if (threadIdx.x == 0) sh.n_cand = 0u;
-    cluster_barrier();  // every CTA is done with the histograms; the counter is zero
-    const uint32_t a_cnt = in_cta(sm32(&sh.n_cand), 0), a_idx = in_cta(sm32(c_idx), 0), a_val = in_cta(sm32(c_val), 0);
-    for_each(sl, [&](int i, float raw) {
-      const float x = raw / T;
-      if (ordered_key(x) >= lo_key) {
-        const unsigned slot = atom_add_cluster_u32(a_cnt, 1u);
-        if (slot < (unsigned)CAND_MAX) {
-          st_cluster_u32(a_idx + 4u * slot, (unsigned)i);
-          st_cluster_u32(a_val + 4u * slot, __float_as_uint(x));
-        }
-      }
-    });
-    cluster_barrier();  // all of them are in the first CTA
-    const int n = (int)ld_cluster_u32(a_cnt);
-    if (n <= CAND_MAX) {  // (more: values tied with the k-th largest; the passes below take those)
-      if (sl.rank == 0) {
-        for (int i = threadIdx.x; i < n; i += THREADS) {
-          c_key[i] = ordered_key(c_val[i]);
-          c_mass[i] = __float2ull_rz(expf(c_val[i] - mx) * FIX_ONE);
-        }
-        __syncthreads();
-        unsigned cut_key = lo_key;
-        if (top_p < 1.f) {
-          unsigned long long z = 0;
-          for (int i = threadIdx.x; i < n; i += THREADS) z += c_mass[i];
-          const unsigned long long s = block_sum_u64(sh, z);
-          unsigned long long remaining = (unsigned long long)ceil((double)top_p * (double)s);
-          if (remaining < 1ull) remaining = 1ull;
-          if (remaining > s) remaining = s;
-          // an entry stays if the mass of the strictly larger ones is below the target
-          unsigned lowest = 0xFFFFFFFFu;
-          for (int i = threadIdx.x; i < n; i += THREADS) {
-            unsigned long long above = 0;
-            const unsigned mine = c_key[i];
-            for (int j = 0; j < n; ++j) above += c_key[j] > mine ? c_mass[j] : 0ull;
-            const bool keep = above < remaining;
-            c_kept[i] = keep ? c_mass[i] : 0ull;
-            if (keep) lowest = min(lowest, mine);
-          }
-          lowest = ~block_max_u32(sh, ~lowest);
-          cut_key = lowest > lo_key ? lowest : lo_key;
-        } else {
-          for (int i = threadIdx.x; i < n; i += THREADS) c_kept[i] = c_mass[i];
-        }
-        __syncthreads();
-        unsigned long long z = 0;
-        for (int i = threadIdx.x; i < n; i += THREADS) z += c_kept[i];
-        const unsigned long long total = block_sum_u64(sh, z);
-        const unsigned long long rnd = splitmix64(rand_keys ? rand_keys[r] : 0ull);
-        const unsigned long long target = __umul64hi(rnd, total);  // uniform in [0, total)
-        for (int i = threadIdx.x; i < n; i += THREADS) {
-          unsigned long long before = 0;
-          const unsigned mine = c_idx[i];
-          for (int j = 0; j < n; ++j) before += c_idx[j] < mine ? c_kept[j] : 0ull;
-          if (before <= target && target - before < c_kept[i]) out_tokens[r] = (int)mine;  // exactly one entry
-        }
-        if (threadIdx.x == 0) {
-          sh.bcast[0] = (unsigned long long)cut_key;
-          sh.bcast[1] = total;
-        }
-      }
-      if (!prow) {
-        cluster_barrier();  // nobody leaves while the first CTA's counter may still be read
-        return;
-      }
-      cluster_barrier();  // the cut and the total stand in the first CTA
-      const unsigned cut_key = (unsigned)ld_cluster_u64(in_cta(sm32(&sh.bcast[0]), 0));
-      const unsigned long long total = ld_cluster_u64(in_cta(sm32(&sh.bcast[1]), 0));
-      cluster_barrier();  // read by all
-      const float inv = 1.f / (float)total;
-      for (int i = sl.lo + threadIdx.x; i < sl.hi; i += THREADS) {
-        const float x = row[i] / T;
-        const unsigned long long w = ordered_key(x) >= cut_key ? __float2ull_rz(expf(x - mx) * FIX_ONE) : 0ull;
-        prow[i] = (float)w * inv;
-      }
-      return;
-    }
-  }
   if (top_p < 1.f) {
-    // mass of what top-k kept
-    unsigned long long z = 0;
-    for_each(sl, [&](int, float raw) {
-      const float x = raw / T;
-      if (ordered_key(x) >= lo_key) z += __float2ull_rz(expf(x - mx) * FIX_ONE);
-    });
-    const unsigned long long s = cluster_sum_u64(sh, sl, block_sum_u64(sh, z));
+    // mass of what top-k kept (of the whole row without top-k: the histogram by mass has it)
+    unsigned long long s = row_mass;
+    if (!have_all) {
+      unsigned long long z = 0;
+      for_each(sl, [&](int, float raw) {
+        const float x = raw / T;
+        if (ordered_key(x) >= lo_key) z += __float2ull_rz(expf(x - mx) * FIX_ONE);
+      });
+      s = cluster_sum_u64(sh, sl, block_sum_u64(sh, z));
+    }
     unsigned long long remaining = (unsigned long long)ceil((double)top_p * (double)s);
     if (remaining < 1ull) remaining = 1ull;
     if (remaining > s) remaining = s;

@@ -815,8 +815,8 @@ def tie_keeping_probs(logits, t, k, p):
 
 def test_sampling_with_few_and_with_many_entries_left_by_top_k(ops):
     """Top-k up to 256 finishes in one CTA's shared memory on the entries that passed; more
-    entries than that (a larger k, or values tied with the k-th largest) take the passes over
-    the row.  Both must give the same distribution and the same draw."""
+    entries than that (a larger k, values tied with the k-th largest, a flat row under top-p
+    alone) take the passes over the row.  Both must give the same distribution and the same draw."""
     v = 5000
     g = torch.Generator().manual_seed(3)
     base = torch.randn(v, generator=g) * 2
@@ -826,9 +826,10 @@ def test_sampling_with_few_and_with_many_entries_left_by_top_k(ops):
     order = edge.argsort(descending=True)
     edge[order[199:201]] = float(edge[order[199]])  # the 200th and the 201st largest are equal
     many_edge = base.clone()
-    many_edge[order[255:258]] = float(many_edge[order[255]])  # 256th..258th equal: 258 entries pass k = 256
-    cases = [(base, 1.0, 256, 0.9), (base, 0.7, 300, 0.8), (tied, 1.0, 10, 0.9), (edge, 1.3, 200, 0.5), (many_edge, 1.0, 256, 0.95),
-             (base, 1.0, 1, 0.5), (base, 0.9, 40, 1.0), (tied, 0.8, 500, 0.3)]  # fmt: skip
+    many_edge[order[511:514]] = float(many_edge[order[511]])  # 512th..514th equal: 514 entries pass k = 512
+    cases = [(base, 1.0, 512, 0.9), (base, 0.7, 600, 0.8), (tied, 1.0, 10, 0.9), (edge, 1.3, 200, 0.5), (many_edge, 1.0, 512, 0.95),
+             (base, 1.0, 1, 0.5), (base, 0.9, 40, 1.0), (tied, 0.8, 500, 0.3), (base, 0.5, 0, 0.9), (base, 0.3, 0, 0.5), (tied, 0.6, 0, 0.7),
+             (edge * 3, 1.0, 0, 0.99)]  # fmt: skip
     logits = torch.stack([c[0] for c in cases])
     temps = torch.tensor([c[1] for c in cases])
     ks = torch.tensor([c[2] for c in cases], dtype=torch.int32)
