@@ -1,0 +1,60 @@
+"""Host-side decisions of the step function that need no device: the list of query tiles a step
+hands to the prompt attention kernel, and the shape a step of many tokens is captured for."""
+
+from __future__ import annotations
+
+import random
+from types import SimpleNamespace
+
+import numpy as np
+
+from kvforge_b200.engine.step import BatchItem, ModelRunner, _Layout
+
+
+def layout_with(q_lens, ctx_lens, tile_sizes, n_cap=None, b_cap=None):
+    nb = len(q_lens)
+    lay = _Layout(n_cap or sum(q_lens), b_cap or nb, 4, 1, nb, tuple(tile_sizes))
+    host = np.zeros(lay.total, dtype=np.int32)
+    host[lay.off["qsl"] : lay.off["qsl"] + nb + 1] = np.concatenate([[0], np.cumsum(q_lens)])
+    host[lay.off["ctx"] : lay.off["ctx"] + nb] = ctx_lens
+    return lay, host
+
+
+def test_query_tiles_cover_every_query_once_longest_walk_first():
+    rng = random.Random(4)
+    for _ in range(50):
+        nb = rng.randint(1, 9)
+        q_lens = [rng.choice([1, 1, 2, 5, 31, 32, 33, 100]) for _ in range(nb)]
+        ctx_lens = [q + rng.randint(0, 300) for q in q_lens]
+        sizes = rng.sample([1, 16, 32, 64, 128], 2)
+        lay, host = layout_with(q_lens, ctx_lens, sizes, n_cap=sum(q_lens) + rng.randint(0, 70), b_cap=nb + rng.randint(0, 3))
+        counts = ModelRunner._fill_query_tiles(None, host, lay, nb)
+        for tq in lay.tile_sizes:
+            cap = lay.tile_cap(tq)
+            total, n_multi, n_single = counts[tq]
+            assert n_single == sum(1 for q in q_lens if q == 1)
+            assert total == sum(-(-q // tq) for q in q_lens) <= cap
+            for name, n_live, wanted in ((f"qtiles_{tq}", total, q_lens), (f"qtiles_multi_{tq}", n_multi, [q if q > 1 else 0 for q in q_lens])):
+                tiles = host[lay.off[name] : lay.off[name] + 2 * cap].reshape(cap, 2)
+                assert (tiles[n_live:, 0] == -1).all()
+                seen = [set() for _ in range(nb)]
+                last_keys = []
+                for seq, q0 in tiles[:n_live]:
+                    assert q0 % tq == 0 and 0 <= q0 < wanted[seq]
+                    assert q0 not in seen[seq]
+                    seen[seq].add(int(q0))
+                    last_keys.append(ctx_lens[seq] - q_lens[seq] + min(q_lens[seq], q0 + tq))
+                assert [len(s) for s in seen] == [-(-w // tq) for w in wanted]
+                assert last_keys == sorted(last_keys, reverse=True)
+
+
+def test_the_shape_a_step_is_captured_for():
+    runner = SimpleNamespace(max_model_len=8192)
+    items = [BatchItem("a", [1] * 700, 300, "last"), BatchItem("b", [5], 2000, "last")]
+    # contexts up to 2,001 tokens: graphs reach the next power of two; a single token is among the sequences
+    assert ModelRunner._graph_key(runner, items, 704, 2) == (704, 2, 2048, True)
+    assert ModelRunner._graph_key(runner, items[:1], 704, 1) == (704, 1, 1024, False)
+    # the decode form (one token per sequence) has no such distinction
+    assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 5000, "last")], 1, 1) == (1, 1, 8192, False)
+    runner.max_model_len = 4096
+    assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 4000, "last")], 1, 1)[2] == 4096
