@@ -10,7 +10,10 @@ Different in how: all index arrays are int32 and are packed on the host into one
 buffer that goes to the device in a single copy; the device copy lives at fixed addresses.
 A step of single tokens only is, per batch-size bucket, captured once as a CUDA graph and
 replayed (the arrays it reads are then laid out for the bucket's full width, so the
-addresses inside the graph stay valid).
+addresses inside the graph stay valid); so is a step of many tokens, for its token count
+rounded up, from the second time its shape comes.  Beside the arrays that umarhassan-cloud/kvforge
+prepares, a step carries lists of its tiles of queries (sequence, first query) for kernels that
+take a fixed number of queries of one sequence per CTA.
 """
 
 from __future__ import annotations
