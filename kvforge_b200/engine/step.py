@@ -32,9 +32,11 @@ from .runtime import QueryTiles, Runtime, StepContext
 
 # graphs for shorter contexts than this are not told apart
 MIN_GRAPH_CONTEXT = 1024
-# steps of at least this many tokens are replayed as graphs too, padded to a multiple of GRAPH_TOKEN_STEP
+# steps of at least this many tokens (more than the decode GEMM takes) are replayed as graphs too, padded to a
+# multiple of GRAPH_TOKEN_STEP: a few decoding requests beside a short portion of a prompt are some 150 kernels,
+# which take longer to launch from Python than to run
 # (padding is work: 224 tokens beside 1,056 cost a fifth more); a shape is captured the second time it comes
-MIN_GRAPH_TOKENS = 512
+MIN_GRAPH_TOKENS = 17
 GRAPH_TOKEN_STEP = 64
 
 

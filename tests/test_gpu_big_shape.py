@@ -78,7 +78,7 @@ def test_llama_1b_width_generation_uses_graphs_and_the_device_token_loop(big):
 
 
 def test_steps_of_many_tokens_replay_as_graphs_with_the_same_logits(big):
-    """A step of 512 tokens or more is replayed as a CUDA graph made for its token count rounded up
+    """A step of more than 16 tokens is replayed as a CUDA graph made for its token count rounded up
     to 64 and its sequence count rounded up to a bucket (here at its first coming); the padding
     must change nothing."""
     from kvforge_b200 import CacheConfig
