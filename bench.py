@@ -501,9 +501,17 @@ def run_load(args, cfg) -> dict:
 
     from kvforge_b200 import CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
 
-    nreq = args.batch if args.batch != 8 else 64
     rng = random.Random(0)
-    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(128, 2048))] for _ in range(nreq)]
+    if args.short_prompts:
+        # many short requests that end at different times: most steps are a batch of decoding
+        # requests beside the short prompt of one that was just admitted
+        nreq = args.batch if args.batch != 8 else 256
+        prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(16, 256))] for _ in range(nreq)]
+        params = [SamplingParams(max_tokens=rng.randint(16, 128), temperature=0.0, ignore_eos=True) for _ in prompts]
+    else:
+        nreq = args.batch if args.batch != 8 else 64
+        prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(128, 2048))] for _ in range(nreq)]
+        params = [SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True)] * nreq
     engine = InferenceEngine(EngineConfig(
         model=cfg, cache=CacheConfig(block_size=16, num_blocks=None, kv_cache_memory_gb=16.0),
         scheduler=SchedulerConfig(max_num_seqs=64, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT), dtype="bfloat16",
@@ -511,10 +519,10 @@ def run_load(args, cfg) -> dict:
     # the same load twice untimed: every graph the timed pass replays exists by then (a shape of
     # many tokens is captured at its second coming)
     for _ in range(2):
-        engine.generate(prompts, SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True))
+        engine.generate(prompts, params)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    outs = engine.generate(prompts, SamplingParams(max_tokens=256, temperature=0.0, ignore_eos=True))
+    outs = engine.generate(prompts, params)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     n_in, n_out = sum(len(q) for q in prompts), sum(len(o.output_token_ids) for o in outs)
@@ -570,6 +578,7 @@ def main() -> int:
     ap.add_argument("--temperature", type=float, default=0.8, help="with --only sample (0 = greedy)")
     ap.add_argument("--top-k", type=int, default=50, help="with --only sample (0 = off)")
     ap.add_argument("--top-p", type=float, default=0.9, help="with --only sample (1 = off)")
+    ap.add_argument("--short-prompts", action="store_true", help="with --only load: 256 requests with prompts of 16 to 256 tokens and 16 to 128 generated tokens")
     ap.add_argument("--peaked", action="store_true", help="with --only sample: rows with a few likely tokens and a long tail instead of normal noise")
     ap.add_argument("--shape", default="gate_up", help="with --only gemm: qkv, o, gate_up, down or lm_head")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch")
