@@ -40,6 +40,12 @@ def _project(rt, name: str, x: torch.Tensor, w: torch.Tensor):
         y = rt.buf(name, n, width)
         ops.gemm_skinny(x, w, y)
         return y
+    splits = ops.library_splits(n, width, w.shape[1]) if x.dtype == torch.bfloat16 else 1
+    if splits > 1:
+        # a few dozen tokens: the library product over slices of K, summed by the same norm
+        part = ops.Partials(rt.buf(name + "_part", splits * n, width, torch.float32, cap=_PART_ROWS).view(splits, n, width))
+        ops.linear_split_k(x, w, part)
+        return part
     y = rt.buf(name, n, width)
     ops.linear(x, w, y)
     return y

@@ -732,6 +732,23 @@ def test_head_dim_is_checked(ops):
         ops.check_head_dim(512)
 
 
+@pytest.mark.parametrize("m,n,k", [(17, 2048, 2048), (64, 2048, 8192), (100, 3072, 3072), (128, 512, 4096)])
+def test_library_product_over_slices_of_k(ops, m, n, k):
+    """The batched library product that serves a few dozen tokens: its float slices sum to x W^T."""
+    g = torch.Generator().manual_seed(m + n)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    splits = ops.library_splits(m, n, k)
+    assert splits in (2, 4) and ops.library_splits(8, n, k) == 1 and ops.library_splits(m, 4 * k, k) == 1
+    part = ops.Partials(torch.full((splits, m, n), float("nan"), device="cuda"))
+    ops.linear_split_k(dev(x), dev(w), part)
+    got = part.t.sum(0).cpu().double()
+    want = x.double() @ w.double().t()
+    assert float((got - want).abs().max()) < 1e-5 * float(want.abs().max())
+    with pytest.raises(ValueError):
+        ops.linear_split_k(dev(x), dev(w), ops.Partials(torch.empty(5, m, n, device="cuda")))
+
+
 # ------------------------------------------------------------------ sampling
 
 
