@@ -7,7 +7,15 @@ batches of prompt portions and decoded tokens, a token-budget scheduler, samplin
 device, all on hand-written CUDA kernels for sm_100a (in bfloat16 and in true float32).
 """
 
-from .config.engine_config import CacheConfig, EngineConfig, SchedulerConfig
+import os as _os
+
+# The library's matrix products inside a captured step get the workspace that cuBLASLt is given
+# when it is first used; with torch's default (1 MiB) the products of a 2,048-token step at the
+# widths of Llama-3.1-8B run 5 % slower captured than launched one by one.  64 MiB (the unit is
+# KiB) unless the caller has said otherwise.
+_os.environ.setdefault("CUBLASLT_WORKSPACE_SIZE", "65536")
+
+from .config.engine_config import CacheConfig, EngineConfig, SchedulerConfig  # noqa: E402
 from .config.model_config import ConfigError, ModelConfig, RopeScaling
 from .config.registry import PRESETS, register_architecture
 from .engine.request import FinishReason, Request, RequestOutput, RequestStatus
