@@ -58,3 +58,15 @@ def test_the_shape_a_step_is_captured_for():
     assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 5000, "last")], 1, 1) == (1, 1, 8192, False)
     runner.max_model_len = 4096
     assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 4000, "last")], 1, 1)[2] == 4096
+
+
+def test_when_the_library_product_is_cut_into_slices_of_k():
+    from kvforge_b200 import ops
+
+    # a few dozen tokens, an output no wider than K, K of 2,048 or more: 4 slices up to 64 rows, 2 up to 128
+    assert ops.library_splits(17, 2048, 2048) == 4 and ops.library_splits(64, 2048, 8192) == 4
+    assert ops.library_splits(65, 4096, 14336) == 2 and ops.library_splits(128, 3072, 3072) == 2
+    # the decode GEMM's rows, many rows, a wide output, a short K: the plain product
+    assert ops.library_splits(16, 2048, 2048) == 1 and ops.library_splits(129, 2048, 8192) == 1
+    assert ops.library_splits(32, 16384, 2048) == 1 and ops.library_splits(32, 96, 160) == 1
+    assert ops.library_splits(32, 2048, 2048 + 64) == 1  # K that does not cut into 4 slices of whole 64s
