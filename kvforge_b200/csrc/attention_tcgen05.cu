@@ -74,6 +74,7 @@ struct TcAttnParams {
   const int* ctx_lens;
   const int* work;  // n_work pairs (sequence or -1, first query of the tile), or null: the grid's y and z say which
   int* err;
+  int num_seqs;  // a list entry that names a sequence beyond these is a dead tile
   int q_stride, out_stride, bt_stride;
   int nh, nkv, block_size, bs_shift;
   int window;
@@ -322,11 +323,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int g = p.nh / p.nkv;
   const int tq = BM / g;
   // which tile of queries: from the list (made on the host, longest walk first), else from the grid
-  const int b = p.work ? p.work[2 * blockIdx.y] : (int)blockIdx.y;
+  int b = p.work ? p.work[2 * blockIdx.y] : (int)blockIdx.y;
   const int q0 = p.work ? p.work[2 * blockIdx.y + 1] : (int)(gridDim.z - 1 - blockIdx.z) * tq;  // the longest walks first
+  if (b >= p.num_seqs) b = -1;  // whatever a list holds, nothing outside the step's arrays is read
   const int q_begin = b >= 0 ? p.qsl[b] : 0, q_len = b >= 0 ? p.qsl[b + 1] - q_begin : 0;
   const int ctx = b >= 0 ? p.ctx_lens[b] : 0;
-  const bool live = q_len > 0 && ctx > 0 && q0 < q_len;  // uniform over the CTA
+  const bool live = q_len > 0 && ctx > 0 && q0 >= 0 && q0 < q_len;  // uniform over the CTA
   // A CTA without a tile leaves at once; the grid's first CTA stays for the dependency wait, so
   // the grid does not complete before its predecessor.
   if (!live && (blockIdx.x | blockIdx.y | blockIdx.z) != 0) return;
@@ -709,6 +711,7 @@ KVF_API int kvf_paged_attention_tcgen05_bf16(const void* q, void* out, const voi
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
   p.block_tables = block_tables; p.qsl = qsl; p.ctx_lens = ctx_lens; p.err = err;
   p.work = work;
+  p.num_seqs = B;
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.bs_shift = -1;

@@ -105,4 +105,12 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& u, float* f) {
   }
 }
 
+// One pair of a rotary encoding: (x1, x2) turned by the angle whose cosine and sine are given.
+// The roundings are spelled out (a product, then a fused multiply-add) so that every kernel
+// that rotates gives the same bits, whichever of them a step's token count selects.
+__device__ __forceinline__ void rotate_pair(float x1, float x2, float cs, float sn, float& y1, float& y2) {
+  y1 = __fmaf_rn(x1, cs, -__fmul_rn(x2, sn));
+  y2 = __fmaf_rn(x2, cs, __fmul_rn(x1, sn));
+}
+
 }  // namespace kvf

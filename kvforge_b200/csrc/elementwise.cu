@@ -253,8 +253,10 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__
     float s, c;
     sincosf(pos * inv_freq[j], &s, &c);
     const float x1 = value(head * d + j), x2 = value(head * d + j + half);
-    const T y1 = from_float<T>(x1 * c - x2 * s);
-    const T y2 = from_float<T>(x2 * c + x1 * s);
+    float r1, r2;
+    rotate_pair(x1, x2, c, s, r1, r2);
+    const T y1 = from_float<T>(r1);
+    const T y2 = from_float<T>(r2);
     if (head < nh) {
       qdst[(size_t)head * d + j] = y1;
       qdst[(size_t)head * d + j + half] = y2;
@@ -332,8 +334,10 @@ __global__ void rope_cache_heads_kernel(T* __restrict__ qkv, const float* __rest
   }
   T y1, y2;
   if (head < nh + nkv) {
-    y1 = from_float<T>(x1 * cs - x2 * sn);
-    y2 = from_float<T>(x2 * cs + x1 * sn);
+    float r1, r2;
+    rotate_pair(x1, x2, cs, sn, r1, r2);
+    y1 = from_float<T>(r1);
+    y2 = from_float<T>(r2);
   } else {
     y1 = from_float<T>(x1);
     y2 = from_float<T>(x2);
@@ -431,8 +435,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restri
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const float cs = cs_sn[j0 + e], sn = cs_sn[half + j0 + e];
-      y1[e] = x1[e] * cs - x2[e] * sn;
-      y2[e] = x2[e] * cs + x1[e] * sn;
+      rotate_pair(x1[e], x2[e], cs, sn, y1[e], y2[e]);
     }
     T* dst = nullptr;
     if (head < nh) {

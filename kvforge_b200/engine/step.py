@@ -139,9 +139,11 @@ class ModelRunner:
         self.pdl = bool(pdl)  # programmatic dependent launch between the kernels of a step
         # the most sequences a step can hold is a bucket of its own, so that no batch size goes without a graph
         self.graph_buckets = sorted({b for b in graph_buckets if b <= rt.max_seqs} | ({rt.max_seqs} if rt.max_seqs <= max(graph_buckets) else set())) or [rt.max_seqs]
-        # keyed by (tokens, sequences, longest context the graph reaches, single-token sequences in a step of many tokens)
-        self._graphs: dict[tuple[int, int, int, bool], tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
-        self.graph_kernels: dict[tuple[int, int, int, bool], int] = {}  # kernels of this library inside each captured graph
+        # keyed by (tokens, sequences, longest context the graph reaches, single-token sequences in a step of
+        # many tokens, decode form); the form is part of the key because a step of many tokens padded to as many
+        # tokens as sequences (64 tokens in 64 sequences) is another graph than 64 decoding sequences
+        self._graphs: dict[tuple, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self.graph_kernels: dict[tuple, int] = {}  # kernels of this library inside each captured graph
         self.num_kernel_launches = 0  # kernels of this library launched by steps, replays included
         self.num_graph_kernels = 0  # those of them that ran inside replayed graphs
         self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
@@ -150,7 +152,7 @@ class ModelRunner:
         self._dev: torch.Tensor | None = None
         self._copy_done: torch.cuda.Event | None = None
         self._tile_counts: dict[int, tuple[int, int, int]] = {}
-        self._graph_seen: dict[tuple[int, int, int, bool], int] = {}  # how often a shape of many tokens has come
+        self._graph_seen: dict[tuple, int] = {}  # how often a shape of many tokens has come
         self.graph_after = 2  # ... and at which coming it is captured
         # made once for the widest step there can be, so its address never changes
         self._ensure(self._layout(rt.max_tokens, rt.max_seqs, self.max_width, rt.max_tokens).total)
@@ -181,13 +183,28 @@ class ModelRunner:
             self._copy_done = torch.cuda.Event()
         self._copy_done.record()
 
-    def _fill(self, items: Sequence[BatchItem], lay: _Layout) -> tuple[int, int, int, int, int]:
-        """Write the arrays of ``items`` into the host buffer under layout ``lay``."""
+    def _fill(self, items: Sequence[BatchItem], lay: _Layout, padded: bool = False, tiles: bool | None = None) -> tuple[int, int, int, int, int]:
+        """Write the arrays of ``items`` into the host buffer under layout ``lay``.
+
+        ``padded``: the layout is wider than the items (a captured shape), so the rest is filled
+        first with padding: token 0 at position 0, written to no slot (-1), part of no sequence.
+        A padding sequence has no queries (``qsl[b+1] == qsl[b]``), no context and state slot -1;
+        a part that keeps state must leave a sequence without queries alone.
+        ``tiles``: whether the lists of query tiles are written; by default only when some
+        sequence brings more than one token (a step of single tokens launches no kernel that
+        reads them).  A captured step of many tokens always launches such a kernel, so its lists
+        are written whatever the items."""
         if self._copy_done is not None:
             self._copy_done.synchronize()  # the last step's copy has left the host buffer
         host = self._host.numpy()
         bm, bs = self.block_manager, self.block_size
         o = lay.off
+        if padded:
+            host[o["token_ids"] : o["token_ids"] + lay.n_cap] = 0
+            host[o["positions"] : o["positions"] + lay.n_cap] = 0
+            host[o["feedback_rows"] : o["feedback_rows"] + lay.n_cap] = -1
+            host[o["logit_rows"] : o["logit_rows"] + lay.r_cap] = 0
+            host[o["slots"] : o["slots"] + self.n_groups * lay.n_cap] = -1
         n = 0
         rows: list[int] = []
         max_q = max_ctx = 0
@@ -222,7 +239,7 @@ class ModelRunner:
             n += k
             qsl[b + 1] = n
             ctx[b] = end
-            sslots[b] = self.state_slots.slot(item.seq_id) if (self.state_slots and self.state_slots.has(item.seq_id)) else 0
+            sslots[b] = self.state_slots.slot(item.seq_id) if (self.state_slots and self.state_slots.has(item.seq_id)) else -1
             max_q = max(max_q, k)
             max_ctx = max(max_ctx, end)
         nb = len(items)
@@ -230,11 +247,13 @@ class ModelRunner:
         for b in range(nb, lay.b_cap):
             qsl[b + 1] = n
             ctx[b] = 0
-            sslots[b] = 0
+            sslots[b] = -1
         if len(rows) > lay.r_cap:
             raise RuntimeError("more logit rows than the layout holds")
         host[o["logit_rows"] : o["logit_rows"] + len(rows)] = rows
-        self._tile_counts = self._fill_query_tiles(host, lay, nb) if max_q > 1 else {}
+        if tiles is None:
+            tiles = max_q > 1
+        self._tile_counts = self._fill_query_tiles(host, lay, nb) if tiles else {}
         return n, nb, len(rows), max_q, max_ctx
 
     def _fill_query_tiles(self, host: np.ndarray, lay: _Layout, nb: int) -> dict[int, tuple[int, int, int]]:
@@ -324,7 +343,7 @@ class ModelRunner:
         single = all(len(it.token_ids) == 1 and it.wanted() == [0] for it in items)
         if self.cuda_graphs and single and len(items) <= self.graph_buckets[-1]:
             bucket = next(b for b in self.graph_buckets if b >= len(items))
-            return self._step_graph(items, bucket, bucket)
+            return self._step_graph(items, bucket, bucket, decode_form=True)
         n_tok = sum(len(it.token_ids) for it in items)
         if n_tok > self.rt.max_tokens or len(items) > self.rt.max_seqs:
             raise ValueError(
@@ -339,11 +358,11 @@ class ModelRunner:
             b_cap = next(b for b in self.graph_buckets if b >= len(items))
             n_cap = min(self.rt.max_tokens, -(-n_tok // GRAPH_TOKEN_STEP) * GRAPH_TOKEN_STEP)
             if n_rows <= b_cap and n_cap >= n_tok:
-                key = self._graph_key(items, n_cap, b_cap)
+                key = self._graph_key(items, n_cap, b_cap, decode_form=False)
                 seen = self._graph_seen.get(key, 0) + 1
                 self._graph_seen[key] = seen
                 if seen >= self.graph_after:  # a shape that comes once is not worth a capture
-                    return self._step_graph(items, n_cap, b_cap)
+                    return self._step_graph(items, n_cap, b_cap, decode_form=False)
         width = max(-(-(it.start_pos + len(it.token_ids)) // self.block_size) for it in items)
         lay = self._layout(n_tok, len(items), width, n_rows)
         self._ensure(lay.total)
@@ -363,38 +382,28 @@ class ModelRunner:
         self._pool = pool
         self.model.attach_cache(pool.caches)
 
-    def _graph_key(self, items: Sequence[BatchItem], n_cap: int, b_cap: int) -> tuple[int, int, int, bool]:
+    def _graph_key(self, items: Sequence[BatchItem], n_cap: int, b_cap: int, decode_form: bool) -> tuple:
         # A graph fixes its grids, so it is made for contexts up to a bound: the next power of two
         # (kernels whose grid follows the longest context then launch at most twice what they need).
         max_ctx = max(it.start_pos + len(it.token_ids) for it in items)
         reach = min(self.max_model_len, max(MIN_GRAPH_CONTEXT, 1 << max(0, max_ctx - 1).bit_length()))
         # a step of many tokens is captured once for batches with single-token sequences among them
         # (those go to the decode kernel) and once for batches without
-        singles = n_cap != b_cap and any(len(it.token_ids) == 1 for it in items)
-        return (n_cap, b_cap, reach, singles)
+        singles = (not decode_form) and any(len(it.token_ids) == 1 for it in items)
+        return (n_cap, b_cap, reach, singles, bool(decode_form))
 
-    def _step_graph(self, items: Sequence[BatchItem], n_cap: int, b_cap: int) -> torch.Tensor:
-        """Replay the step as a graph made for ``n_cap`` tokens in ``b_cap`` sequences (``n_cap ==
-        b_cap``: one token each, the decode form)."""
+    def _step_graph(self, items: Sequence[BatchItem], n_cap: int, b_cap: int, decode_form: bool) -> torch.Tensor:
+        """Replay the step as a graph made for ``n_cap`` tokens in ``b_cap`` sequences.
+        ``decode_form``: every sequence brings one token and wants its logits (then ``n_cap ==
+        b_cap``); else a sequence may bring any number of the tokens."""
         lay = self._layout(n_cap, b_cap, self.max_width, b_cap)
         self._ensure(lay.total)
-        # padding tokens: token 0 at position 0, written to no slot, part of no sequence
-        if self._copy_done is not None:
-            self._copy_done.synchronize()
-        host, o = self._host.numpy(), lay.off
-        host[o["token_ids"] : o["token_ids"] + n_cap] = 0
-        host[o["positions"] : o["positions"] + n_cap] = 0
-        host[o["feedback_rows"] : o["feedback_rows"] + n_cap] = -1
-        host[o["logit_rows"] : o["logit_rows"] + b_cap] = 0
-        for g in range(self.n_groups):
-            host[o["slots"] + g * n_cap : o["slots"] + (g + 1) * n_cap] = -1
-        n, _, r, max_q, max_ctx = self._fill(items, lay)
-        self._upload(lay.total)
-        key = self._graph_key(items, n_cap, b_cap)
-        reach = key[2]
+        key = self._graph_key(items, n_cap, b_cap, decode_form)
         entry = self._graphs.get(key)
         if entry is None:
             entry = self._capture(key, lay)
+        n, _, r, max_q, max_ctx = self._fill(items, lay, padded=True, tiles=not decode_form)
+        self._upload(lay.total)
         graph, logits = entry
         graph.replay()
         self.num_kernel_launches += self.graph_kernels[key]
@@ -403,11 +412,17 @@ class ModelRunner:
         self.num_tokens_processed += n
         return logits[:r]
 
-    def _capture(self, key: tuple[int, int, int, bool], lay: _Layout):
-        n_cap, b_cap, reach, singles = key
+    def _capture(self, key: tuple, lay: _Layout):
+        """Make the graph of a shape.  Nothing of the step that asked for it runs here: the one
+        eager run that sizes every buffer and loads every kernel outside the capture sees a batch
+        of padding only (no sequence has a query, no token has a slot), so it writes no key, no
+        value and no state; the step's own arrays go to the device afterwards and the step runs
+        once, as the first replay."""
+        n_cap, b_cap, reach, singles, decode_form = key
+        self._fill((), lay, padded=True, tiles=not decode_form)
+        self._upload(lay.total)
         # one token per sequence: the decode form; else a sequence may bring up to all the tokens
-        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if n_cap == b_cap else n_cap, reach, bound=reach, all_tiles=True, singles=singles)
-        # one eager run first: sizes every buffer and loads every kernel outside the capture
+        ctx = self._context(lay, n_cap, b_cap, b_cap, 1 if decode_form else n_cap, reach, bound=reach, all_tiles=True, singles=singles)
         self.model.forward(ctx)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()

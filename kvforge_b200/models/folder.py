@@ -20,6 +20,7 @@ def write_random_model(
     store_dtype: torch.dtype = torch.bfloat16,
     init_std: float = 0.02,
     norm_std: float = 0.0,
+    device: torch.device | str = "cpu",
 ) -> Path:
     """``config`` is a typed model configuration (its ``architectures[0]`` picks the model)."""
     arch = get_architecture(config.architectures[0])
@@ -27,5 +28,5 @@ def write_random_model(
     model = DecoderModel(spec)
     skip = (spec.lm_head_name,) if spec.tie_word_embeddings else ()
     return write_model_dir(
-        model_dir, config.to_hf_dict(), model.expected_weights(), seed, store_dtype, init_std, norm_std, skip
+        model_dir, config.to_hf_dict(), model.expected_weights(), seed, store_dtype, init_std, norm_std, skip, device
     )

@@ -342,8 +342,9 @@ def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
     microseconds (its chain of dependent reads, its share of the merge), so ranges are not
     short: 256 keys, 512 with many (sequence, kv head) pairs (measured inside the decode step at
     1, 8 and 64 sequences), and more when the context is so long that there would be more than
-    ``MAX_ATTN_SPLITS`` of them.  Ranges start
-    at multiples of it, whatever the batch."""
+    ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of it.  Since the size follows the
+    number of sequences, so does the order in which a context's keys are merged: a caller that
+    wants sums that do not depend on the batch at all (the 32-bit path) passes ``num_seqs=1``."""
     pairs = num_seqs * nkv
     split = 512 if pairs >= 256 else 256
     while -(-max_context // split) > MAX_ATTN_SPLITS:

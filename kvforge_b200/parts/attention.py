@@ -122,7 +122,9 @@ class PagedAttention(Mixer):
         # context of this step (of this graph, when the step is captured)
         bound = max(ctx.context_bound, ctx.max_context_len, rt.max_model_len, 1)
         reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
-        split = ops.attention_split_size(ctx.num_seqs, self.nkv, bound)
+        # 32-bit: one range size whatever the batch, so a request's sums come in the same order beside
+        # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
+        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound)
         # made for the smallest range size, so that one buffer serves every batch size
         smallest = ops.attention_split_size(1, 1, bound)
         sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)

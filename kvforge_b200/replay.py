@@ -14,6 +14,12 @@ wanted.  All entries of a step run as one batch.  ``end``: requests that are fin
 the step; their pages are given back.  A step with wanted places writes
 ``<out>/<step>.f32``: little-endian float32 ``[wanted, vocab]`` in the order of the entries
 and of ``want``.  After every step ``done <step>`` is printed and flushed.
+
+The page size is 16 tokens unless ``--block-size`` says otherwise, the pool holds
+``--max-tokens`` tokens (each request rounded up to 64, or to the page if that is larger)
+unless ``--num-blocks`` gives it in pages, and ``--cuda-graphs`` replays the steps the way
+bfloat16 generation does by default: captured graphs for padded shapes, every shape captured
+the first time it comes.
 """
 
 from __future__ import annotations
@@ -23,7 +29,8 @@ import json
 import sys
 from pathlib import Path
 
-PAGE = 16  # tokens per page of the replay engine
+PAGE = 16  # tokens per page of the replay engine unless --block-size is given
+ROUND = 64  # --max-tokens counts each request rounded up to this (or to the page, if larger)
 
 
 def parse_args(argv=None):
@@ -33,30 +40,59 @@ def parse_args(argv=None):
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
     ap.add_argument("--max-live", type=int, default=16, help="most requests live at a time")
+    ap.add_argument("--block-size", type=int, default=PAGE, help="tokens per page of the cache")
+    ap.add_argument("--num-blocks", type=int, default=None, help="pages of the pool (default: what --max-tokens needs)")
+    ap.add_argument("--cuda-graphs", action="store_true", help="replay steps as captured CUDA graphs, as generation does")
     return ap.parse_args(argv)
 
 
+def pages_for(max_tokens: int, block_size: int, max_live: int) -> int:
+    """Pages that hold ``max_tokens`` tokens when each live request's count was rounded up to
+    ``ROUND``: with pages that divide ``ROUND`` exactly that many tokens; with other page sizes
+    every live request may waste the better part of a page on top."""
+    pages = -(-int(max_tokens) // block_size)
+    if ROUND % block_size:
+        pages += max_live
+    return max(1, pages)
+
+
 class TraceRunner:
-    def __init__(self, model_dir: str, dtype: str, max_tokens: int, max_live: int = 16) -> None:
+    def __init__(
+        self,
+        model_dir: str,
+        dtype: str,
+        max_tokens: int,
+        max_live: int = 16,
+        block_size: int = PAGE,
+        num_blocks: int | None = None,
+        cuda_graphs: bool = False,
+    ) -> None:
         from .config.engine_config import CacheConfig
         from .engine.core import EngineCore
 
-        num_blocks = max(1, -(-int(max_tokens) // PAGE))
-        budget = num_blocks * PAGE
+        block_size = int(block_size)
+        if block_size <= 0:
+            raise ValueError("--block-size must be positive")
+        if num_blocks is None:
+            num_blocks = pages_for(max_tokens, block_size, max_live)
+        budget = max(int(max_tokens), block_size)
         self.core = EngineCore.from_model_dir(
             model_dir,
             dtype=dtype,
-            cache=CacheConfig(block_size=PAGE, num_blocks=num_blocks, watermark=0.0),
+            cache=CacheConfig(block_size=block_size, num_blocks=int(num_blocks), watermark=0.0),
             max_num_seqs=max_live,
             max_num_batched_tokens=budget,
             max_model_len=budget,
-            cuda_graphs=False,
-            lazy_buffers=True,
+            cuda_graphs=bool(cuda_graphs),
+            # captured graphs hold buffer addresses, so buffers are made for the whole budget at once
+            lazy_buffers=not cuda_graphs,
         )
+        self.core.runner.graph_after = 1  # a replayed trace shows each shape once: capture it the first time
         self.lengths: dict[str, int] = {}
 
-    def step(self, record: dict):
-        """Runs one step; returns the float logits ``[wanted, vocab]`` on the host, or ``None``."""
+    def step(self, record: dict, to_host: bool = True):
+        """Runs one step; returns the float logits ``[wanted, vocab]`` on the host (or, with
+        ``to_host=False``, a copy on the device), or ``None`` if nothing was wanted."""
         from .engine.step import BatchItem
 
         core = self.core
@@ -81,7 +117,7 @@ class TraceRunner:
         logits = core.runner.step(items) if items else None
         host = None
         if logits is not None and logits.shape[0] > 0:
-            host = logits.cpu()
+            host = logits.cpu() if to_host else logits.clone()
         elif logits is not None:
             import torch
 
@@ -100,7 +136,7 @@ def main(argv=None) -> int:
     args = parse_args(argv)
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
-    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.max_live)
+    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.max_live, args.block_size, args.num_blocks, args.cuda_graphs)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -71,17 +71,20 @@ def write_model_dir(
     init_std: float = 0.02,
     norm_std: float = 0.0,
     skip: tuple[str, ...] = (),
+    device: torch.device | str = "cpu",
 ) -> Path:
     """Write ``config.json`` and ``model.safetensors``.  Floating tensors are stored in
-    ``store_dtype``; ``skip`` names tensors to leave out (a tied output head)."""
+    ``store_dtype``; ``skip`` names tensors to leave out (a tied output head).  ``device``:
+    where the values are drawn (a device's generator draws other values than the host's; the
+    folder is the record either way)."""
     d = Path(model_dir)
     d.mkdir(parents=True, exist_ok=True)
     tensors = {}
     for name, decl in expected.items():
         if name in skip:
             continue
-        t = draw(name, decl, seed, "cpu", init_std, norm_std)
-        tensors[name] = t if decl.kind == "table" else t.to(store_dtype)
+        t = draw(name, decl, seed, device, init_std, norm_std)
+        tensors[name] = (t if decl.kind == "table" else t.to(store_dtype)).cpu()
     write_safetensors(d / "model.safetensors", tensors)
     (d / "config.json").write_text(json.dumps(config_json, indent=2))
     return d

@@ -23,7 +23,7 @@ def big(tmp_path_factory):
     cfg = ModelConfig(**{**base.__dict__, "num_layers": 2, "max_position_embeddings": 4096})
     folder = tmp_path_factory.mktemp("big") / "llama-1b-width-2-layers"
     # weights large enough that attention is not uniform: q.k has a spread of a few units
-    write_random_model(folder, cfg, seed=5, store_dtype=torch.bfloat16, init_std=0.03, norm_std=0.05)
+    write_random_model(folder, cfg, seed=5, store_dtype=torch.bfloat16, init_std=0.03, norm_std=0.05, device="cuda")
     reqs = {"a": random_tokens(cfg.vocab_size, 300, seed=1), "b": random_tokens(cfg.vocab_size, 97, seed=2)}
     plain = PlainLlama(folder, device="cuda")  # the plain implementation in 32-bit, run on the GPU for speed
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -119,20 +119,82 @@ def test_steps_of_many_tokens_replay_as_graphs_with_the_same_logits(big):
 @pytest.mark.parametrize("preset", ["llama-3.2-3b", "llama-3.1-8b"])
 def test_wider_llamas_with_head_size_128(tmp_path_factory, preset):
     """The widths of Llama-3.2-3B (24 heads of 128 over 8 kv heads, hidden 3072) and Llama-3.1-8B
-    (hidden 4096, intermediate 14336, untied head), two layers each: whole prompts, portions beside
-    decoded tokens, and the last tokens one by one, in bfloat16 against the plain implementation."""
+    (hidden 4096, intermediate 14336, untied head), two layers each: whole prompts, portions of
+    changing size, portions beside decoded tokens, and the last tokens one by one, in 32-bit and in
+    bfloat16 against the plain implementation."""
     from test_gpu_replay import check, replay_in_process
 
     base = PRESETS[preset]
     cfg = ModelConfig(**{**base.__dict__, "num_layers": 2, "max_position_embeddings": 4096})
     folder = tmp_path_factory.mktemp("wide") / f"{preset}-width-2-layers"
-    write_random_model(folder, cfg, seed=6, store_dtype=torch.bfloat16, init_std=0.025, norm_std=0.05)
+    write_random_model(folder, cfg, seed=6, store_dtype=torch.bfloat16, init_std=0.025, norm_std=0.05, device="cuda")
     reqs = {"a": random_tokens(cfg.vocab_size, 210, seed=3), "b": random_tokens(cfg.vocab_size, 66, seed=4)}
     plain = PlainLlama(folder, device="cuda")
     torch.backends.cuda.matmul.allow_tf32 = False
     ref = {rid: plain.logits(t).cpu() for rid, t in reqs.items()}
     del plain
     torch.cuda.empty_cache()
-    for steps in (traces.whole(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {"a": 190, "b": 50}, max_live=2, seed=2)):
-        outputs = replay_in_process(folder, "bfloat16", steps)
-        check(steps, outputs, ref, 6e-2)
+    for dtype, tol in (("float32", 5e-5), ("bfloat16", 6e-2)):
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {"a": 190, "b": 50}, max_live=2, seed=2)):
+            outputs = replay_in_process(folder, dtype, steps)
+            check(steps, outputs, ref, tol)
+
+
+def test_llama_1b_whole_model_of_16_layers(tmp_path_factory):
+    """Every layer of the Llama-3.2-1B shape (16 layers, tied head, llama3 scaling with factor 32),
+    random weights: a few hundred tokens whole, in portions of changing size, with the last tokens
+    one by one and two requests mixed, in 32-bit and bfloat16, against the plain implementation."""
+    from test_gpu_replay import check, replay_in_process
+
+    cfg = PRESETS["llama-3.2-1b"]
+    assert cfg.num_layers == 16
+    folder = tmp_path_factory.mktemp("whole") / "llama-1b-16-layers"
+    write_random_model(folder, cfg, seed=8, store_dtype=torch.bfloat16, init_std=0.03, norm_std=0.05, device="cuda")
+    reqs = {"a": random_tokens(cfg.vocab_size, 260, seed=5), "b": random_tokens(cfg.vocab_size, 75, seed=6)}
+    plain = PlainLlama(folder, device="cuda")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = {rid: plain.logits(t).cpu() for rid, t in reqs.items()}
+    del plain
+    torch.cuda.empty_cache()
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 8e-2)):
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 16), traces.mixed(reqs, {"a": 240, "b": 60}, max_live=2, seed=3)):
+            outputs = replay_in_process(folder, dtype, steps)
+            check(steps, outputs, ref, tol)
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16", "bfloat16-graphs"])
+@pytest.mark.parametrize("live", [24, 64])
+def test_llama_1b_width_many_requests_decoding_at_once(big, mode, live):
+    """24 and 64 requests decoding at once at the width of Llama-3.2-1B (the batch-64 point of the
+    benchmark): the library products of 17 to 64 rows, their slices of K, the graphs of the buckets
+    32 and 64, key ranges of 512 once there are 256 pairs of sequence and kv head; requests leave
+    and join on the way.  Logits stay on the device and are compared there."""
+    import random
+
+    from test_gpu_replay import run_trace
+
+    folder, _, _ = big
+    vocab = PRESETS["llama-3.2-1b"].vocab_size
+    rng = random.Random(live)
+    reqs = {f"m{i}": random_tokens(vocab, rng.randint(14, 36), seed=300 + i) for i in range(live + live // 2)}
+    prompt_lens = {rid: max(1, len(t) - rng.randint(6, 10)) for rid, t in reqs.items()}
+    plain = PlainLlama(folder, device="cuda")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+    del plain
+    steps = traces.many_decoders(reqs, prompt_lens, live, seed=live)
+    dtype = mode.split("-")[0]
+    tol = 5e-5 if dtype == "float32" else 6e-2
+    outputs, runner = run_trace(folder, dtype, steps, max_live=64, to_host=False, cuda_graphs=mode.endswith("graphs"))
+    rows = 0
+    for s, places, got in zip(steps, traces.wanted_places(steps), outputs):
+        assert got is not None and got.shape[0] == len(places)
+        for i, (rid, pos) in enumerate(places):
+            err = rel_err(got[i], ref[rid][pos])
+            assert err < tol, f"step {s['step']} request {rid} position {pos}: error {err:.3e}"
+            rows += 1
+    assert rows > 10 * live
+    if mode.endswith("graphs"):
+        assert (64 if live > 32 else 32) in {key[1] for key in runner.core.runner._graphs if key[4]}
+    del runner, outputs, ref
+    torch.cuda.empty_cache()

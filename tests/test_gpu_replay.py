@@ -67,17 +67,23 @@ def mean_bound(folders, oracle):
     return out
 
 
-def replay_in_process(model_dir, dtype, steps, max_tokens=None):
+def run_trace(model_dir, dtype, steps, max_tokens=None, to_host=True, **kw):
+    """Replays ``steps``; returns the logits of every step and the runner (for its counters)."""
     from kvforge_b200.replay import TraceRunner
 
-    runner = TraceRunner(str(model_dir), dtype, max_tokens or traces.tokens_needed(steps))
+    page = max(64, kw.get("block_size", 16))
+    runner = TraceRunner(str(model_dir), dtype, max_tokens or traces.tokens_needed(steps, page), **kw)
     out = []
     for s in steps:
-        logits = runner.step(s)
+        logits = runner.step(s, to_host=to_host)
         out.append(None if logits is None else logits.clone())
     runner.core.block_manager.check_invariants()
     assert runner.core.block_manager.num_free_blocks == runner.core.block_manager.num_blocks
-    return out
+    return out, runner
+
+
+def replay_in_process(model_dir, dtype, steps, max_tokens=None, **kw):
+    return run_trace(model_dir, dtype, steps, max_tokens, **kw)[0]
 
 
 def check(steps, outputs, ref_logits, tol, mean_tol=None):
@@ -102,24 +108,130 @@ def check(steps, outputs, ref_logits, tol, mean_tol=None):
     return worst
 
 
+REGIMES = ["whole", "tail", "portions", "mixed"]
+
+
+def regime_steps(reqs, regime):
+    if regime == "whole":
+        return traces.whole(reqs)
+    if regime == "tail":
+        return traces.tail_one_by_one(reqs, 32)
+    if regime == "portions":
+        return traces.portions(reqs)
+    prompt_lens = {rid: max(1, len(t) - 12) for rid, t in reqs.items()}
+    steps = traces.mixed(reqs, prompt_lens, max_live=4, seed=5)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and any(len(e["tokens"]) > 1 for s in steps for e in s["entries"])
+    return steps
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(TINY))
-@pytest.mark.parametrize("regime", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("regime", REGIMES)
 def test_replay_regimes(folders, oracle, mean_bound, name, dtype, regime):
     reqs, ref = oracle[name]
-    if regime == "whole":
-        steps = traces.whole(reqs)
-    elif regime == "tail":
-        steps = traces.tail_one_by_one(reqs, 32)
-    elif regime == "portions":
-        steps = traces.portions(reqs)
-    else:
-        prompt_lens = {rid: max(1, len(t) - 12) for rid, t in reqs.items()}
-        steps = traces.mixed(reqs, prompt_lens, max_live=4, seed=5)
-        assert max(len(s["entries"]) for s in steps) >= 3
-        assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and any(len(e["tokens"]) > 1 for s in steps for e in s["entries"])
+    steps = regime_steps(reqs, regime)
     outputs = replay_in_process(folders[name], dtype, steps)
     check(steps, outputs, ref, TOL[dtype], mean_bound[name] if dtype == "bfloat16" else None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", [n for n in TINY if TINY[n]["block_size"] != 16])
+@pytest.mark.parametrize("regime", REGIMES)
+def test_replay_regimes_at_the_models_own_page_size(folders, oracle, mean_bound, name, dtype, regime):
+    """Pages of 8 (tiny-b), 4 (tiny-c) and 32 (tiny-e) tokens instead of the replay program's 16."""
+    reqs, ref = oracle[name]
+    steps = regime_steps(reqs, regime)
+    outputs = replay_in_process(folders[name], dtype, steps, block_size=TINY[name]["block_size"])
+    check(steps, outputs, ref, TOL[dtype], mean_bound[name] if dtype == "bfloat16" else None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+@pytest.mark.parametrize("regime", REGIMES)
+def test_replay_regimes_as_captured_graphs(folders, oracle, name, dtype, regime):
+    """The same four cuttings the way bfloat16 generation runs them by default: steps of single
+    tokens and steps of more than 16 tokens replayed as CUDA graphs made for padded shapes
+    (tokens up to a multiple of 64, sequences up to a bucket), every shape captured the first
+    time it comes.  A step asks for the last row of each entry, since a step that wants more rows
+    than it has sequences is not replayed as a graph."""
+    reqs, ref = oracle[name]
+    steps = traces.last_only(regime_steps(reqs, regime))
+    outputs, runner = run_trace(folders[name], dtype, steps, block_size=TINY[name]["block_size"], cuda_graphs=True)
+    check(steps, outputs, ref, TOL[dtype])
+    mr = runner.core.runner
+    forms = {key[4] for key in mr._graphs}
+    if regime != "whole":
+        assert True in forms, "no step of single tokens was replayed as a graph"
+    if any(sum(len(e["tokens"]) for e in s["entries"]) >= 17 for s in steps):
+        assert False in forms, "no step of many tokens was replayed as a graph"
+    assert mr.num_graph_kernels > 0
+
+
+DECODER_MODELS = ["tiny-b", "tiny-d", "tiny-e"]
+
+
+@pytest.fixture(scope="module")
+def decoder_oracle(folders):
+    """Per model and number of live requests: requests of different lengths and their plain logits."""
+    cache = {}
+
+    def get(name, live):
+        if (name, live) not in cache:
+            import random
+
+            rng = random.Random(live)
+            vocab = TINY[name]["cfg"].vocab_size
+            reqs = {f"{name}-m{i}": random_tokens(vocab, rng.randint(14, 40), seed=500 + i) for i in range(live + live // 2)}
+            prompt_lens = {rid: max(1, len(t) - rng.randint(6, 12)) for rid, t in reqs.items()}
+            plain = PlainLlama(folders[name])
+            cache[(name, live)] = (reqs, prompt_lens, {rid: plain.logits(t) for rid, t in reqs.items()})
+        return cache[(name, live)]
+
+    return get
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16", "bfloat16-graphs"])
+@pytest.mark.parametrize("name", DECODER_MODELS)
+@pytest.mark.parametrize("live", [17, 24, 33, 64])
+def test_many_requests_decoding_at_once(folders, decoder_oracle, name, mode, live):
+    """Steps of 17 to 64 single decoded tokens, with requests leaving and joining: above 16 rows
+    every matrix product of a bfloat16 step takes another route than below (the library instead of
+    the decode GEMM, its product over slices of K for the narrow outputs), the graphs are those of
+    the buckets 32 and 64, and a joining prompt makes a mixed step with dozens of single tokens."""
+    reqs, prompt_lens, ref = decoder_oracle(name, live)
+    steps = traces.many_decoders(reqs, prompt_lens, live, seed=live)
+    assert any(len(s["entries"]) == live and all(len(e["tokens"]) == 1 for e in s["entries"]) for s in steps)
+    dtype = mode.split("-")[0]
+    outputs, runner = run_trace(folders[name], dtype, steps, max_live=64, block_size=TINY[name]["block_size"], cuda_graphs=mode.endswith("graphs"))
+    check(steps, outputs, ref, TOL[dtype])
+    if mode.endswith("graphs"):
+        buckets = {key[1] for key in runner.core.runner._graphs if key[4]}
+        assert (64 if live > 32 else 32) in buckets
+
+
+def test_float32_logits_of_a_request_do_not_depend_on_how_many_decode_beside_it(folders):
+    """One request with a context of several hundred keys decodes alone and beside 129 others
+    (260 pairs of sequence and kv head).  In 32-bit the key ranges of the decode attention have one
+    size whatever the batch, and every product sums in a fixed order, so the rows are bit-equal."""
+    name = "tiny-a"
+    vocab = TINY[name]["cfg"].vocab_size
+    long = random_tokens(vocab, 604, seed=77)
+    others = {f"o{i}": random_tokens(vocab, 6, seed=900 + i) for i in range(129)}
+    alone = traces.tail_one_by_one({"x": long}, tail=4)
+    crowd = [{"step": 0, "entries": [{"id": "x", "tokens": long[:600], "want": [599]}], "end": []}]
+    for i in range(0, 129, 43):  # the short prompts, 43 a step, all but their last token
+        crowd.append({"step": len(crowd), "entries": [{"id": rid, "tokens": t[:5], "want": [4]} for rid, t in list(others.items())[i : i + 43]], "end": []})
+    for k in range(4):
+        entries = [{"id": "x", "tokens": [long[600 + k]], "want": [0]}]
+        if k == 0:
+            entries += [{"id": rid, "tokens": [t[5]], "want": [0]} for rid, t in others.items()]
+        crowd.append({"step": len(crowd), "entries": entries, "end": list(others) if k == 0 else (["x"] if k == 3 else [])})
+    a = replay_in_process(folders[name], "float32", alone, max_live=130)
+    b = replay_in_process(folders[name], "float32", crowd, max_live=130)
+    assert torch.equal(a[0][0], b[0][0])  # the prompt's last row
+    for k in range(4):
+        assert torch.equal(a[1 + k][0], b[4 + k][0]), f"decoded token {k}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -52,12 +52,24 @@ def test_the_shape_a_step_is_captured_for():
     runner = SimpleNamespace(max_model_len=8192)
     items = [BatchItem("a", [1] * 700, 300, "last"), BatchItem("b", [5], 2000, "last")]
     # contexts up to 2,001 tokens: graphs reach the next power of two; a single token is among the sequences
-    assert ModelRunner._graph_key(runner, items, 704, 2) == (704, 2, 2048, True)
-    assert ModelRunner._graph_key(runner, items[:1], 704, 1) == (704, 1, 1024, False)
+    assert ModelRunner._graph_key(runner, items, 704, 2, False) == (704, 2, 2048, True, False)
+    assert ModelRunner._graph_key(runner, items[:1], 704, 1, False) == (704, 1, 1024, False, False)
     # the decode form (one token per sequence) has no such distinction
-    assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 5000, "last")], 1, 1) == (1, 1, 8192, False)
+    assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 5000, "last")], 1, 1, True) == (1, 1, 8192, False, True)
     runner.max_model_len = 4096
-    assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 4000, "last")], 1, 1)[2] == 4096
+    assert ModelRunner._graph_key(runner, [BatchItem("b", [5], 4000, "last")], 1, 1, True)[2] == 4096
+
+
+def test_a_step_of_many_tokens_padded_to_its_sequence_count_is_no_decode_graph():
+    """64 tokens in 64 sequences come two ways: 64 decoding requests (the decode form), or some
+    decoding requests beside a short portion of a prompt, padded to 64 and 64.  The two are
+    different graphs (the second computes every query of the portion) and must not share a key."""
+    runner = SimpleNamespace(max_model_len=4096)
+    decoding = [BatchItem(f"d{i}", [3], 100 + i, "last") for i in range(64)]
+    mixed = [BatchItem(f"d{i}", [3], 100 + i, "last") for i in range(40)] + [BatchItem("p", [1] * 20, 0, "last")]
+    a = ModelRunner._graph_key(runner, decoding, 64, 64, True)
+    b = ModelRunner._graph_key(runner, mixed, 64, 64, False)
+    assert a != b and a[:3] == b[:3]
 
 
 def test_when_the_library_product_is_cut_into_slices_of_k():

@@ -70,6 +70,54 @@ def mixed(requests: dict[str, list[int]], prompt_lens: dict[str, int], max_live:
     return steps
 
 
+def last_only(steps: list[dict]) -> list[dict]:
+    """The same steps asking for the logits of each entry's last token alone (a step of many
+    tokens is replayed as a captured graph only when it wants no more rows than it has sequences)."""
+    return [{**s, "entries": [{**e, "want": [len(e["tokens"]) - 1]} for e in s["entries"]]} for s in steps]
+
+
+def many_decoders(requests: dict[str, list[int]], prompt_lens: dict[str, int], live: int, seed: int = 0, join_p: float = 0.6) -> list[dict]:
+    """Steps of many single decoded tokens: ``live`` requests are admitted (their prompts whole, a
+    few per step), then every live request decodes one token per step; requests are of different
+    lengths, so they leave at different times, and when one has left another joins, its prompt
+    beside the decoded tokens of the others, so that the number of sequences moves across the
+    sizes a step is padded to.  Logits are wanted for the last token of every entry."""
+    rng = random.Random(seed)
+    waiting = list(requests)
+    pos: dict[str, int] = {}
+    steps: list[dict] = []
+
+    def emit(entries, end):
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+
+    def advance(rid, n):
+        toks, p = requests[rid], pos[rid]
+        pos[rid] = p + n
+        return {"id": rid, "tokens": toks[p : p + n], "want": [n - 1]}
+
+    first = [waiting.pop(0) for _ in range(min(live, len(waiting)))]
+    for i in range(0, len(first), 5):  # prompts, five requests a step
+        group = first[i : i + 5]
+        for rid in group:
+            pos[rid] = 0
+        emit([advance(rid, prompt_lens[rid]) for rid in group], [])
+    while pos:
+        entries, end = [], []
+        for rid in list(pos):
+            entries.append(advance(rid, 1))
+            if pos[rid] == len(requests[rid]):
+                end.append(rid)
+                del pos[rid]
+        joiners = 0
+        while waiting and len(entries) < live and rng.random() < join_p and joiners < 2:
+            rid = waiting.pop(0)
+            pos[rid] = 0
+            entries.append(advance(rid, prompt_lens[rid]))
+            joiners += 1
+        emit(entries, end)
+    return steps
+
+
 def tokens_needed(steps: list[dict], page: int = 64) -> int:
     """Most tokens live requests hold at any time, each request rounded up to ``page``."""
     held: dict[str, int] = {}
