@@ -21,12 +21,6 @@
 // memory into the range's partial result; the CTA that finishes last among the ranges of a
 // (sequence, kv head) merges the ranges in range order.
 //
-// With ROPE the kernel also does what the rotation kernel would do before it: the queries, and
-// the new token's key and value, come as the float slices of the split-K product that made
-// them; every CTA sums and turns the queries of its heads itself, and the warp whose unit holds
-// the new position turns the key, writes key and value to the cache, and puts them into its
-// tile in shared memory (the copy of that page may have read the slot before or after).
-//
 // With CLUSTER the CTAs of the ranges of one (sequence, kv head) are one thread-block cluster
 // (up to 16), and the merge goes through distributed shared memory: every CTA leaves its partial
 // result in its own shared memory, a cluster barrier, then CTA r merges a slice of the outputs by
@@ -66,16 +60,6 @@ struct DecParams {
   int split_size, max_splits, grid_splits;
   int total_rows;  // rows of the cache seen as [rows][D]: a copy from this row reads zeros
   float scale_log2;
-  // ROPE only: the projections as float slices [nsplit][tokens][(nh + 2 nkv) * D], one token per sequence
-  const float* qkv_part;
-  long long part_stride;  // floats between slices
-  int nsplit;
-  const int* positions;   // per token
-  const float* inv_freq;  // [D / 2]
-  const int* slots;       // per token: where its key and value go (block * block_size + offset), < 0: nowhere
-  bf16* kcache;
-  bf16* vcache;
-  long long num_slots;
 };
 
 __device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -178,11 +162,10 @@ template <int D, int ST> struct Shape {
   static constexpr uint32_t RED_BYTES = NWARPS * 8 * (D + 2) * 4;
   static constexpr uint32_t CPART_OFFSET = RED_BYTES;
   static_assert(CPART_OFFSET + 8 * (D + 2) * 4 <= TILES_BYTES, "the partial results lie in the tile area");
-  static constexpr uint32_t ANGLE_OFFSET = FLAG_OFFSET + 16;  // ROPE: cos then sin of the token's D/2 angles
-  static constexpr uint32_t SMEM_BYTES = ANGLE_OFFSET + NWARPS * D * 4;  // a copy per warp: no block-wide barrier
+  static constexpr uint32_t SMEM_BYTES = FLAG_OFFSET + 16;
 };
 
-template <int D, int ST, bool ROPE, bool CLUSTER>
+template <int D, int ST, bool CLUSTER>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const DecParams p) {
@@ -239,14 +222,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
     }
   };
-  // ROPE: the token's angles, once per CTA (positions come with the step's metadata, so this
-  // too is done before the wait).  Pair j turns dims j and j + D/2.
   const int token = q_begin + q_len - 1;
-  float* angles = reinterpret_cast<float*>(smem_raw + S::ANGLE_OFFSET) + warp * D;
-  if (ROPE && live) {
-    for (int j = lane; j < D / 2; j += 32) sincosf((float)p.positions[token] * p.inv_freq[j], &angles[D / 2 + j], &angles[j]);
-    __syncwarp();
-  }
   int issued = 0;
   if (kv_hi < ctx) {  // no key of this range is written during this step
     for (; issued < STAGES && issued < n_mine; ++issued) issue(issued);
@@ -276,28 +252,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     {
       const int head = lane >> 2;
       const bool valid = head < g;
-      if (ROPE) {
-        // sum of the slices in slice order, then the turn: the same arithmetic as the rotation kernel
-        const float* src = p.qkv_part + (size_t)token * ((size_t)(p.nh + 2 * p.nkv) * D) + (size_t)(kvh * g + (valid ? head : 0)) * D;
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int col = 16 * k + ((lane & 3) << 1) + 8 * h;
-            float2 a = make_float2(0.f, 0.f), bb = make_float2(0.f, 0.f);
-            if (valid) {
-              for (int sl = 0; sl < p.nsplit; ++sl) {
-                const float2 u = *reinterpret_cast<const float2*>(src + (size_t)sl * p.part_stride + col);
-                const float2 w = *reinterpret_cast<const float2*>(src + (size_t)sl * p.part_stride + col + D / 2);
-                a.x += u.x; a.y += u.y; bb.x += w.x; bb.y += w.y;
-              }
-            }
-            const float2 cs = *reinterpret_cast<const float2*>(angles + col), sn = *reinterpret_cast<const float2*>(angles + D / 2 + col);
-            qf[k][h] = kvf_pack_bf16x2(a.x * cs.x - bb.x * sn.x, a.y * cs.y - bb.y * sn.y);
-            qf[k + D / 32][h] = kvf_pack_bf16x2(bb.x * cs.x + a.x * sn.x, bb.y * cs.y + a.y * sn.y);
-          }
-        }
-      } else {
+      {
         const bf16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * g + (valid ? head : 0)) * D;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -305,32 +260,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           qf[kk][0] = valid ? *reinterpret_cast<const uint32_t*>(src + col) : 0u;
           qf[kk][1] = valid ? *reinterpret_cast<const uint32_t*>(src + col + 8) : 0u;
         }
-      }
-    }
-    // ROPE: the warp whose unit holds the new position makes the new key and value now, while its
-    // copies are in flight: lane j holds key dims j and j + D/2 (+32 for D = 128) and value dims 2 lane, +1 (+64)
-    const int new_unit = (ROPE && kv_hi == ctx) ? (ctx - 1 - kv_lo) / UNIT : -1;
-    const bool makes_new = new_unit >= 0 && (new_unit % NWARPS) == warp;
-    uint32_t new_k[D / 64][2], new_v[D / 64];
-    if (ROPE && makes_new) {
-      const size_t width = (size_t)(p.nh + 2 * p.nkv) * D;
-      const float* ksrc = p.qkv_part + (size_t)token * width + (size_t)(p.nh + kvh) * D;
-      const float* vsrc = ksrc + (size_t)p.nkv * D;
-#pragma unroll
-      for (int t = 0; t < D / 64; ++t) {
-        const int j = lane + 32 * t;
-        float x1 = 0.f, x2 = 0.f;
-        float2 v = make_float2(0.f, 0.f);
-        for (int sl = 0; sl < p.nsplit; ++sl) {
-          x1 += ksrc[(size_t)sl * p.part_stride + j];
-          x2 += ksrc[(size_t)sl * p.part_stride + j + D / 2];
-          const float2 u = *reinterpret_cast<const float2*>(vsrc + (size_t)sl * p.part_stride + 2 * lane + 64 * t);
-          v.x += u.x; v.y += u.y;
-        }
-        const float cs = angles[j], sn = angles[D / 2 + j];
-        new_k[t][0] = __bfloat16_as_ushort(__float2bfloat16_rn(x1 * cs - x2 * sn));
-        new_k[t][1] = __bfloat16_as_ushort(__float2bfloat16_rn(x2 * cs + x1 * sn));
-        new_v[t] = kvf_pack_bf16x2(v.x, v.y);
       }
     }
     // this lane's two heads: n0 = 2 (lane%4), n0 + 1.  o[mt][e]: dim 16 mt + lane/4 (+8 for e >= 2), head n0 + (e & 1)
@@ -347,29 +276,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       ok = __all_sync(0xffffffffu, bar_wait(bars + 8 * st, (i / STAGES) & 1, p.err));
       if (!ok) break;
       const bool edge = key0 < first_seen || key0 + UNIT > kv_hi;
-      if (ROPE && makes_new && warp + NWARPS * i == new_unit) {
-        // this unit holds the new position: key and value go to the cache and into the tile
-        const int r = ctx - 1 - key0;
-        long long slot = p.slots ? (long long)p.slots[token] : -1;
-        if (slot >= p.num_slots) {
-          if (lane == 0 && p.err) atomicOr(p.err, 2);
-          slot = -1;
-        }
-        const size_t crow = slot >= 0 ? (((size_t)(slot / p.block_size) * p.nkv + kvh) * p.block_size + (size_t)(slot % p.block_size)) * D : 0;
-#pragma unroll
-        for (int t = 0; t < D / 64; ++t) {
-          const int j = lane + 32 * t, j2 = j + D / 2, dv = 2 * lane + 64 * t;
-          asm volatile("st.shared.b16 [%0], %1;" ::"r"(ks + unit_off(r, j >> 3) + ((j & 7) << 1)), "h"((unsigned short)new_k[t][0]) : "memory");
-          asm volatile("st.shared.b16 [%0], %1;" ::"r"(ks + unit_off(r, j2 >> 3) + ((j2 & 7) << 1)), "h"((unsigned short)new_k[t][1]) : "memory");
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(vs + unit_off(r, dv >> 3) + ((dv & 7) << 1)), "r"(new_v[t]) : "memory");
-          if (slot >= 0) {
-            p.kcache[crow + j] = __ushort_as_bfloat16((unsigned short)new_k[t][0]);
-            p.kcache[crow + j2] = __ushort_as_bfloat16((unsigned short)new_k[t][1]);
-            *reinterpret_cast<uint32_t*>(p.vcache + crow + dv) = new_v[t];
-          }
-        }
-        __syncwarp();
-      }
       if (key0 + UNIT > kv_hi) {
         // keys at or past kv_hi inside a live page hold whatever was there: their values are zeroed
         // (their scores are masked below), so that nothing of them reaches the sum
@@ -568,14 +474,14 @@ int cache_map(CUtensorMap* map, const void* ptr, long long rows, int d) {
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int D, int ST, bool ROPE>
+template <int D, int ST>
 int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int B, bool cluster, cudaStream_t st) {
   size_t smem = Shape<D, ST>::SMEM_BYTES;
   static_assert(Shape<D, ST>::FLAG_OFFSET >= NWARPS * 1024 * 4, "the range merge's weights lie in the tile area");
   const dim3 grid(p.grid_splits, B, p.nkv);
   if (cluster) {
     // the ranges of a (sequence, kv head) as one cluster; more than 8 CTAs need the non-portable size
-    auto kern = attn_decode_tma_kernel<D, ST, ROPE, true>;
+    auto kern = attn_decode_tma_kernel<D, ST, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess && p.grid_splits > 8) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e == cudaSuccess) {
@@ -598,7 +504,7 @@ int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p,
     }
     (void)cudaGetLastError();  // a cluster this size does not fit here: the ticket form does the same work
   }
-  auto kern = attn_decode_tma_kernel<D, ST, ROPE, false>;
+  auto kern = attn_decode_tma_kernel<D, ST, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   return launch(kern, grid, dim3(NWARPS * 32), smem, st, mk, mv, p);
@@ -608,16 +514,7 @@ int launch_dec(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p,
 
 namespace {
 
-struct RopeSource {  // where ROPE finds the projections; all null/zero without it
-  const float* qkv_part = nullptr;
-  long long part_stride = 0;
-  int nsplit = 0;
-  const int* positions = nullptr;
-  const float* inv_freq = nullptr;
-  const int* slots = nullptr;
-};
-
-int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, const void* vcache,
+int run_dec(const void* q, void* out, const void* kcache, const void* vcache,
             const int* block_tables, const int* qsl, const int* ctx_lens, int B, int q_stride, int out_stride,
             int bt_stride, int nh, int nkv, int d, int block_size, long long num_blocks, float scale, int window,
             int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, int* err,
@@ -632,10 +529,7 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
     return (int)cudaErrorInvalidValue;
   if ((q_stride & 1) || (out_stride & 1) || ((((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15)) return (int)cudaErrorInvalidValue;
   if ((unsigned)B > 65535u || (unsigned)nkv > 65535u) return (int)cudaErrorInvalidValue;
-  const bool rope = rs.qkv_part != nullptr;
-  if (rope && (rs.nsplit < 1 || (rs.part_stride & 1) || !rs.positions || !rs.inv_freq || (((uintptr_t)rs.qkv_part) & 7)))
-    return (int)cudaErrorInvalidValue;
-  if (!rope && !q) return (int)cudaErrorInvalidValue;
+  if (!q) return (int)cudaErrorInvalidValue;
   CUtensorMap mk, mv;
   int rc = cache_map(&mk, kcache, rows, d);
   if (rc) return rc;
@@ -651,10 +545,6 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.total_rows = (int)rows;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.qkv_part = rs.qkv_part; p.part_stride = rs.part_stride; p.nsplit = rs.nsplit;
-  p.positions = rs.positions; p.inv_freq = rs.inv_freq; p.slots = rs.slots;
-  p.kcache = (bf16*)const_cast<void*>(kcache); p.vcache = (bf16*)const_cast<void*>(vcache);
-  p.num_slots = num_blocks * block_size;
   // more CTAs than fit at four stages: two stages, so that they run in fewer waves
   const long long ctas = (long long)p.grid_splits * B * nkv;
   static int sms = 0;
@@ -665,12 +555,8 @@ int run_dec(const void* q, const RopeSource& rs, void* out, const void* kcache, 
   }
   const bool small = ctas <= 3ll * sms;
   const bool cl = cluster != 0 && p.grid_splits <= 16;
-  if (rope) {
-    if (d == 64) return small ? launch_dec<64, 4, true>(mk, mv, p, B, cl, st) : launch_dec<64, 2, true>(mk, mv, p, B, cl, st);
-    return launch_dec<128, 2, true>(mk, mv, p, B, cl, st);
-  }
-  if (d == 64) return small ? launch_dec<64, 4, false>(mk, mv, p, B, cl, st) : launch_dec<64, 2, false>(mk, mv, p, B, cl, st);
-  return launch_dec<128, 2, false>(mk, mv, p, B, cl, st);
+  if (d == 64) return small ? launch_dec<64, 4>(mk, mv, p, B, cl, st) : launch_dec<64, 2>(mk, mv, p, B, cl, st);
+  return launch_dec<128, 2>(mk, mv, p, B, cl, st);
 }
 
 }  // namespace
@@ -689,29 +575,7 @@ KVF_API int kvf_paged_attention_decode_tma_bf16(const void* q, void* out, const 
                                                 int block_size, long long num_blocks, float scale, int window,
                                                 int split_size, int max_splits, int grid_splits, float* part_acc,
                                                 float* part_ml, int* tickets, int* err, int flags, cudaStream_t st) {
-  return run_dec(q, RopeSource(), out, kcache, vcache, block_tables, qsl, ctx_lens, B, q_stride, out_stride, bt_stride, nh,
+  return run_dec(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, q_stride, out_stride, bt_stride, nh,
                  nkv, d, block_size, num_blocks, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml,
                  tickets, err, flags, st);
-}
-
-// The same with the rotation and the cache write of the new token folded in.  qkv_part: float
-// [nsplit][tokens][(nh + 2 nkv) * d], slices part_stride floats apart, the projections of the
-// step's tokens (one per sequence, token qsl[b]) before rotation; the kernel sums the slices in
-// slice order, turns q and k by positions[token] * inv_freq[j] (pairs j, j + d/2), uses them,
-// and writes k and v to slot slots[token] of the cache (< 0: nowhere).
-KVF_API int kvf_paged_attention_decode_rope_tma_bf16(const float* qkv_part, int nsplit, long long part_stride,
-                                                     const int* positions, const float* inv_freq, const int* slots,
-                                                     void* out, void* kcache, void* vcache, const int* block_tables,
-                                                     const int* qsl, const int* ctx_lens, int B, int out_stride,
-                                                     int bt_stride, int nh, int nkv, int d, int block_size,
-                                                     long long num_blocks, float scale, int window, int split_size,
-                                                     int max_splits, int grid_splits, float* part_acc, float* part_ml,
-                                                     int* tickets, int* err, int cluster, cudaStream_t st) {
-  RopeSource rs;
-  rs.qkv_part = qkv_part; rs.part_stride = part_stride; rs.nsplit = nsplit;
-  rs.positions = positions; rs.inv_freq = inv_freq; rs.slots = slots;
-  if (!qkv_part) return (int)cudaErrorInvalidValue;
-  return run_dec(nullptr, rs, out, kcache, vcache, block_tables, qsl, ctx_lens, B, 0, out_stride, bt_stride, nh, nkv, d,
-                 block_size, num_blocks, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml, tickets,
-                 err, cluster, st);
 }

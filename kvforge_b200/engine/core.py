@@ -9,7 +9,6 @@ The order of construction follows umarhassan-cloud/kvforge's ``InferenceEngine._
 
 from __future__ import annotations
 
-import os
 from pathlib import Path
 
 import torch
@@ -84,7 +83,7 @@ class EngineCore:
         self.pool = KVPool(self.model, self.num_blocks, cache.block_size, max_num_seqs, self.dtype, self.device)
         self.runner = ModelRunner(
             self.model, self.rt, self.block_manager, self.state_slots, self.max_model_len, cuda_graphs=cuda_graphs,
-            pdl=(self.dtype == torch.bfloat16 and os.environ.get("KVFORGE_PDL", "1") != "0") if pdl is None else pdl,
+            pdl=(self.dtype == torch.bfloat16) if pdl is None else pdl,
         )  # fmt: skip
         self.runner.attach_pool(self.pool)
 

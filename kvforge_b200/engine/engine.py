@@ -77,7 +77,7 @@ class InferenceEngine:
             max_num_seqs=sc.max_num_seqs,
             max_num_batched_tokens=sc.max_num_batched_tokens,
             max_model_len=sc.max_model_len,
-            cuda_graphs=config.cuda_graphs and config.dtype == torch.bfloat16,
+            cuda_graphs=config.cuda_graphs,
         )
         self.block_manager = self.core.block_manager
         self.kv_cache = self.core.pool

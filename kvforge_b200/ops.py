@@ -29,7 +29,6 @@ _SIGNATURES = {
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
     "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppip",
-    "kvf_paged_attention_decode_rope_tma_bf16": "pilppp" "pppppp" "iiiiiii" "l" "f" "iiii" "ppppip",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
@@ -537,85 +536,6 @@ def paged_attention(
         ),
         name,
         2 if scratch is not None else 1,
-    )  # fmt: skip
-
-
-def decode_rope_attention_supported(dtype: torch.dtype, nh: int, nkv: int, d: int, block_size: int, num_blocks: int, rot: int) -> bool:
-    """Whether ``paged_attention_decode_rope`` takes this shape: what the TMA decode kernel takes,
-    with every dim of a head turning."""
-    return tma_decode_supported(dtype, nh, nkv, d, block_size, num_blocks) and rot == d
-
-
-def paged_attention_decode_rope(
-    qkv: Partials,
-    positions: torch.Tensor,
-    inv_freq: torch.Tensor,
-    slots: torch.Tensor,
-    out: torch.Tensor,
-    kcache: torch.Tensor,
-    vcache: torch.Tensor,
-    block_tables: torch.Tensor,
-    qsl: torch.Tensor,
-    ctx_lens: torch.Tensor,
-    num_seqs: int,
-    nh: int,
-    nkv: int,
-    d: int,
-    scale: float,
-    scratch: tuple[torch.Tensor, ...],
-    max_context: int,
-    window: int = 0,
-    split_size: int = 256,
-    err: torch.Tensor | None = None,
-    cluster: bool = True,
-) -> None:
-    """A decode step's rotation, cache write and attention in one kernel (bfloat16 caches).
-
-    ``qkv``: the ``Partials`` ``[S, N, (nh+2nkv)*d]`` of the projection of the step's ``N =
-    num_seqs`` tokens, one per sequence in order.  Their queries and keys turn by
-    ``positions * inv_freq`` (``inv_freq`` float ``[d/2]``), key and value go to ``slots`` of
-    the cache, and ``out [N, nh*d]`` receives the attention over the whole context, the new
-    token included.  ``scratch`` as for the decode form of ``paged_attention``, tickets included.
-    """
-    width = (nh + 2 * nkv) * d
-    _need(qkv.t, torch.float32, "partials", contiguous=False)
-    if qkv.t.dim() != 3 or qkv.t.shape[1] != num_seqs or qkv.t.shape[2] != width or qkv.t.stride(1) != width or qkv.t.stride(2) != 1:
-        raise ValueError("paged_attention_decode_rope: partials must be [S, num_seqs, width] with dense rows")
-    _need(out, torch.bfloat16, "out")
-    _need(kcache, torch.bfloat16, "kcache")
-    _need(vcache, torch.bfloat16, "vcache")
-    _need(inv_freq, torch.float32, "inv_freq")
-    for t, what in ((positions, "positions"), (slots, "slots"), (block_tables, "block_tables"), (qsl, "query_start_loc"), (ctx_lens, "context_lens")):
-        _need(t, torch.int32, what)
-    if kcache.dim() != 4 or kcache.shape[1] != nkv or kcache.shape[3] != d or kcache.shape != vcache.shape:
-        raise ValueError("paged_attention_decode_rope: cache shape must be [num_blocks, nkv, block_size, d]")
-    block_size = kcache.shape[2]
-    if not decode_rope_attention_supported(out.dtype, nh, nkv, d, block_size, kcache.shape[0], 2 * inv_freq.numel()):
-        raise ValueError("paged_attention_decode_rope does not take this shape")
-    if len(scratch) != 3:
-        raise ValueError("paged_attention_decode_rope: scratch is (sums, maxima and sums, tickets)")
-    pa, pm, tickets = scratch
-    _need(pa, torch.float32, "scratch acc")
-    _need(pm, torch.float32, "scratch ml")
-    _need(tickets, torch.int32, "scratch tickets")
-    if split_size <= 0 or split_size % 64:
-        raise ValueError("split_size must be a positive multiple of 64")
-    max_splits = pa.shape[2]
-    if pa.shape[0] < num_seqs or pa.shape[1] != nh or pa.shape[3] != d or tickets.numel() < num_seqs * nkv:
-        raise ValueError("paged_attention_decode_rope: scratch shape does not fit")
-    if -(-max_context // split_size) > max_splits:
-        raise ValueError("paged_attention_decode_rope: scratch is too small for the longest context")
-    grid_splits = max(1, -(-max_context // split_size))
-    bt_stride = block_tables.shape[-1] if block_tables.dim() == 2 else block_tables.numel() // max(1, num_seqs)
-    name = "kvf_paged_attention_decode_rope_tma_bf16"
-    _check(
-        _fn(name)(
-            _ptr(qkv.t), qkv.nsplit, qkv.split_stride, _ptr(positions), _ptr(inv_freq), _ptr(slots),
-            _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
-            num_seqs, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]), float(scale),
-            int(window), split_size, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(cluster), _stream(),
-        ),
-        name,
     )  # fmt: skip
 
 

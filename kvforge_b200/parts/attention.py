@@ -10,7 +10,6 @@ The three input projections are one product here (their weights are stacked at l
 from __future__ import annotations
 
 import math
-import os
 
 import torch
 
@@ -77,10 +76,6 @@ class PagedAttention(Mixer):
         self.position = None  # shared instance, set by the model before bind
         self.q_dim = self.nh * self.d
         self.qkv_dim = (self.nh + 2 * self.nkv) * self.d
-        # decode steps: rotation and cache write inside the attention kernel.  Measured inside the
-        # decode step at 1 and 8 sequences it gains nothing over the separate rotation kernel (which
-        # runs under the attention kernel's early copies), so it is off unless KVFORGE_FUSE_ROPE=1.
-        self.fuse_decode = os.environ.get("KVFORGE_FUSE_ROPE", "0") == "1"
 
     @classmethod
     def weight_decls(cls, params):
@@ -145,23 +140,6 @@ class PagedAttention(Mixer):
         if cache.writable:
             slots = ctx.slot_mappings[cache.group]
             splits = ops.skinny_splits(self.qkv_dim, self.hidden) if skinny else 1
-            fused = (
-                skinny and ctx.all_single_query and n == ctx.num_seqs and self.fuse_decode
-                and ops.decode_rope_attention_supported(x.dtype, self.nh, self.nkv, self.d, ctx.block_size, cache.k.shape[0], 2 * self.inv_freq.numel())
-            )  # fmt: skip
-            if fused:
-                # decode: the attention kernel sums the slices, turns q and k and writes the cache itself
-                part = ops.Partials(rt.buf("attn.qkv_part", splits * n, self.qkv_dim, torch.float32, cap=_PART_ROWS).view(splits, n, self.qkv_dim))
-                ops.gemm_skinny(x, self.w_qkv, part)
-                out = rt.buf("attn.out", n, self.q_dim)
-                scratch, bound, split = self._scratch(ctx)
-                ops.paged_attention_decode_rope(
-                    part, ctx.positions, self.inv_freq, slots, out, cache.k, cache.v, ctx.block_tables[cache.group],
-                    ctx.query_start_loc, ctx.context_lens, ctx.num_seqs, self.nh, self.nkv, self.d, self.scale,
-                    scratch, bound, window=int(self.window or 0), split_size=split, err=rt.err,
-                    cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
-                )  # fmt: skip
-                return _project(rt, "attn.proj", out, self.w_o)
             if splits > 1:
                 # decode: slices of K in parallel; the rotation kernel sums them
                 part = ops.Partials(rt.buf("attn.qkv_part", splits * n, self.qkv_dim, torch.float32, cap=_PART_ROWS).view(splits, n, self.qkv_dim))

@@ -73,6 +73,7 @@ def test_bfloat16_generation_with_and_without_graphs(folders, name):
     b = engine_for(folders[name], name, "bfloat16", cuda_graphs=False).generate(prompts, greedy(12))
     assert [o.output_token_ids for o in a] == [o.output_token_ids for o in b]
     plain = PlainLlama(folders[name])
+    checked = 0
     for p, o in zip(prompts, a):
         ids = list(p)
         for tok in o.output_token_ids:
@@ -80,7 +81,58 @@ def test_bfloat16_generation_with_and_without_graphs(folders, name):
             top = logits.topk(2).values
             if float(top[0] - top[1]) > 0.08 * float(logits.abs().max()):
                 assert tok == int(logits.argmax())
+                checked += 1
             ids.append(tok)
+    assert checked >= 24, f"only {checked} of 48 tokens had a margin wide enough to compare"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_dozens_of_decoding_requests_beside_short_prompts_that_arrive_late(folders, dtype):
+    """About forty requests decode while short prompts keep arriving, with room for 64 sequences:
+    such a step holds 33 to 63 single tokens and a portion of a few tokens, at most 64 tokens in
+    all, so as a graph it is padded to 64 tokens in 64 sequences, the very numbers of the graph of
+    64 decoding requests.  The two are different graphs; taking one for the other would compute
+    only the last query of the portion.  Tokens are the plain model's: all of them in 32-bit, in
+    bfloat16 wherever its top-2 margin is larger than bfloat16 rounding."""
+    name = "tiny-d"
+    rng = random.Random(3)
+    prompts = prompts_for(name, [rng.randint(5, 20) for _ in range(58)], seed=70)
+    lengths = [rng.randint(10, 22) for _ in prompts]
+    plain = PlainLlama(folders[name])
+    engine = engine_for(folders[name], name, dtype, num_blocks=400, max_num_seqs=64, max_num_batched_tokens=256, max_model_len=64)
+    ids = [engine.add_request(p, greedy(n)) for p, n in zip(prompts[:40], lengths[:40])]
+    late = list(zip(prompts[40:], lengths[40:]))
+    done = {}
+    shapes = set()
+    while engine.has_unfinished_requests():
+        if late and engine.runner.num_forward_passes >= 2:
+            p, n = late.pop(0)  # one more prompt with every step
+            ids.append(engine.add_request(p, greedy(n)))
+        for out in engine.step():
+            if out.finished:
+                done[out.request_id] = out
+    shapes = set(engine.runner._graphs)
+    assert any(k[0] == 64 and k[1] == 64 and k[4] for k in shapes) or any(k[0] == 64 and k[1] == 64 and not k[4] for k in shapes)
+    assert any(not k[4] and k[3] for k in shapes), "no mixed step was replayed as a graph"
+    engine.core.rt.check_error_flag()
+    checked = 0
+    for rid, p, n in zip(ids, prompts, lengths):
+        got = done[rid].output_token_ids
+        assert len(got) == n
+        if dtype == "float32":
+            assert got == plain.greedy(p, n), rid
+            checked += n
+            continue
+        seq = list(p)
+        for tok in got:
+            logits = plain.logits(seq)[-1]
+            top = logits.topk(2).values
+            if float(top[0] - top[1]) > 0.08 * float(logits.abs().max()):
+                assert tok == int(logits.argmax()), rid
+                checked += 1
+            seq.append(tok)
+    assert checked > 300
+    assert engine.block_manager.num_free_blocks == engine.block_manager.num_blocks
 
 
 def test_requests_that_join_late_and_leave_early(folders):

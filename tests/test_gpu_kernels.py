@@ -632,51 +632,6 @@ def test_tma_decode_reads_zeros_for_pages_that_were_given_back(ops):
     assert torch.allclose(out[0].float().cpu(), ref, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("nh,nkv,d,bs", [(8, 2, 64, 16), (32, 8, 64, 16), (3, 1, 64, 32), (24, 8, 128, 32), (14, 2, 128, 16)])
-@pytest.mark.parametrize("nsplit,split,window", [(1, 64, 0), (5, 256, 0), (3, 128, 40)])
-def test_decode_attention_with_rotation_inside_equals_rotation_then_attention(ops, nh, nkv, d, bs, nsplit, split, window):
-    """One kernel that sums the slices, turns q and k, writes the cache and attends, against the
-    rotation kernel followed by the decode attention kernel."""
-    ctx = [700, 1, 256, 257, 33, 64, 65, 16, 17, 300]
-    nseq = len(ctx)
-    g = torch.Generator().manual_seed(nh * d + nsplit)
-    kv = [(torch.randn(c, nkv, d, generator=g).bfloat16(), torch.randn(c, nkv, d, generator=g).bfloat16()) for c in ctx]
-    kc, vc, tables = paged(kv, nkv, d, bs, torch.bfloat16, seed=3, junk=(float("nan"), float("nan")))
-    width = (nh + 2 * nkv) * d
-    parts = torch.randn(nsplit, nseq, width, generator=g) * 0.6
-    positions = torch.tensor([c - 1 for c in ctx], dtype=torch.int32)
-    slots = torch.tensor([int(tables[b, (c - 1) // bs]) * bs + (c - 1) % bs for b, c in enumerate(ctx)], dtype=torch.int32)
-    inv_freq = dev(plain_inv_freq(d, 10000.0))
-    qsl = dev(torch.arange(nseq + 1, dtype=torch.int32))
-    cl = dev(torch.tensor(ctx, dtype=torch.int32))
-    sa, sm = ops.attention_scratch_shapes(nseq, nh, d, max(ctx), split)
-    scale = 1.0 / math.sqrt(d)
-
-    def scratch():
-        return (torch.empty(sa, device="cuda"), torch.empty(sm, device="cuda"), torch.zeros(nseq * nkv, dtype=torch.int32, device="cuda"))
-
-    # rotation kernel, then attention
-    k1, v1 = dev(kc), dev(vc)
-    q = torch.empty(nseq, nh * d, device="cuda", dtype=torch.bfloat16)
-    ops.rope_cache_write(ops.Partials(dev(parts)), dev(positions), inv_freq, dev(slots), k1, v1, nh, nkv, d, bs, err_flag(), q_out=q)
-    want = torch.empty(nseq, nh * d, device="cuda", dtype=torch.bfloat16)
-    ops.paged_attention(q, want, k1, v1, dev(tables), qsl, cl, nseq, 1, nh, nkv, d, scale, window=window, scratch=scratch(), max_context=max(ctx), split_size=split, kernel="tma", err=err_flag())
-    # one kernel
-    k2, v2 = dev(kc), dev(vc)
-    got = torch.full((nseq, nh * d), float("nan"), device="cuda", dtype=torch.bfloat16)
-    err_flag().zero_()
-    ops.paged_attention_decode_rope(
-        ops.Partials(dev(parts)), dev(positions), inv_freq, dev(slots), got, k2, v2, dev(tables), qsl, cl, nseq, nh, nkv, d,
-        scale, scratch(), max(ctx), window=window, split_size=split, err=err_flag(),
-    )  # fmt: skip
-    assert int(err_flag().sum()) == 0
-    assert not torch.isnan(got.float()).any()
-    assert torch.allclose(got.float(), want.float(), rtol=1e-2, atol=1e-2)
-    # the cache holds the same new keys and values, and nothing else moved
-    for a, b in ((k1, k2), (v1, v2)):
-        assert torch.equal(torch.nan_to_num(a.float(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
-
-
 @pytest.mark.parametrize("decode_form", [False, True, "fused"])
 def test_mma_attention_finds_a_far_key_and_respects_the_window(ops, decode_form):
     for far in (0, 15, 16, 63, 64, 255, 256, 511, 640):

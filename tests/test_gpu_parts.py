@@ -225,20 +225,25 @@ def test_layers_with_a_window_have_pages_of_their_own(tmp_path, variant_architec
             assert most_saved >= 5, cut  # 150 tokens are 10 pages of 16; a window of 21 needs 3
 
 
-def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
-    """A mixer that keeps a decaying sum per request (no keys, no pages), written here with
-    torch operations, plugged in through the public registries only."""
-    from kvforge_b200 import ModelConfig
-    from kvforge_b200.config.registry import register_architecture, unregister_architecture
-    from kvforge_b200.models.llama import llama_spec
-    from kvforge_b200.parts.base import CacheNeed, Mixer, PartSpec, WeightDecl, register_mixer, MIXERS
-    from kvforge_b200.replay import TraceRunner
-    from test_gpu_replay import check
+DECAY = 0.9
+TOY_STATE = 24
 
-    decay = 0.9
+
+def toy_state_architecture():
+    """Registers (once) a mixer that keeps a decaying sum per request (no keys, no pages), written
+    here with torch operations, and returns the builder of a model whose odd layers use it while
+    its even layers keep attention: state slots and pages in one model.  Everything goes through
+    the public registries; no file of the framework knows of it.
+
+    The mixer works on the device alone, with shapes that depend only on the step's capacity, so
+    that a step can be captured as a CUDA graph: which sequence a token belongs to comes from
+    ``query_start_loc``; a token outside every sequence (padding of a captured shape) and a
+    sequence without queries or without a slot (``state_slots[b] < 0``) touch no state."""
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.base import MIXERS, CacheNeed, Mixer, PartSpec, WeightDecl, register_mixer
 
     class DecayingSum(Mixer):
-        """state_t = decay * state_{t-1} + x_t W_in^T ;  y_t = state_t W_out^T"""
+        """state_t = DECAY * state_{t-1} + x_t W_in^T ;  y_t = state_t W_out^T"""
 
         def __init__(self, params, prefix=""):
             super().__init__(params, prefix)
@@ -260,17 +265,26 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             self.w_in, self.w_out = weights["in_proj.weight"].float(), weights["out_proj.weight"].float()
 
         def forward(self, ctx, x, cache):
+            n, nb = x.shape[0], ctx.num_seqs
             u = x.float() @ self.w_in.t()
-            out = torch.empty_like(u)
-            for b in range(ctx.num_seqs):
-                lo, hi = int(ctx.h_query_start_loc[b]), int(ctx.h_query_start_loc[b + 1])
-                slot = int(ctx.h_state_slots[b])
-                state = cache.state[slot].clone()
-                for t in range(lo, hi):
-                    state = decay * state + u[t]
-                    out[t] = state
-                cache.state[slot] = state
-            return (out @ self.w_out.t()).to(x.dtype)
+            qsl = ctx.query_start_loc.long()
+            tok = torch.arange(n, device=x.device)
+            seq = torch.searchsorted(qsl[1:].contiguous(), tok, right=True).clamp(max=nb - 1)  # how many sequences end at or before the token
+            slot = ctx.state_slots.long()[seq]
+            live = (tok < qsl[nb]) & (slot >= 0)
+            slot = slot.clamp(min=0)
+            # y_t = DECAY^(t - first + 1) * state + sum over the sequence's tokens s <= t of DECAY^(t - s) * u_s
+            lag = tok[:, None] - tok[None, :]
+            same = (seq[:, None] == seq[None, :]) & (lag >= 0) & live[:, None] & live[None, :]
+            mix = torch.where(same, DECAY ** lag.clamp(min=0).float(), torch.zeros((), device=x.device))
+            before = cache.state[slot]
+            y = mix @ u + (DECAY ** (tok - qsl[seq] + 1).clamp(min=0).float())[:, None] * before
+            y = torch.where(live[:, None], y, torch.zeros((), device=x.device))
+            # the state after the step is y at a sequence's last token; slots of other requests stay as they are
+            last = live & (tok == qsl[seq + 1] - 1)
+            pick = (last[None, :] & (slot[None, :] == torch.arange(cache.state.shape[0], device=x.device)[:, None])).float()
+            cache.state.copy_(torch.where(pick.sum(1, keepdim=True) > 0, pick @ y, cache.state))
+            return (y @ self.w_out.t()).to(x.dtype)
 
     if "decaying_sum" not in MIXERS:
         register_mixer("decaying_sum")(DecayingSum)
@@ -279,45 +293,116 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         spec = llama_spec(cfg)
         for i, ls in enumerate(spec.layers):
             if i % 2 == 1:  # odd layers keep a state, even layers keep keys: both kinds in one model
-                ls.block.params["mixer"] = PartSpec("decaying_sum", {"hidden_size": cfg.hidden_size, "state_size": 24})
+                ls.block.params["mixer"] = PartSpec("decaying_sum", {"hidden_size": cfg.hidden_size, "state_size": TOY_STATE})
                 ls.block.params["mixer_name"] = "toy"
         return spec
 
+    return build
+
+
+class ToyStatePlain(PlainLlama):
+    """The plain model with the decaying sum in its odd layers, token by token."""
+
+    def attention(self, layer, x, positions, kv=None):
+        if layer % 2 == 0:
+            return super().attention(layer, x, positions, kv)
+        u = x.float() @ self.w[f"layers.{layer}.toy.in_proj.weight"].float().t()
+        state = torch.zeros(TOY_STATE)
+        rows = []
+        for t in range(x.shape[0]):
+            state = DECAY * state + u[t]
+            rows.append(state)
+        return (torch.stack(rows) @ self.w[f"layers.{layer}.toy.out_proj.weight"].float().t()).to(x.dtype), None
+
+
+def toy_state_folder(tmp_path, build, store_dtype):
+    from kvforge_b200.parts.model import DecoderModel
+    from kvforge_b200.weights.random_init import write_model_dir
+
+    cfg = TINY["tiny-b"]["cfg"]
+    cj = cfg.to_hf_dict()
+    cj["architectures"] = ["ToyStateForCausalLM"]
+    model = DecoderModel(build(cfg))
+    assert model.state_shapes == [None, (TOY_STATE,), None] and len(model.groups) == 1 and len(model.groups[0].calls) == 2
+    return write_model_dir(tmp_path / "toy", cj, model.expected_weights(), seed=5, store_dtype=store_dtype, init_std=0.1, norm_std=0.1)
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from kvforge_b200 import ModelConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.replay import TraceRunner
+    from test_gpu_replay import check
+
+    build = toy_state_architecture()
     register_architecture("ToyStateForCausalLM", ModelConfig.from_hf_dict, build)
     try:
-        from kvforge_b200.parts.model import DecoderModel
-        from kvforge_b200.weights.random_init import write_model_dir
-
-        cfg = TINY["tiny-b"]["cfg"]
-        cj = cfg.to_hf_dict()
-        cj["architectures"] = ["ToyStateForCausalLM"]
-        model = DecoderModel(build(cfg))
-        assert model.state_shapes == [None, (24,), None] and len(model.groups) == 1 and len(model.groups[0].calls) == 2
-        folder = write_model_dir(tmp_path / "toy", cj, model.expected_weights(), seed=5, store_dtype=torch.float32, init_std=0.1, norm_std=0.1)
-
-        class ToyPlain(PlainLlama):
-            def attention(self, layer, x, positions, kv=None):
-                if layer % 2 == 0:
-                    return super().attention(layer, x, positions, kv)
-                u = x @ self.w[f"layers.{layer}.toy.in_proj.weight"].t()
-                state = torch.zeros(24)
-                rows = []
-                for t in range(x.shape[0]):
-                    state = decay * state + u[t]
-                    rows.append(state)
-                return torch.stack(rows) @ self.w[f"layers.{layer}.toy.out_proj.weight"].t(), None
-
-        plain = ToyPlain(folder)
+        folder = toy_state_folder(tmp_path, build, torch.float32)
+        plain = ToyStatePlain(folder)
         reqs = {f"r{i}": random_tokens(320, n, seed=i) for i, n in enumerate([33, 5, 48, 20, 27])}
         ref = {rid: plain.logits(t) for rid, t in reqs.items()}
-        for steps in (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: len(t) - 6 for r, t in reqs.items()}, max_live=3, seed=2)):
-            runner = TraceRunner(str(folder), "float32", traces.tokens_needed(steps), max_live=3)
-            outs = []
-            for s in steps:
-                o = runner.step(s)
-                outs.append(None if o is None else o.clone())
-            check(steps, outs, ref, 2e-5)  # slots are used again: a new request must start from zero
-            runner.core.state_slots.check_invariants()
+        cuts = (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: len(t) - 6 for r, t in reqs.items()}, max_live=3, seed=2))
+        for graphs in (False, True):
+            for steps in cuts:
+                if graphs:
+                    steps = traces.last_only(steps)
+                runner = TraceRunner(str(folder), "float32", traces.tokens_needed(steps), max_live=3, block_size=8, cuda_graphs=graphs)
+                outs = []
+                for s in steps:
+                    o = runner.step(s)
+                    outs.append(None if o is None else o.clone())
+                check(steps, outs, ref, 2e-5)  # slots are used again: a new request must start from zero
+                runner.core.state_slots.check_invariants()
+                if graphs and steps is not cuts[0]:
+                    assert runner.core.runner.num_graph_kernels > 0
+    finally:
+        unregister_architecture("ToyStateForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_toy_mixers_state_survives_graphs_chunked_prefill_and_preemption_in_the_engine(tmp_path, dtype):
+    """The same toy model through ``InferenceEngine`` with CUDA graphs: prompts cut into portions
+    by a small token budget, four state slots for six requests, and so few pages that running
+    requests are preempted and recomputed (their slot is given back and a fresh one starts from
+    zero).  A step on which a graph is captured must advance the state once, not twice.  Tokens
+    are the plain model's: all of them in 32-bit, in bfloat16 wherever its top-2 margin is
+    larger than bfloat16 rounding."""
+    from kvforge_b200 import CacheConfig, EngineConfig, InferenceEngine, ModelConfig, SamplingParams, SchedulerConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+
+    build = toy_state_architecture()
+    register_architecture("ToyStateForCausalLM", ModelConfig.from_hf_dict, build)
+    try:
+        folder = toy_state_folder(tmp_path, build, torch.bfloat16)
+        plain = ToyStatePlain(folder)
+        prompts = [random_tokens(320, n, seed=60 + i) for i, n in enumerate([33, 21, 40, 18, 27, 36])]
+        cfg = EngineConfig(
+            cache=CacheConfig(block_size=8, num_blocks=18),
+            scheduler=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=24, max_model_len=128),
+            dtype=dtype, cuda_graphs=True,
+        )  # fmt: skip
+        engine = InferenceEngine(cfg, model=folder)
+        outs = engine.generate(prompts, SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True))
+        assert engine.scheduler.num_preemptions > 0
+        assert engine.runner.num_graph_kernels > 0 and any(key[4] for key in engine.runner._graphs) and any(not key[4] for key in engine.runner._graphs)
+        engine.core.rt.check_error_flag()
+        engine.core.state_slots.check_invariants()
+        assert engine.block_manager.num_free_blocks == 18
+        checked = 0
+        for p, o in zip(prompts, outs):
+            assert o.finished and len(o.output_token_ids) == 20
+            if dtype == "float32":
+                assert o.output_token_ids == plain.greedy(p, 20)
+                checked += 20
+                continue
+            ids = list(p)
+            for tok in o.output_token_ids:
+                logits = plain.logits(ids)[-1]
+                top = logits.topk(2).values
+                if float(top[0] - top[1]) > 0.08 * float(logits.abs().max()):
+                    assert tok == int(logits.argmax())
+                    checked += 1
+                ids.append(tok)  # the plain model follows the engine's tokens, so a close call costs one comparison
+        assert checked > 40
     finally:
         unregister_architecture("ToyStateForCausalLM")
 
