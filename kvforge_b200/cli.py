@@ -52,7 +52,15 @@ def main() -> int:
         for line in Path(args.prompt_file).read_text().splitlines():
             if line.strip():
                 prompts.append([int(t) for t in line.split(",") if t.strip()])
-    tokenizer = ByteTokenizer() if args.prompt else None
+    tokenizer = None
+    if args.prompt:  # text goes in as bytes, fitted to the vocabulary of the model that will run
+        if args.hf_model:
+            from .config.model_config import read_config_json
+
+            vocab = int(read_config_json(args.hf_model)["vocab_size"])
+        else:
+            vocab = PRESETS[args.preset].vocab_size
+        tokenizer = ByteTokenizer(vocab)
     prompts.extend(args.prompt)
     if not prompts:
         p.error("give --prompt-ids, --prompt-file or --prompt")

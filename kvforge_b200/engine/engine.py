@@ -6,7 +6,8 @@ Names and meanings follow umarhassan-cloud/kvforge's ``InferenceEngine``
 ``has_unfinished_requests``, ``generate`` (outputs in prompt order), ``step``, ``stats``.
 The model is given as a folder (``config.json`` + safetensors), or is made with random
 weights from ``config.model`` and ``config.seed`` as kvforge does when it is given none
-(engine.py:52-54).
+(engine.py:52-54).  ``tokenizer``: for string prompts, any object with ``encode(text)``,
+``decode(ids)`` and ``eos_token_id`` (``engine/tokenizer.py`` has one that needs no files).
 """
 
 from __future__ import annotations
@@ -28,10 +29,6 @@ from .metrics import MetricsCollector
 from .request import FinishReason, Request, RequestOutput
 from .scheduler import ScheduledRequest, Scheduler
 from .step import BatchItem
-from .tokenizer import Tokenizer
-
-
-PLACEHOLDER = -1  # stands in an output list for a token that is still on the device
 
 
 @dataclass
@@ -51,7 +48,7 @@ class InferenceEngine:
         self,
         config: EngineConfig | None = None,
         model: str | Path | None = None,
-        tokenizer: Tokenizer | None = None,
+        tokenizer: Any = None,
         init_std: float = 0.02,
     ) -> None:
         self.config = config = config or EngineConfig()
@@ -94,6 +91,18 @@ class InferenceEngine:
         self.vocab_size = spec.vocab_size
 
     # ------------------------------------------------------------------ API
+    def _token_ids(self, prompt: str | Sequence[int]) -> list[int]:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("a prompt given as text needs a tokenizer; give token ids or pass tokenizer=")
+            ids = list(self.tokenizer.encode(prompt))
+        else:
+            ids = [int(t) for t in prompt]
+        bad = next((t for t in ids if not 0 <= t < self.vocab_size), None)
+        if bad is not None:
+            raise ValueError(f"token id {bad} is outside the model's vocabulary of {self.vocab_size}")
+        return ids
+
     def add_request(
         self,
         prompt: str | Sequence[int],
@@ -101,56 +110,46 @@ class InferenceEngine:
         request_id: str | None = None,
         arrival_time: float | None = None,
     ) -> str:
-        """engine.py:106-134."""
-        if isinstance(prompt, str):
-            if self.tokenizer is None:
-                raise ValueError("string prompts need a tokenizer")
-            token_ids = self.tokenizer.encode(prompt)
-        else:
-            token_ids = [int(t) for t in prompt]
-        if any(t < 0 or t >= self.vocab_size for t in token_ids):
-            raise ValueError("prompt contains out-of-vocabulary token ids")
-        request_id = request_id or f"req-{next(self._ids)}"
-        eos = self.tokenizer.eos_token_id if self.tokenizer else self.core.spec.eos_token_id
-        params = sampling_params or SamplingParams()
-        req = Request(
-            request_id=request_id,
-            prompt_token_ids=token_ids,
-            sampling_params=params,
-            eos_token_id=eos,
-            stream_base=request_stream_base(self.config.seed, request_id, params),
+        """Queue a prompt (text or token ids) and return the request's name (engine.py:106-134).
+        The scheduler refuses what can never run (``RequestRejectedError``)."""
+        ids = self._token_ids(prompt)
+        name = request_id if request_id else f"req-{next(self._ids)}"
+        params = sampling_params if sampling_params is not None else SamplingParams()
+        eos = getattr(self.tokenizer, "eos_token_id", None) if self.tokenizer is not None else self.core.spec.eos_token_id
+        self.scheduler.add_request(
+            Request(name, ids, params, arrival_time, eos, stream_base=request_stream_base(self.config.seed, name, params))
         )
-        if arrival_time is not None:
-            req.arrival_time = arrival_time
-        self.scheduler.add_request(req)
-        return request_id
+        return name
 
     def abort_request(self, request_id: str) -> bool:
+        """End a live request now; whatever of it is still on the device is discarded."""
         req = self.scheduler.abort_request(request_id)
-        if req is not None:
-            self.metrics.record_finished(req)
-            if self._pending is not None:
-                self._pending.skip.add(request_id)
-            if req.output_token_ids and req.output_token_ids[-1] == PLACEHOLDER:
-                req.output_token_ids.pop()
-                req.token_times.pop()
-        return req is not None
+        if req is None:
+            return False
+        if self._pending is not None:
+            self._pending.skip.add(request_id)
+        req.drop_token_in_flight()
+        self.metrics.record_finished(req)
+        return True
 
     def generate(
         self,
         prompts: Sequence[str | Sequence[int]],
         sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
     ) -> list[RequestOutput]:
-        """Offline batch generation; outputs in prompt order (engine.py:145-159)."""
-        if sampling_params is None or isinstance(sampling_params, SamplingParams):
-            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
-        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
-        done: dict[str, RequestOutput] = {}
+        """Run all prompts to their end; one output per prompt, in the order given
+        (engine.py:145-159).  ``sampling_params``: one for all, or one per prompt."""
+        if isinstance(sampling_params, SamplingParams) or sampling_params is None:
+            per_prompt = [sampling_params] * len(prompts)
+        else:
+            per_prompt = list(sampling_params)
+            if len(per_prompt) != len(prompts):
+                raise ValueError(f"{len(per_prompt)} sampling parameter sets for {len(prompts)} prompts")
+        names = [self.add_request(prompt, sp) for prompt, sp in zip(prompts, per_prompt)]
+        final: dict[str, RequestOutput] = {}
         while self.has_unfinished_requests():
-            for out in self.step():
-                if out.finished:
-                    done[out.request_id] = out
-        return [done[i] for i in ids if i in done]
+            final.update((out.request_id, out) for out in self.step() if out.finished)
+        return [final[name] for name in names if name in final]
 
     # ------------------------------------------------------------------ step
     def has_unfinished_requests(self) -> bool:
@@ -193,7 +192,7 @@ class InferenceEngine:
         start = r.num_computed_tokens
         if s.num_new_tokens == 1 and start == r.num_tokens - 1:
             return False  # a single newest token can come from the device
-        return PLACEHOLDER in r.output_token_ids[max(0, start - r.num_prompt_tokens) :]
+        return r.in_flight_within(start)
 
     def _launch(self, group: list[ScheduledRequest], previous) -> "_Pending | None":
         """engine.py:196-228: a portion that reaches the end of the known tokens asks for the
@@ -206,12 +205,12 @@ class InferenceEngine:
             completes = start + s.num_new_tokens == r.num_tokens
             want = "last" if completes else "none"
             row = None
-            if previous is not None and s.num_new_tokens == 1 and r.output_token_ids and r.output_token_ids[-1] == PLACEHOLDER:
+            if previous is not None and s.num_new_tokens == 1 and r.has_token_in_flight:
                 row = previous.rows.get(r.request_id)
             if row is not None:
                 items.append(BatchItem(r.request_id, [0], start, want, feedback_row=row))
             else:
-                items.append(BatchItem(r.request_id, r.all_token_ids[start : start + s.num_new_tokens], start, want))
+                items.append(BatchItem(r.request_id, r.tokens(start, s.num_new_tokens), start, want))
             if completes:
                 sampled.append(r)
         logits = self.runner.step(items)
@@ -229,13 +228,11 @@ class InferenceEngine:
         host[n : n + 1].copy_(self.core.rt.err, non_blocking=True)
         event = self._events[self._flip]
         event.record()
-        now = time.perf_counter()
         max_len = self.config.scheduler.max_model_len
-        pending = _Pending(sampled, [r.num_output_tokens for r in sampled], host, event, {r.request_id: i for i, r in enumerate(sampled)})
+        pending = _Pending(sampled, [r.launch_token() for r in sampled], host, event, {r.request_id: i for i, r in enumerate(sampled)})
         for r in sampled:
-            r.append_token(PLACEHOLDER, now)
             # stops by count need no token value: decide them now, so the request is not run again
-            if r.num_output_tokens >= r.sampling_params.max_tokens or r.num_tokens >= max_len:
+            if r.at_count_limit(max_len):
                 self.scheduler.finish_request(r, FinishReason.LENGTH)
         return pending
 
@@ -250,16 +247,14 @@ class InferenceEngine:
         if values[n]:
             self.core.rt.check_error_flag()
         outputs: list[RequestOutput] = []
+        now = time.perf_counter()
         for r, idx, tok in zip(pending.sampled, pending.indices, values):
             if r.request_id in pending.skip or idx >= len(r.output_token_ids):
                 continue  # stopped or aborted meanwhile: this token is not part of its output
-            r.output_token_ids[idx] = tok
-            params = r.sampling_params
-            stop = not params.ignore_eos and (tok == r.eos_token_id or tok in params.stop_token_ids)  # request.py:99-110
-            if stop and not (r.is_finished and r.finish_reason == FinishReason.STOP):
-                # whatever was appended after it (a placeholder of the step in flight) is dropped
-                del r.output_token_ids[idx + 1 :]
-                del r.token_times[idx + 1 :]
+            r.land_token(idx, tok, now)
+            if r.stops_at(tok) and not (r.is_finished and r.finish_reason == FinishReason.STOP):
+                # whatever was launched after it (the token of the step in flight) is dropped
+                r.truncate_output(idx + 1)
                 if not r.is_finished:
                     self.scheduler.finish_request(r, FinishReason.STOP)
                 else:  # already closed by count in the same step: the stop token wins
@@ -269,6 +264,7 @@ class InferenceEngine:
             last = idx == len(r.output_token_ids) - 1
             finished = r.is_finished and last
             if finished:
+                r.finish_time = now  # the request ends for its caller when its last token is on the host
                 self.metrics.record_finished(r)
             elif not r.is_finished:
                 self.block_manager.mark_computed(r.request_id, r.num_computed_tokens)
@@ -287,20 +283,17 @@ class InferenceEngine:
 
     # ------------------------------------------------------------------ stats
     def stats(self) -> dict[str, Any]:
-        """engine.py:275-297."""
-        bm = self.block_manager.stats()
+        """Figures of the run so far under the headings kvforge reports (engine.py:275-297):
+        serving metrics, the cache's pages and bytes, the scheduler's queues, forward passes."""
+        pages = self.block_manager.stats()
+        per_page = self.kv_cache.bytes_per_block
+        cache = asdict(pages)
+        cache.update(bytes_total=self.kv_cache.memory_bytes, bytes_per_block=per_page, bytes_in_use=pages.num_used_blocks * per_page)
+        queues = {key: getattr(self.scheduler, key) for key in ("num_running", "num_waiting", "num_preemptions")}
         return {
             "metrics": self.metrics.summary(),
-            "kv_cache": {
-                **asdict(bm),
-                "bytes_total": self.kv_cache.memory_bytes,
-                "bytes_per_block": self.kv_cache.bytes_per_block,
-                "bytes_in_use": bm.num_used_blocks * self.kv_cache.bytes_per_block,
-            },
-            "scheduler": {
-                "num_running": self.scheduler.num_running,
-                "num_waiting": self.scheduler.num_waiting,
-                "num_preemptions": self.scheduler.num_preemptions,
-            },
+            "kv_cache": cache,
+            "scheduler": queues,
             "forward_passes": self.runner.num_forward_passes,
+            "graphs_captured": len(self.runner.graph_kernels),
         }

@@ -15,6 +15,7 @@ import torch
 
 from .. import ops
 from .base import CacheNeed, Mixer, PartSpec, WeightDecl, build_part, register_mixer
+from .projection import PART_ROWS, project
 
 
 # Decode attention merges its key ranges through a thread-block cluster's shared memory only with
@@ -22,33 +23,6 @@ from .base import CacheNeed, Mixer, PartSpec, WeightDecl, build_part, register_m
 # and loses at 8 and 64, where the ranges past the context (a captured graph's grid covers twice
 # the context at most) hold their places until their cluster is done.
 CLUSTER_MERGE_MAX_PAIRS = 16
-
-_PART_ROWS = ops.SKINNY_MAX_M * ops.SKINNY_MAX_SPLIT  # rows of the largest set of split-K slices
-
-
-def _project(rt, name: str, x: torch.Tensor, w: torch.Tensor):
-    """``x @ w^T`` back to the model width: the decode product (slices of K, summed by the norm
-    that follows) for a few tokens, the library product otherwise."""
-    n, width = x.shape[0], w.shape[0]
-    if ops.skinny_ok(x, w):
-        splits = ops.skinny_splits(width, w.shape[1])
-        if splits > 1:
-            part = ops.Partials(rt.buf(name + "_part", splits * n, width, torch.float32, cap=_PART_ROWS).view(splits, n, width))
-            ops.gemm_skinny(x, w, part)
-            return part
-        y = rt.buf(name, n, width)
-        ops.gemm_skinny(x, w, y)
-        return y
-    splits = ops.library_splits(n, width, w.shape[1]) if x.dtype == torch.bfloat16 else 1
-    if splits > 1:
-        # a few dozen tokens: the library product over slices of K, summed by the same norm
-        part = ops.Partials(rt.buf(name + "_part", splits * n, width, torch.float32, cap=_PART_ROWS).view(splits, n, width))
-        ops.linear_split_k(x, w, part)
-        return part
-    y = rt.buf(name, n, width)
-    ops.linear(x, w, y)
-    return y
-
 
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
@@ -142,7 +116,7 @@ class PagedAttention(Mixer):
             splits = ops.skinny_splits(self.qkv_dim, self.hidden) if skinny else 1
             if splits > 1:
                 # decode: slices of K in parallel; the rotation kernel sums them
-                part = ops.Partials(rt.buf("attn.qkv_part", splits * n, self.qkv_dim, torch.float32, cap=_PART_ROWS).view(splits, n, self.qkv_dim))
+                part = ops.Partials(rt.buf("attn.qkv_part", splits * n, self.qkv_dim, torch.float32, cap=PART_ROWS).view(splits, n, self.qkv_dim))
                 ops.gemm_skinny(x, self.w_qkv, part)
                 q = rt.buf("attn.q", n, self.q_dim)
                 ops.rope_cache_write(part, ctx.positions, self.inv_freq, slots, cache.k, cache.v, self.nh, self.nkv, self.d, ctx.block_size, rt.err, q_out=q)
@@ -163,7 +137,7 @@ class PagedAttention(Mixer):
             q_stride = self.q_dim
         out = rt.buf("attn.out", n, self.q_dim)
         self.attend(ctx, q, q_stride, out, cache)
-        return _project(rt, "attn.proj", out, self.w_o)
+        return project(rt, "attn.proj", out, self.w_o)
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256

@@ -7,8 +7,8 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .attention import _project
 from .base import FeedForward, WeightDecl, register_feed_forward
+from .projection import project
 
 
 @register_feed_forward("gated_mlp")
@@ -57,4 +57,4 @@ class GatedMLP(FeedForward):
             gu = rt.buf("mlp.gate_up", n, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gu)
             ops.silu_mul(gu, act, interleaved=self.interleaved)
-        return _project(rt, "mlp.out", act, self.w_down)
+        return project(rt, "mlp.out", act, self.w_down)

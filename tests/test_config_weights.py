@@ -134,3 +134,48 @@ def test_loader_storage_rules(tmp_path):
     assert "lm_head.weight" not in w  # tied: the folder has no separate head
     w32 = load_weights(d, model.expected_weights(), torch.float32, "cpu")
     assert torch.equal(w32["model.embed_tokens.weight"], w["model.embed_tokens.weight"].float())
+
+
+def test_a_checkpoint_in_shards_reads_like_one_file(tmp_path):
+    """The same tensors split over two files with an index (the layout of larger checkpoints),
+    and the same two files without an index: both load to what the single file gives."""
+    import json
+
+    d = make_model_dir(tmp_path, "tiny-b")
+    model = DecoderModel(get_architecture("LlamaForCausalLM").build_spec(TINY["tiny-b"]["cfg"]))
+    expected = model.expected_weights()
+    one = load_weights(d, expected, torch.float32, "cpu")
+    f = SafetensorsFile(d / "model.safetensors")
+    names = sorted(f.keys())
+    halves = (names[::2], names[1::2])
+    for with_index in (True, False):
+        sharded = tmp_path / f"sharded-{with_index}"
+        sharded.mkdir()
+        (sharded / "config.json").write_text((d / "config.json").read_text())
+        weight_map = {}
+        for i, part in enumerate(halves):
+            fname = f"model-{i + 1:05d}-of-00002.safetensors"
+            write_safetensors(sharded / fname, {n: f.tensor(n).clone() for n in part})
+            weight_map.update({n: fname for n in part})
+        if with_index:
+            (sharded / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+        got = load_weights(sharded, expected, torch.float32, "cpu")
+        assert sorted(got) == sorted(one) and all(torch.equal(got[n], one[n]) for n in one)
+    # a shard that is missing shows as its tensors missing, in the one error
+    (tmp_path / "sharded-False" / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(WeightsError) as e:
+        load_weights(tmp_path / "sharded-False", expected, torch.float32, "cpu")
+    assert sorted(e.value.missing) == sorted(n for n in halves[1] if not expected[n].optional)
+
+
+def test_bytes_as_tokens_fit_the_vocabulary():
+    from kvforge_b200.engine.tokenizer import BytesAsTokens
+
+    big = BytesAsTokens(320)
+    ids = big.encode("héllo")
+    assert ids[0] == 256 and ids[1:] == list("héllo".encode()) and big.eos_token_id == 257
+    assert big.decode(ids + [257]) == "héllo"
+    exact = BytesAsTokens(256)  # no room for the two marks
+    assert exact.encode("hi") == [104, 105] and exact.eos_token_id is None and exact.bos_token_id is None
+    small = BytesAsTokens(200)
+    assert all(0 <= t < 200 for t in small.encode("héllo ÿ"))

@@ -9,7 +9,7 @@ from pathlib import Path
 import pytest
 import torch
 
-from golden.make_golden import GOLDEN_SEED, GOLDEN_TOKENS, checksum
+from golden.make_golden import GOLDEN_TOKENS
 from kvforge_b200 import PRESETS
 from kvforge_b200.models.folder import write_random_model
 from plain_llama import (
@@ -24,19 +24,18 @@ from plain_llama import (
     rope_cos_sin,
 )
 
-GOLDEN = Path(__file__).parent / "golden" / "kvforge_reference_logits.safetensors"
+GOLDEN_DIR = Path(__file__).parent / "golden"
+GOLDEN = GOLDEN_DIR / "kvforge_reference_logits.safetensors"
 
 
 @pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
-def test_plain_matches_kvforge_model(tmp_path, name):
+def test_plain_matches_kvforge_model(name):
+    """The committed model folders (``tests/golden/tiny-a``, ``tiny-b``) through the plain
+    implementation against the logits kvforge's own model code gave for them."""
     gold = read_safetensors(GOLDEN)
-    write_random_model(tmp_path / name, PRESETS[name], seed=GOLDEN_SEED, store_dtype=torch.float32, init_std=0.1, norm_std=0.1)
-    raw = read_safetensors(tmp_path / name / "model.safetensors")
-    if not torch.equal(checksum(raw), gold[f"{name}.weights_checksum"]):
-        pytest.skip("this torch build draws other random weights than the golden file was made with")
     tokens = gold[f"{name}.tokens"].tolist()
     assert tokens == GOLDEN_TOKENS[name]
-    logits = PlainLlama(tmp_path / name).logits(tokens)
+    logits = PlainLlama(GOLDEN_DIR / name).logits(tokens)
     ref = gold[f"{name}.logits"]
     assert logits.shape == ref.shape
     assert float((logits - ref).abs().max()) < 2e-5 * max(1.0, float(ref.abs().max()))
@@ -62,6 +61,36 @@ def test_llama3_scaling_three_regimes_and_continuity():
         a = llama3_scaled_inv_freq(f * (1 + eps), factor, lo, hi, orig) / (f * (1 + eps))
         b = llama3_scaled_inv_freq(f * (1 - eps), factor, lo, hi, orig) / (f * (1 - eps))
         assert abs(float(a) - want) < 1e-3 and abs(float(b) - want) < 1e-3
+
+
+# llama3 scaling worked out by hand from its published definition, in plain double arithmetic:
+# f = theta^(-2j/d), wavelength lam = 2 pi / f; kept for lam < P/high, f/factor for lam > P/low,
+# else s = (P/lam - low)/(high - low) and (1 - s) f/factor + s f.  E.g. the 1B line for j = 16:
+# f = 500000^-0.5 = 1.414213562e-3, lam = 4442.88, P/lam = 1.843850, s = 0.2812833,
+# (0.7187167/32 + 0.2812833) f = 0.3037432 f = 4.295568e-4.
+LLAMA3_LITERALS = [
+    # (head_dim, theta, factor, low, high, original context): {pair index: scaled frequency}
+    ((64, 500000.0, 32.0, 1.0, 4.0, 8192), {0: 1.0, 7: 5.666962145e-02, 14: 3.211445995e-03, 15: 1.290547928e-03, 16: 4.295567966e-04, 17: 9.708287803e-05, 18: 1.946163818e-05, 31: 9.418306725e-08}),
+    ((128, 500000.0, 32.0, 1.0, 4.0, 8192), {28: 3.211445995e-03, 29: 2.118406997e-03, 31: 7.625412034e-04, 34: 9.708287803e-05, 35: 2.389053088e-05, 63: 7.672314972e-08}),
+    ((128, 500000.0, 8.0, 1.0, 4.0, 8192), {1: 8.146172339e-01, 29: 2.166570764e-03, 32: 5.248461610e-04, 34: 1.785078128e-04, 35: 9.556212354e-05, 63: 3.068925989e-07}),
+    ((32, 500000.0, 8.0, 1.0, 4.0, 64), {0: 1.0, 1: 4.403666027e-01, 2: 7.940300918e-02, 3: 1.067463754e-02, 15: 5.677088101e-07}),
+]
+
+
+@pytest.mark.parametrize("args,literals", LLAMA3_LITERALS)
+def test_llama3_scaling_literal_values(args, literals):
+    """The plain formula and the engine's (``kvforge_b200/parts/rope.py``) against values worked
+    out by hand for the rope parameters of the 1B, 3B and 8B shapes and of tiny-b."""
+    from kvforge_b200.parts.rope import llama3_scale, rotary_inv_freq
+
+    d, theta, factor, low, high, orig = args
+    plain = llama3_scaled_inv_freq(plain_inv_freq(d, theta), factor, low, high, orig)
+    engine = llama3_scale(rotary_inv_freq(d, theta), factor, low, high, orig)
+    for j, want in literals.items():
+        # 32-bit frequencies: the power is taken in float, so the last digits may differ
+        assert abs(float(plain[j]) - want) <= 2e-6 * want, (j, float(plain[j]), want)
+        assert abs(float(engine[j]) - want) <= 2e-6 * want, (j, float(engine[j]), want)
+    assert torch.allclose(plain, engine, rtol=1e-6, atol=0)
 
 
 def test_rms_norm_formula():

@@ -200,17 +200,34 @@ def test_window_group_requests_run_to_the_end():
     assert steps == 7 + 19 and s.block_manager.num_free_blocks == 8
 
 
-def test_stop_rules():
+def test_stop_rules_and_tokens_in_flight():
     r = Request("a", [1, 2, 3], SamplingParams(max_tokens=3, stop_token_ids=[9]), eos_token_id=7)
+    assert r.stops_at(9) and r.stops_at(7) and not r.stops_at(5)
     r.append_token(5)
-    assert r.check_stop(100) is None
-    r.append_token(9)
-    assert r.check_stop(100) == FinishReason.STOP
+    assert not r.at_count_limit(100)
     r2 = Request("b", [1], SamplingParams(max_tokens=2, ignore_eos=True), eos_token_id=7)
+    assert not r2.stops_at(7)
     r2.append_token(7)
-    assert r2.check_stop(100) is None
+    assert not r2.at_count_limit(100)
     r2.append_token(7)
-    assert r2.check_stop(100) == FinishReason.LENGTH
+    assert r2.at_count_limit(100)
     r3 = Request("c", [1, 2], SamplingParams(max_tokens=50))
     r3.append_token(1)
-    assert r3.check_stop(3) == FinishReason.LENGTH
+    assert r3.at_count_limit(3)
+    # a launched token holds its place and counts, gets its time when it lands, and can be dropped
+    r4 = Request("d", [4, 5], SamplingParams(max_tokens=4), arrival_time=10.0)
+    r4.num_computed_tokens = 2
+    i0 = r4.launch_token()
+    assert r4.has_token_in_flight and r4.num_tokens == 3 and r4.ttft is None and r4.in_flight_within(0) and not r4.is_prefill
+    i1 = r4.launch_token()
+    r4.land_token(i0, 8, now=10.5)
+    assert r4.ttft == 0.5 and r4.tokens(1, 2) == [5, 8]
+    assert not r4.in_flight_within(4) or r4.in_flight_within(3)
+    assert r4.in_flight_within(3) and not Request("e", [1]).in_flight_within(0)
+    r4.land_token(i1, 9, now=10.75)
+    assert r4.tpot == 0.25 and not r4.has_token_in_flight
+    r4.launch_token()
+    r4.drop_token_in_flight()
+    assert r4.output_token_ids == [8, 9] and len(r4.token_times) == 2
+    r4.truncate_output(1)
+    assert r4.output_token_ids == [8] and r4.tokens(0, 3) == [4, 5, 8]
