@@ -30,8 +30,8 @@ PREFILL_TOKENS = 2048
 
 
 def peaks() -> dict:
-    """Measured peaks if the driver wrote them, else the fallback figures of an earlier
-    measurement on this pool."""
+    """Measured peaks from ``MEASURED_PEAKS.json`` beside this file if it is there, else
+    fallback figures of an earlier measurement of a B200 (a copy's bandwidth, cuBLAS bfloat16)."""
     out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
     path = ROOT / "MEASURED_PEAKS.json"
     if path.is_file():
@@ -556,13 +556,183 @@ def run_only(args) -> dict:
     return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(1e3 * seconds, 3), "tokens_per_s": round(PREFILL_TOKENS / seconds, 1)}
 
 
+REF_DIR = ROOT / "baseline" / "_ref"
+
+
+def _reference_package() -> str | None:
+    """Puts umarhassan-cloud/kvforge's package (``tokenvault``) on the path.  It is pure Python:
+    what a wheel of it would install is a copy of its ``src/tokenvault`` folder, and that copy is
+    what ``baseline/_ref/tokenvault`` holds (its build backend, hatchling, is not installed
+    offline, so pip cannot make the wheel).  Returns why it is not there, or ``None``."""
+    if not (REF_DIR / "tokenvault" / "__init__.py").is_file():
+        src = Path(os.environ.get("KVFORGE_REFERENCE_SRC", "/root/reference/src")) / "tokenvault"
+        if not src.is_dir():
+            return f"no copy of the reference package under {REF_DIR.relative_to(ROOT)} and no checkout at {src.parent} to copy it from"
+        import shutil
+
+        REF_DIR.mkdir(parents=True, exist_ok=True)
+        shutil.copytree(src, REF_DIR / "tokenvault", ignore=shutil.ignore_patterns("__pycache__"))
+    sys.path.insert(0, str(REF_DIR))
+    return None
+
+
 def run_reference(args) -> dict:
-    """umarhassan-cloud/kvforge builds with hatchling, which is in neither this image nor its
-    offline wheelhouse, so ``pip install --no-index --no-build-isolation`` cannot build it."""
-    ref = ROOT / "baseline" / "_ref" / "tokenvault"
-    if not ref.is_dir():
-        return {"impl": "reference", "unavailable": "offline install failed: build backend hatchling is not installed and not in the wheelhouse"}
-    return {"impl": "reference", "unavailable": "reference arm not wired: the reference has no GPU kernels of its own and publishes no GPU numbers"}
+    """The same measurement on umarhassan-cloud/kvforge itself, unmodified, through its public
+    API: ``tokenvault.InferenceEngine`` on ``cuda`` in bfloat16 at its own ``llama-1b`` preset
+    (the Llama-3.2-1B shape; it has no llama3 frequency scaling, which changes neither bytes nor
+    flops), pages of 16 tokens, 8 prompts of 2,048 random token ids, the same warm-up and step
+    count.  ``e2e`` is ``InferenceEngine.step`` (host token ids in, host token ids out);
+    ``value`` is its step function and sampler alone (``ModelRunner.execute`` + ``Sampler``),
+    the counterpart of the own arm's device-timed figure.  Nothing of kvforge_b200 is imported."""
+    why = _reference_package()
+    if why:
+        return {"impl": "reference", "unavailable": why}
+    try:
+        import torch
+        import tokenvault
+        from tokenvault import CacheConfig, EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig
+        from tokenvault.batching.continuous import BatchItem
+        from tokenvault.model_loader import PRESETS as REF_PRESETS
+    except Exception as e:  # the copy is there but does not import here
+        return {"impl": "reference", "unavailable": f"importing the reference failed: {type(e).__name__}: {e}"}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    try:
+        return _time_reference(args, torch, InferenceEngine, EngineConfig, CacheConfig, SchedulerConfig, SamplingParams, BatchItem, REF_PRESETS["llama-1b"], tokenvault.__file__)
+    except Exception as e:
+        return {"impl": "reference", "unavailable": f"the reference failed on this device: {type(e).__name__}: {str(e)[:300]}"}
+
+
+def _time_reference(args, torch, InferenceEngine, EngineConfig, CacheConfig, SchedulerConfig, SamplingParams, BatchItem, cfg, where) -> dict:
+    batch, steps, warmup = 8, args.steps, args.warmup
+    pk = peaks()
+
+    def engine_for(n_seqs: int):
+        blocks = n_seqs * (CONTEXT // 16) + 8
+        return InferenceEngine(EngineConfig(
+            model=cfg, cache=CacheConfig(block_size=16, num_blocks=blocks, watermark=0.0),
+            scheduler=SchedulerConfig(max_num_seqs=n_seqs, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT),
+            device="cuda", dtype=torch.bfloat16, seed=0,
+        ))  # fmt: skip
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    gen = torch.Generator().manual_seed(2)
+    engine = engine_for(batch)
+    sp = SamplingParams(max_tokens=warmup + steps + 2 * batch + 8, temperature=0.0, ignore_eos=True)
+    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=gen).tolist() for _ in range(batch)]
+
+    # prefill of one 2,048-token prompt through the step function, as the own arm times it
+    bm = engine.block_manager
+    p_times = []
+    for _ in range(3):
+        bm.allocate("p", prompts[0])
+        torch.cuda.synchronize()
+        a, b = events()
+        a.record()
+        engine.runner.execute([BatchItem("p", prompts[0], 0, "last")])
+        b.record()
+        torch.cuda.synchronize()
+        p_times.append(a.elapsed_time(b) / 1e3)
+        bm.free("p")
+    p_seconds = min(p_times[1:])
+
+    # end to end: the engine's own loop
+    for prompt in prompts:
+        engine.add_request(prompt, sp)
+    while any(r.is_prefill for r in engine.scheduler.running) or engine.scheduler.num_waiting:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    sampler.start()
+    a, b = events()
+    t0 = time.perf_counter()
+    a.record()
+    produced = 0
+    for _ in range(steps):
+        produced += sum(len(o.new_token_ids) for o in engine.step())
+    b.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    e2e_seconds = max(a.elapsed_time(b) / 1e3, wall)
+    assert produced == batch * steps, (produced, batch * steps)
+    ctx_now = engine.scheduler.running[0].num_tokens
+    width = -(-ctx_now // 16)
+    # what its prepare_inputs copies per step (int64 tensors made from host lists) and what comes back
+    h2d = 8 * (6 * batch + 1 + batch * width)
+    d2h = 8 * batch
+    for r in list(engine.scheduler.running):
+        engine.abort_request(r.request_id)
+
+    # the step function and the sampler alone, at batch 8 / 1 / 64
+    def decode(n_seqs: int, k: int, w: int) -> float:
+        eng = engine if n_seqs <= batch else engine_for(n_seqs)
+        ids = [f"d{i}" for i in range(n_seqs)]
+        toks = torch.randint(0, cfg.vocab_size, (n_seqs, PROMPT_LEN), generator=gen).tolist()
+        for rid, t in zip(ids, toks):
+            eng.block_manager.allocate(rid, t)
+        for c in eng.kv_cache.key_caches + eng.kv_cache.value_caches:
+            c.normal_(0.0, 0.5)  # synthetic cache contents
+        params = [SamplingParams(temperature=0.0)] * n_seqs
+        pos = PROMPT_LEN
+        a, b = events()
+        for i in range(w + k):
+            if i == w:
+                torch.cuda.synchronize()
+                a.record()
+            for rid in ids:
+                eng.block_manager.append_slots(rid, pos + 1, pos)
+            logits = eng.runner.execute([BatchItem(rid, [7 + i], pos, "last") for rid in ids])
+            eng.sampler(logits, params)
+            pos += 1
+        b.record()
+        torch.cuda.synchronize()
+        for rid in ids:
+            eng.block_manager.free(rid)
+        return a.elapsed_time(b) / 1e3 / k
+
+    step_s = decode(batch, steps, warmup)
+    k = max(16, steps // 2)
+    points = {"decode_b1": round(1 / decode(1, k, 3), 1), "decode_b64": round(64 / decode(64, k, 3), 1)}
+    layers = cfg.num_layers
+    h, d, nh, nkv, inter, v = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, cfg.intermediate_size, cfg.vocab_size
+    per_layer = h * d * (nh + 2 * nkv) + nh * d * h + 3 * h * inter
+    weight_bytes = 2 * (layers * per_layer + v * h)
+    mean_ctx = PROMPT_LEN + warmup + steps / 2
+    achieved = (weight_bytes + batch * mean_ctx * 2 * layers * nkv * d * 2) / step_s / 1e9
+    p_flops = PREFILL_TOKENS * 2 * layers * per_layer + 2 * v * h + layers * 4 * nh * d * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2
+    return {
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, context 2048->4096)",
+        "value": round(batch / step_s, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": round(1e3 * step_s, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (random token ids, random-init weights, synthetic cache contents for the device-timed decode)",
+        "impl": "reference",
+        "config": {
+            "model": "tokenvault preset llama-1b (Llama-3.2-1B shape)", "layers": layers, "hidden": h, "heads": nh, "kv_heads": nkv,
+            "head_dim": d, "intermediate": inter, "vocab": v, "global_batch": batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+            "kv_block_size": 16, "tied_embeddings": cfg.tie_word_embeddings, "rope": "theta 5e5, no llama3 scaling (the reference has none; same bytes and flops)",
+            "attention_backend": "gather (its default)", "parallelism": "single-gpu", "package": "unmodified copy of src/tokenvault",
+            "peaks": pk["source"],
+        },  # fmt: skip
+        "e2e": {"value": round(produced / e2e_seconds, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "prefill": {"value": round(PREFILL_TOKENS / p_seconds, 1), "tokens": PREFILL_TOKENS, "ms": round(1e3 * p_seconds, 3),
+                    "frac": round(p_flops / p_seconds / (pk["bf16_tflops"] * 1e12), 4)},  # fmt: skip
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
 
 
 def main() -> int:
