@@ -102,6 +102,9 @@ class StepContext:
     # Where a token comes from the device: per token a row of ``token_feedback`` or -1.
     feedback_rows: torch.Tensor | None = None
     token_feedback: torch.Tensor | None = None
+    # The step's float residual stream [N, hidden], set by the model before its blocks run.  A mixer
+    # or feed-forward may add its result into it directly and return ``ops.ADDED`` instead of a tensor.
+    residual: torch.Tensor | None = None
     # Upper bound on any context (fixes grid sizes of captured decode steps).
     context_bound: int = 0
     # Per registered tile size a ``QueryTiles``.  Empty when every sequence brings one token.

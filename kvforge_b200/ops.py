@@ -190,6 +190,8 @@ def add_rmsnorm(
     if out.shape[-1] != h or weight.numel() != h:
         raise ValueError("add_rmsnorm: widths do not agree")
     dptr, pptr, nsplit, stride = None, None, 0, 0
+    if delta is ADDED:
+        delta = None
     if isinstance(delta, Partials):
         _need(delta.t, torch.float32, "partials", contiguous=False)
         if delta.t.shape[-1] != h or delta.t.stride(1) != h or delta.t.stride(2) != 1:
@@ -687,6 +689,29 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         raise TypeError("linear: out must be bfloat16 or float32")
+
+
+class _Added:
+    """What a mixer or a feed-forward returns when it has added its result into the step's float
+    residual stream (``StepContext.residual``) itself: nothing is left for the norm to add."""
+
+    def __repr__(self) -> str:
+        return "ADDED"
+
+
+ADDED = _Added()
+
+
+def linear_add(x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor) -> None:
+    """``acc += x @ w^T`` for bfloat16 ``x [M, K]``, ``w [N, K]`` and float ``acc [M, N]``: the library
+    product with 32-bit accumulation whose epilogue reads and writes ``acc`` in 32-bit, so the sum
+    with the residual stream is never rounded to bfloat16 and costs no pass of its own."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(w, torch.bfloat16, "w", contiguous=False)
+    _need(acc, torch.float32, "acc", contiguous=False)
+    if tuple(acc.shape) != (x.shape[0], w.shape[0]) or w.shape[1] != x.shape[1]:
+        raise ValueError("linear_add: shapes do not agree")
+    torch.addmm(acc, x, w.t(), out_dtype=torch.float32, out=acc)
 
 
 LIBRARY_SPLIT_MAX_M = 128  # up to here the library product of a narrow output gains from slices of K

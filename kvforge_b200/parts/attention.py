@@ -137,7 +137,7 @@ class PagedAttention(Mixer):
             q_stride = self.q_dim
         out = rt.buf("attn.out", n, self.q_dim)
         self.attend(ctx, q, q_stride, out, cache)
-        return project(rt, "attn.proj", out, self.w_o)
+        return project(rt, "attn.proj", out, self.w_o, ctx)
 
     def attend(self, ctx, q, q_stride, out, cache) -> None:
         scratch, bound, split = None, None, 256

@@ -11,12 +11,13 @@ Kinds of part and the call each must answer:
 * position encoding — ``table(rt)`` returns what its mixer's kernel needs (for rotary:
   the float ``inv_freq`` vector).  Built once per distinct spec and shared.
 * norm — ``forward(ctx, resid, delta, rows=None) -> x``: adds ``delta`` (``None``, a tensor in
-  the storage type, or the ``ops.Partials`` of a split-K product) into the float residual
-  stream, returns the normed rows in the storage type.
+  the storage type, the ``ops.Partials`` of a split-K product, or ``ops.ADDED`` when its
+  producer has added it into ``ctx.residual`` already) into the float residual stream, returns
+  the normed rows in the storage type.
 * mixer — ``cache_need()`` and ``state_shape()`` declare what it keeps between steps;
   ``forward(ctx, x, cache) -> y`` mixes along the sequence.  ``cache`` is a
   ``LayerCache`` (pages of this call, or of the call it reads) or ``None``.  ``y`` is a
-  tensor in the storage type or ``ops.Partials``; only a norm ever reads it.
+  tensor in the storage type, ``ops.Partials`` or ``ops.ADDED``; only a norm ever reads it.
 * feed-forward — ``forward(ctx, x) -> y`` per token (``y`` as for a mixer).
 * block — the arrangement of the above in one layer:
   ``forward(ctx, resid, delta, cache) -> delta`` (the sum not yet added to ``resid``).

@@ -57,4 +57,4 @@ class GatedMLP(FeedForward):
             gu = rt.buf("mlp.gate_up", n, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gu)
             ops.silu_mul(gu, act, interleaved=self.interleaved)
-        return project(rt, "mlp.out", act, self.w_down)
+        return project(rt, "mlp.out", act, self.w_down, ctx)

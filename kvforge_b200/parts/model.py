@@ -159,6 +159,7 @@ class DecoderModel:
         rt = self.rt
         resid = rt.buf("model.resid", ctx.num_tokens, self.spec.hidden_size, torch.float32)
         ops.embed(self.embed_table, ctx.token_ids, resid, rt.err, ctx.feedback_rows, ctx.token_feedback)
+        ctx.residual = resid
         delta = None
         for idx, call in enumerate(self.spec.execution):
             delta = self.blocks[call.layer].forward(ctx, resid, delta, self.caches[idx])

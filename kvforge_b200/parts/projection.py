@@ -12,9 +12,11 @@ from .. import ops
 PART_ROWS = ops.SKINNY_MAX_M * ops.SKINNY_MAX_SPLIT  # rows of the largest set of split-K slices
 
 
-def project(rt, name: str, x: torch.Tensor, w: torch.Tensor):
+def project(rt, name: str, x: torch.Tensor, w: torch.Tensor, ctx=None):
     """``x @ w^T`` back to the model width: the decode product (slices of K, summed by the norm
-    that follows) for a few tokens, the library product otherwise."""
+    that follows) for a few tokens, the library product otherwise.  Given the step's context, the
+    library product of many bfloat16 tokens adds its result straight into the float residual
+    stream (``ctx.residual``) and ``ops.ADDED`` is returned."""
     n, width = x.shape[0], w.shape[0]
     if ops.skinny_ok(x, w):
         splits = ops.skinny_splits(width, w.shape[1])
@@ -31,6 +33,10 @@ def project(rt, name: str, x: torch.Tensor, w: torch.Tensor):
         part = ops.Partials(rt.buf(name + "_part", splits * n, width, torch.float32, cap=PART_ROWS).view(splits, n, width))
         ops.linear_split_k(x, w, part)
         return part
+    resid = getattr(ctx, "residual", None)
+    if resid is not None and x.dtype == torch.bfloat16 and resid.shape[0] >= n and resid.shape[1] == width:
+        ops.linear_add(x, w, resid[:n])
+        return ops.ADDED
     y = rt.buf(name, n, width)
     ops.linear(x, w, y)
     return y
