@@ -80,10 +80,9 @@ class PagedAttention(Mixer):
         if self.position_spec is not None and self.position is None:
             self.position = build_part("position", self.position_spec)
             self.position.bind({}, rt)
-        if self.position is not None:
-            self.inv_freq = self.position.table()
-        else:
-            self.inv_freq = torch.empty(0, dtype=torch.float32, device=rt.device)
+        table = self.position.table() if self.position is not None else None
+        # no table: q and k are stored and used as the projections leave them
+        self.inv_freq = table if table is not None else torch.empty(0, dtype=torch.float32, device=rt.device)
 
     def _scratch(self, ctx):
         rt = self.rt

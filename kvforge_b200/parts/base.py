@@ -8,8 +8,15 @@ from the context, what it needs of the cache from the view it is given.
 
 Kinds of part and the call each must answer:
 
-* position encoding — ``table(rt)`` returns what its mixer's kernel needs (for rotary:
-  the float ``inv_freq`` vector).  Built once per distinct spec and shared.
+* position encoding — either of two calls, each with a default that does nothing.
+  ``table()`` is for encodings that turn pairs of query and key dims by the token's position:
+  it returns the float frequencies ``[rot/2]`` that the mixer's kernel multiplies positions
+  with (``None``: queries and keys are left as they are).  Such an encoding is named in a
+  mixer's ``position`` parameter, built once per distinct spec and shared.
+  ``embed(ctx, resid)`` is for encodings that act on the residual stream right after the
+  embedding lookup (learned or fixed absolute positions): it adds to ``resid[n]`` in place from
+  ``ctx.positions``.  Such an encoding is named in ``ModelSpec.input_position`` and may have
+  weights of its own.
 * norm — ``forward(ctx, resid, delta, rows=None) -> x``: adds ``delta`` (``None``, a tensor in
   the storage type, the ``ops.Partials`` of a split-K product, or ``ops.ADDED`` when its
   producer has added it into ``ctx.residual`` already) into the float residual stream, returns
@@ -96,8 +103,13 @@ class Part:
 
 
 class PositionEncoding(Part):
-    def table(self) -> torch.Tensor:  # pragma: no cover - interface
-        raise NotImplementedError
+    def table(self) -> torch.Tensor | None:
+        """Float frequencies ``[rot/2]`` for a mixer that turns q and k, or ``None``."""
+        return None
+
+    def embed(self, ctx, resid: torch.Tensor) -> None:
+        """Add this encoding to the float residual stream after the embedding lookup."""
+        return None
 
 
 class Norm(Part):

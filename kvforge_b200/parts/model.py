@@ -46,6 +46,10 @@ class ModelSpec:
     # names that may be in a checkpoint and are not weights
     ignore_suffixes: tuple[str, ...] = ("rotary_emb.inv_freq",)
     max_position_embeddings: int = 0
+    # a position encoding that acts on the residual stream after the embedding lookup (``embed``);
+    # its tensors, if it has any, carry ``input_position_prefix``
+    input_position: PartSpec | None = None
+    input_position_prefix: str = "model.embed_positions."
     eos_token_id: int | None = None
     bos_token_id: int | None = None
 
@@ -78,6 +82,7 @@ class DecoderModel:
         self.spec = spec
         self.blocks: list[Block] = [build_part("block", ls.block, ls.prefix) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
+        self.input_position = build_part("position", spec.input_position, spec.input_position_prefix) if spec.input_position else None
         # cache groups from what the mixers declare
         self.groups: list[CacheGroup] = []
         self.call_group: list[tuple[int, int] | None] = []  # per call: (group, entry) of its own cache
@@ -125,6 +130,8 @@ class DecoderModel:
         for block in self.blocks:
             yield from block.sub_parts()
         yield self.final_norm
+        if self.input_position is not None:
+            yield self.input_position
 
     def bind(self, weights: dict[str, torch.Tensor], rt) -> None:
         s = self.spec
@@ -160,6 +167,8 @@ class DecoderModel:
         resid = rt.buf("model.resid", ctx.num_tokens, self.spec.hidden_size, torch.float32)
         ops.embed(self.embed_table, ctx.token_ids, resid, rt.err, ctx.feedback_rows, ctx.token_feedback)
         ctx.residual = resid
+        if self.input_position is not None:
+            self.input_position.embed(ctx, resid)
         delta = None
         for idx, call in enumerate(self.spec.execution):
             delta = self.blocks[call.layer].forward(ctx, resid, delta, self.caches[idx])

@@ -518,3 +518,77 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_bu
             check(steps, outs, ref, 2e-5)
     finally:
         unregister_architecture("ToyRoutedForCausalLM")
+
+
+def test_a_toy_position_encoding_added_at_the_embedding_and_attention_without_rotation(tmp_path):
+    """Learned absolute positions: a table of its own tensor, added to the residual stream after
+    the embedding lookup; the attention layers get no position encoding at all and leave queries
+    and keys as projected.  Both through the public registries and ``ModelSpec`` alone, in 32-bit
+    and bfloat16, eager and as captured graphs."""
+    from kvforge_b200 import ModelConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.base import POSITION_ENCODINGS, PartSpec, PositionEncoding, WeightDecl, register_position_encoding
+    from kvforge_b200.parts.model import DecoderModel
+    from kvforge_b200.weights.random_init import write_model_dir
+    from test_gpu_replay import TOL, check, run_trace
+
+    max_pos = 160
+
+    class LearnedPositions(PositionEncoding):
+        @classmethod
+        def weight_decls(cls, params):
+            return {"weight": WeightDecl((int(params["max_positions"]), int(params["hidden_size"])))}
+
+        def bind(self, weights, rt):
+            super().bind(weights, rt)
+            self.weight = weights["weight"].float()
+
+        def embed(self, ctx, resid):
+            resid.add_(self.weight[ctx.positions.long()])
+
+    if "toy_learned_positions" not in POSITION_ENCODINGS:
+        register_position_encoding("toy_learned_positions")(LearnedPositions)
+
+    def build(cfg):
+        spec = llama_spec(cfg)
+        for ls in spec.layers:
+            mixer = ls.block.params["mixer"]
+            ls.block.params["mixer"] = PartSpec(mixer.kind, {**mixer.params, "position": None})
+        spec.input_position = PartSpec("toy_learned_positions", {"max_positions": max_pos, "hidden_size": cfg.hidden_size})
+        return spec
+
+    register_architecture("ToyLearnedPositionsForCausalLM", ModelConfig.from_hf_dict, build)
+    try:
+        cfg = TINY["tiny-d"]["cfg"]
+        cj = cfg.to_hf_dict()
+        cj["architectures"] = ["ToyLearnedPositionsForCausalLM"]
+        model = DecoderModel(build(cfg))
+        assert "model.embed_positions.weight" in model.expected_weights()
+        assert cfg.tie_word_embeddings  # so the folder holds no separate output head
+        folder = write_model_dir(tmp_path / "toy", cj, model.expected_weights(), seed=9, store_dtype=torch.bfloat16, init_std=0.1, norm_std=0.1, skip=("lm_head.weight",))
+
+        class ToyPlain(PlainLlama):
+            def __init__(self, *a, **k):
+                super().__init__(*a, **k)
+                self.inv_freq = torch.zeros(self.d // 2)  # angle 0: no rotation
+
+            def embed(self, ids):
+                return super().embed(ids) + self.w["embed_positions.weight"][: ids.shape[0]]
+
+        plain = ToyPlain(folder)
+        reqs = {f"r{i}": random_tokens(cfg.vocab_size, n, seed=20 + i) for i, n in enumerate([70, 5, 130, 33])}
+        ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+        # positions matter: the same tokens in another order give other logits at the last place
+        swapped = list(reqs["r0"])
+        swapped[3], swapped[40] = swapped[40], swapped[3]
+        assert rel_err(plain.logits(swapped)[-1], ref["r0"][-1]) > 1e-3
+        cuts = (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: max(1, len(t) - 6) for r, t in reqs.items()}, max_live=3, seed=2))
+        for dtype in ("float32", "bfloat16"):
+            for graphs in (False, True):
+                for steps in cuts:
+                    steps = traces.last_only(steps) if graphs else steps
+                    outs, _ = run_trace(folder, dtype, steps, max_live=3, cuda_graphs=graphs)
+                    check(steps, outs, ref, TOL[dtype])
+    finally:
+        unregister_architecture("ToyLearnedPositionsForCausalLM")
