@@ -15,7 +15,8 @@ the step; their pages are given back.  A step with wanted places writes
 ``<out>/<step>.f32``: little-endian float32 ``[wanted, vocab]`` in the order of the entries
 and of ``want``.  After every step ``done <step>`` is printed and flushed.
 
-The page size is 16 tokens unless ``--block-size`` says otherwise, the pool holds
+``--preset NAME --seed S`` stands for ``--model``: the named shape with random weights made
+on the device.  The page size is 16 tokens unless ``--block-size`` says otherwise, the pool holds
 ``--max-tokens`` tokens (each request rounded up to 64, or to the page if that is larger)
 unless ``--num-blocks`` gives it in pages, and ``--cuda-graphs`` replays the steps the way
 bfloat16 generation does by default: captured graphs for padded shapes, every shape captured
@@ -35,7 +36,10 @@ ROUND = 64  # --max-tokens counts each request rounded up to this (or to the pag
 
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    src = ap.add_mutually_exclusive_group(required=True)
+    src.add_argument("--model", help="folder with config.json and model.safetensors")
+    src.add_argument("--preset", help="a named shape instead of a folder: random weights made on the device from --seed")
+    ap.add_argument("--seed", type=int, default=0, help="with --preset: seed of the random weights")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="most tokens live requests hold at any time")
@@ -59,16 +63,18 @@ def pages_for(max_tokens: int, block_size: int, max_live: int) -> int:
 class TraceRunner:
     def __init__(
         self,
-        model_dir: str,
+        model_dir: str | None,
         dtype: str,
         max_tokens: int,
         max_live: int = 16,
         block_size: int = PAGE,
         num_blocks: int | None = None,
         cuda_graphs: bool = False,
+        preset: str | None = None,
+        seed: int = 0,
     ) -> None:
         from .config.engine_config import CacheConfig
-        from .engine.core import EngineCore
+        from .engine.core import EngineCore, spec_from_config
 
         block_size = int(block_size)
         if block_size <= 0:
@@ -76,8 +82,17 @@ class TraceRunner:
         if num_blocks is None:
             num_blocks = pages_for(max_tokens, block_size, max_live)
         budget = max(int(max_tokens), block_size)
-        self.core = EngineCore.from_model_dir(
-            model_dir,
+        if (model_dir is None) == (preset is None):
+            raise ValueError("give a model folder or a preset, not both")
+        if preset is not None:
+            from .config.registry import PRESETS
+
+            if preset not in PRESETS:
+                raise ValueError(f"no preset named {preset!r} (known: {sorted(PRESETS)})")
+            make = lambda **kw: EngineCore(spec_from_config(PRESETS[preset]), seed=seed, **kw)  # noqa: E731
+        else:
+            make = lambda **kw: EngineCore.from_model_dir(model_dir, **kw)  # noqa: E731
+        self.core = make(
             dtype=dtype,
             cache=CacheConfig(block_size=block_size, num_blocks=int(num_blocks), watermark=0.0),
             max_num_seqs=max_live,
@@ -136,7 +151,7 @@ def main(argv=None) -> int:
     args = parse_args(argv)
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
-    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.max_live, args.block_size, args.num_blocks, args.cuda_graphs)
+    runner = TraceRunner(args.model, args.dtype, args.max_tokens, args.max_live, args.block_size, args.num_blocks, args.cuda_graphs, args.preset, args.seed)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -327,3 +327,23 @@ def test_trace_run_program(folders, oracle, tmp_path):
         assert a.size == len(rows) * vocab
         outputs.append(torch.from_numpy(a.reshape(len(rows), vocab)))
     check(steps, outputs, ref, TOL["float32"])
+
+
+def test_a_preset_with_a_seed_stands_for_a_model_folder(tmp_path):
+    """``--preset NAME --seed S`` makes on the device the weights that the random-weights mode
+    writes into a folder for the same shape and seed (drawn on the same device): same logits."""
+    from kvforge_b200 import PRESETS
+    from kvforge_b200.models.folder import write_random_model
+    from kvforge_b200.replay import TraceRunner
+
+    folder = write_random_model(tmp_path / "m", PRESETS["tiny-b"], seed=4, store_dtype=torch.float32, device="cuda")
+    toks = random_tokens(PRESETS["tiny-b"].vocab_size, 40, seed=8)
+    steps = traces.portions({"a": toks})
+    a = run_trace(folder, "float32", steps)[0]
+    runner = TraceRunner(None, "float32", traces.tokens_needed(steps), preset="tiny-b", seed=4)
+    b = [runner.step(s) for s in steps]
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    other = TraceRunner(None, "float32", traces.tokens_needed(steps), preset="tiny-b", seed=5)
+    assert not torch.equal(other.step(steps[0]), a[0])
+    with pytest.raises(ValueError):
+        TraceRunner(None, "float32", 64)
