@@ -58,6 +58,7 @@ struct DecParams {
   int window;
   int single_only;  // sequences that bring more than one query are left alone (another kernel's)
   int split_size, max_splits, grid_splits;
+  int wave_target;  // > 0: the range size doubles until the ranges of the longest context are at most this many CTAs
   int total_rows;  // rows of the cache seen as [rows][D]: a copy from this row reads zeros
   float scale_log2;
 };
@@ -179,13 +180,25 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int g = p.nh / p.nkv;  // <= 8
   const int q_begin = p.qsl[b], q_len = p.qsl[b + 1] - q_begin;
   const int ctx = p.ctx_lens[b];
-  const int range_lo = split * p.split_size;
+  // The range size of the launch, or a multiple of it: with few (sequence, kv head) pairs a long
+  // context makes more CTAs than run at once, and a second, small wave costs more than longer
+  // ranges do.  Every CTA works the size out for itself from the step's longest context, so all
+  // agree; the grid was made for the launch's size, and ranges that get no keys leave below.
+  int split_size = p.split_size;
+  if (p.wave_target > 0) {
+    int longest = 0;
+    for (int i = lane; i < (int)gridDim.y; i += 32) longest = max(longest, p.ctx_lens[i]);
+    longest = __reduce_max_sync(0xffffffffu, longest);
+    const int pairs = (int)(gridDim.y * gridDim.z);
+    while (split_size < 8192 && (long long)pairs * ((longest + split_size - 1) / split_size) > p.wave_target) split_size <<= 1;
+  }
+  const int range_lo = split * split_size;
   // dead: no query, a range past the context (the merge never reads it), or shared memory that
   // does not start where the swizzle needs it (refused: bit 8 of the error flag)
   const bool aligned = (base & 1023u) == 0;
   const bool seq_live = (p.single_only ? q_len == 1 : q_len > 0) && ctx > 0;  // the same for all ranges of a sequence: for a whole cluster
   const bool live = seq_live && range_lo < ctx && aligned;
-  const int kv_hi = min(ctx, range_lo + p.split_size);
+  const int kv_hi = min(ctx, range_lo + split_size);
   const int first_seen = max(range_lo, p.window > 0 ? ctx - p.window : 0);  // first key this range may show
   const int kv_lo = (first_seen / UNIT) * UNIT;
   const bool empty = kv_lo >= kv_hi;  // wholly before the window
@@ -231,7 +244,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (!aligned && threadIdx.x == 0 && p.err) atomicOr(p.err, 8);
   if (CLUSTER ? !seq_live : !live) return;
   const size_t slot0 = ((size_t)b * p.nh + (size_t)kvh * g) * p.max_splits + split;  // + head * max_splits
-  const int ns = min(min(p.max_splits, p.grid_splits), (ctx + p.split_size - 1) / p.split_size);
+  const int ns = min(min(p.max_splits, p.grid_splits), (ctx + split_size - 1) / split_size);
 
   float* cpart = reinterpret_cast<float*>(smem_raw + S::CPART_OFFSET);  // CLUSTER: [8][D + 2]
   if (empty || !live) {  // (not live: only with CLUSTER) nothing to add, and it says so
@@ -518,7 +531,7 @@ int run_dec(const void* q, void* out, const void* kcache, const void* vcache,
             const int* block_tables, const int* qsl, const int* ctx_lens, int B, int q_stride, int out_stride,
             int bt_stride, int nh, int nkv, int d, int block_size, long long num_blocks, float scale, int window,
             int split_size, int max_splits, int grid_splits, float* part_acc, float* part_ml, int* tickets, int* err,
-            int flags, cudaStream_t st) {
+            int flags, int wave_target, cudaStream_t st) {
   if (B <= 0) return 0;
   const int cluster = flags & 1;
   if ((d != 64 && d != 128) || nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh / nkv > 8) return (int)cudaErrorInvalidValue;
@@ -541,7 +554,7 @@ int run_dec(const void* q, void* out, const void* kcache, const void* vcache,
   p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.single_only = (flags & 2) ? 1 : 0;
-  p.split_size = split_size; p.max_splits = max_splits;
+  p.split_size = split_size; p.max_splits = max_splits; p.wave_target = wave_target > 0 ? wave_target : 0;
   p.grid_splits = grid_splits > 0 && grid_splits < max_splits ? grid_splits : max_splits;
   p.total_rows = (int)rows;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -569,13 +582,16 @@ int run_dec(const void* q, void* out, const void* kcache, const void* vcache,
 // through a thread-block cluster's shared memory instead (scratch and tickets are then unused,
 // unless such a cluster cannot be launched here).  flags bit 1: only sequences that bring exactly
 // one query are computed (the others of a mixed batch belong to the kernel of prompts).
+// wave_target > 0: the kernel doubles split_size (up to 8,192) until the ranges of the longest
+// context of the batch, over all B * nkv pairs, are at most that many.
 KVF_API int kvf_paged_attention_decode_tma_bf16(const void* q, void* out, const void* kcache, const void* vcache,
                                                 const int* block_tables, const int* qsl, const int* ctx_lens, int B,
                                                 int q_stride, int out_stride, int bt_stride, int nh, int nkv, int d,
                                                 int block_size, long long num_blocks, float scale, int window,
                                                 int split_size, int max_splits, int grid_splits, float* part_acc,
-                                                float* part_ml, int* tickets, int* err, int flags, cudaStream_t st) {
+                                                float* part_ml, int* tickets, int* err, int flags, int wave_target,
+                                                cudaStream_t st) {
   return run_dec(q, out, kcache, vcache, block_tables, qsl, ctx_lens, B, q_stride, out_stride, bt_stride, nh,
                  nkv, d, block_size, num_blocks, scale, window, split_size, max_splits, grid_splits, part_acc, part_ml,
-                 tickets, err, flags, st);
+                 tickets, err, flags, wave_target, st);
 }

@@ -28,7 +28,7 @@ _SIGNATURES = {
     "kvf_paged_attention_mma_bf16": "pppppppiiiiiiiiifiiiippp",
     "kvf_paged_attention_tcgen05_bf16": "pppppppiiiiiiiiilfipipp",
     "kvf_paged_attention_decode_fused_bf16": "pppppppiiiiiiiifiiiipppp",
-    "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppip",
+    "kvf_paged_attention_decode_tma_bf16": "pppppppiiiiiiiilfiiiippppiip",
     "kvf_gemm_nt_f32": "pppiiiiiip",
     "kvf_gemm_skinny_bf16": "pppiiiiiiiilp",
     "kvf_set_pdl": "i",
@@ -338,19 +338,35 @@ def cast_from_float(src: torch.Tensor, out: torch.Tensor) -> None:
 MAX_ATTN_SPLITS = 1024  # ranges per (sequence, head) the merge kernel takes
 
 
+ATTN_ONE_WAVE = 640  # CTAs of the decode attention that run as one wave with room to spare (six fit an SM)
+
+
 def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
-    """Keys per range of the decode form.  A range is a CTA, and a CTA has a fixed cost of a few
-    microseconds (its chain of dependent reads, its share of the merge), so ranges are not
-    short: 256 keys, 512 with many (sequence, kv head) pairs (measured inside the decode step at
-    1, 8 and 64 sequences), and more when the context is so long that there would be more than
-    ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of it.  Since the size follows the
-    number of sequences, so does the order in which a context's keys are merged: a caller that
-    wants sums that do not depend on the batch at all (the 32-bit path) passes ``num_seqs=1``."""
+    """Keys per range of the decode form, as the launch fixes it.  A range is a CTA, and a CTA has
+    a fixed cost of a few microseconds (its chain of dependent reads, its share of the merge), so
+    ranges are not short: 256 keys, 512 with many (sequence, kv head) pairs (measured inside the
+    decode step at 1, 8 and 64 sequences), and more when the context is so long that there would
+    be more than ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of the size.  (The TMA
+    kernel may double the size further at run time, see ``attention_wave_target``.)  Since the
+    size follows the number of sequences, so does the order in which a context's keys are merged:
+    a caller that wants sums that do not depend on the batch at all (the 32-bit path) passes
+    ``num_seqs=1``."""
     pairs = num_seqs * nkv
     split = 512 if pairs >= 256 else 256
     while -(-max_context // split) > MAX_ATTN_SPLITS:
         split *= 2
     return split
+
+
+def attention_wave_target(num_seqs: int, nkv: int) -> int:
+    """How many live CTAs the TMA decode kernel aims at: it doubles the range size, on the
+    device, from the step's longest context, until the ranges of all (sequence, kv head) pairs
+    are at most this many: one wave of CTAs for few pairs (8 sequences at 4,096 keys: ranges of
+    256 make 1,024 CTAs, a wave and a small second one, 21.7 us; ranges of 512 one wave, 15.3 us),
+    about four ranges a pair for many (64 sequences at 8,192 keys: ranges of 512 take 196 us,
+    ranges of 2,048 take 162 us).  The launch's grid is made for the smallest size; CTAs of
+    ranges that a larger size leaves without keys exit at once."""
+    return max(ATTN_ONE_WAVE, 4 * num_seqs * nkv)
 
 
 def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, split_size: int = 256) -> tuple[tuple[int, ...], tuple[int, ...]]:
@@ -416,6 +432,7 @@ def paged_attention(
     cluster: bool = True,
     query_tiles: tuple[torch.Tensor, int] | None = None,
     single_only: bool = False,
+    wave_target: int = 0,
 ) -> None:
     """Paged GQA attention of a flat batch (the contract is at the top of
     ``csrc/attention_generic.cu``).
@@ -432,7 +449,9 @@ def paged_attention(
     -1, first query) pairs, one per tile of ``tcgen05_query_tile`` queries, and how many of them to
     launch; without it the grid spans every sequence times the tiles of the longest query run.
     ``single_only`` (TMA decode kernel): of a mixed batch only the sequences that bring exactly one
-    query are computed; the rows of the others are left untouched.
+    query are computed; the rows of the others are left untouched.  ``wave_target`` (TMA decode
+    kernel, 0 = off): the kernel doubles ``split_size`` until the ranges of the step's longest
+    context, over all pairs, are at most this many (``attention_wave_target``).
     """
     s = _suffix(q.dtype)
     check_head_dim(d)
@@ -513,7 +532,7 @@ def paged_attention(
             _fn(name)(
                 _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), _ptr(qsl), _ptr(ctx_lens),
                 num_seqs, q_stride, out.shape[-1], bt_stride, nh, nkv, d, block_size, int(kcache.shape[0]), float(scale),
-                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(bool(cluster)) | (2 if single_only else 0), _stream(),
+                int(window), split, max_splits, grid_splits, _ptr(pa), _ptr(pm), _ptr(tickets), _ptr(err), int(bool(cluster)) | (2 if single_only else 0), int(wave_target), _stream(),
             ),
             name,
         )  # fmt: skip

@@ -143,6 +143,9 @@ class PagedAttention(Mixer):
         common = dict(window=int(self.window or 0), q_stride=q_stride, err=self.rt.err)
         args = (q, out, cache.k, cache.v, ctx.block_tables[cache.group], ctx.query_start_loc, ctx.context_lens, ctx.num_seqs)
         shape = (self.nh, self.nkv, self.d, self.scale)
+        # bfloat16: the decode kernel may lengthen its key ranges from the step's longest context (the merge
+        # order then follows the batch, within rounding); 32-bit keeps one order whatever the batch
+        wave = ops.attention_wave_target(ctx.num_seqs, self.nkv) if q.dtype == torch.bfloat16 else 0
         if ctx.all_single_query:
             scratch, bound, split = self._scratch(ctx)
         tiles = ctx.query_tiles.get(self._query_tile)
@@ -150,12 +153,12 @@ class PagedAttention(Mixer):
             # a mixed batch: the sequences that bring one token go to the decode kernel (key ranges in
             # parallel), the portions of prompts to the kernel of prompts; each leaves the other's rows alone
             scratch, bound, split = self._scratch(ctx)
-            ops.paged_attention(*args, 1, *shape, scratch=scratch, max_context=bound, split_size=split, kernel="tma", cluster=False, single_only=True, **common)
+            ops.paged_attention(*args, 1, *shape, scratch=scratch, max_context=bound, split_size=split, kernel="tma", cluster=False, single_only=True, wave_target=wave, **common)
             if tiles.multi_count > 0:
                 ops.paged_attention(*args, ctx.max_query_len, *shape, query_tiles=(tiles.multi, tiles.multi_count), **common)
             return
         ops.paged_attention(
             *args, ctx.max_query_len, *shape, scratch=scratch, max_context=bound, split_size=split,
-            cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS,
+            cluster=ctx.num_seqs * self.nkv <= CLUSTER_MERGE_MAX_PAIRS, wave_target=wave if scratch is not None else 0,
             query_tiles=(tiles.tiles, tiles.count) if tiles is not None else None, **common,
         )  # fmt: skip

@@ -279,7 +279,7 @@ def paged(kv_per_seq, nkv, d, bs, dtype, seed=0, extra_blocks=5, junk=(1e4, -1e4
     return kc, vc, tables
 
 
-def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256, junk=(1e4, -1e4), cluster=True):
+def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode_form=False, seed=0, craft=None, kernel="generic", split=256, junk=(1e4, -1e4), cluster=True, wave_target=0):
     g = torch.Generator().manual_seed(seed)
     kv = [(torch.randn(c, nkv, d, generator=g).to(dtype), torch.randn(c, nkv, d, generator=g).to(dtype)) for c in ctx_lens]
     qs = [torch.randn(ql, nh, d, generator=g).to(dtype) for ql in q_lens]
@@ -302,7 +302,7 @@ def run_attention(ops, dtype, nh, nkv, d, bs, ctx_lens, q_lens, window=0, decode
         ops.paged_attention(
             dev(q), out, dev(kc), dev(vc), dev(tables), dev(qsl), dev(torch.tensor(ctx_lens, dtype=torch.int32)),
             len(ctx_lens), max(q_lens), nh, nkv, d, scale, window=window, scratch=scratch, max_context=bound,
-            split_size=split, kernel=kernel, err=err_flag(), cluster=cluster,
+            split_size=split, kernel=kernel, err=err_flag(), cluster=cluster, wave_target=wave_target,
         )  # fmt: skip
     if decode_form == "fused":
         assert int(scratch[2].abs().sum()) == 0
@@ -533,6 +533,23 @@ def test_paged_attention_tma_decode(ops, nh, nkv, d, bs, split, cluster):
     assert int(err_flag().sum()) == 0
     assert not torch.isnan(out).any()
     assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("target", [1, 7, 12, 40, 10000])
+@pytest.mark.parametrize("cluster", [False, True])
+def test_tma_decode_lengthens_its_ranges_to_the_wave_it_is_given(ops, target, cluster):
+    """With a target number of CTAs the kernel doubles the range size from the batch's longest
+    context (1,500 keys, 4 pairs: ranges of 64 would be 96 CTAs): whatever size comes out, every
+    sequence's result is the plain one, also those whose contexts end inside a lengthened range,
+    and a window still cuts where it should."""
+    ctx = [700, 1, 256, 257, 33, 64, 65, 1500, 16, 17]
+    err_flag().zero_()
+    for window in (0, 90):
+        out, ref, _ = run_attention(ops, torch.bfloat16, 8, 2, 64, 16, ctx, [1] * len(ctx), decode_form="fused", kernel="tma", split=64,
+                                    window=window, junk=(float("nan"), float("nan")), cluster=cluster, wave_target=target)  # fmt: skip
+        assert int(err_flag().sum()) == 0
+        assert not torch.isnan(out).any()
+        assert torch.allclose(out, ref, rtol=2e-2, atol=2e-2), (target, window)
 
 
 def test_tma_decode_finds_a_far_key_and_respects_the_window(ops):
