@@ -363,10 +363,11 @@ def attention_wave_target(num_seqs: int, nkv: int) -> int:
     device, from the step's longest context, until the ranges of all (sequence, kv head) pairs
     are at most this many: one wave of CTAs for few pairs (8 sequences at 4,096 keys: ranges of
     256 make 1,024 CTAs, a wave and a small second one, 21.7 us; ranges of 512 one wave, 15.3 us),
-    about four ranges a pair for many (64 sequences at 8,192 keys: ranges of 512 take 196 us,
-    ranges of 2,048 take 162 us).  The launch's grid is made for the smallest size; CTAs of
-    ranges that a larger size leaves without keys exit at once."""
-    return max(ATTN_ONE_WAVE, 4 * num_seqs * nkv)
+    at most six ranges a pair for many (64 sequences at 8,192 keys: ranges of 512 take 196 us,
+    ranges of 2,048 take 162 us; four a pair made ranges so long that their CTAs no longer ran
+    as even waves).  The launch's grid is made for the smallest size; CTAs of ranges that a
+    larger size leaves without keys exit at once."""
+    return max(ATTN_ONE_WAVE, 6 * num_seqs * nkv)
 
 
 def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, split_size: int = 256) -> tuple[tuple[int, ...], tuple[int, ...]]:
