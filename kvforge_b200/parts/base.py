@@ -27,7 +27,10 @@ Kinds of part and the call each must answer:
   tensor in the storage type, ``ops.Partials`` or ``ops.ADDED``; only a norm ever reads it.
 * feed-forward — ``forward(ctx, x) -> y`` per token (``y`` as for a mixer).
 * block — the arrangement of the above in one layer:
-  ``forward(ctx, resid, delta, cache) -> delta`` (the sum not yet added to ``resid``).
+  ``forward(ctx, resid, delta, cache) -> delta`` (the sum not yet added to ``resid``).  An
+  arrangement in which a part's result must not go straight into the residual stream (a norm
+  after the sum, two parts reading the same stream) sets ``ctx.residual = None`` around that
+  part's call and gets a tensor or ``ops.Partials`` back.
 """
 
 from __future__ import annotations
