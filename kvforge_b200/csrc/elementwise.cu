@@ -150,47 +150,59 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
-// The same for many rows: a warp per row keeps the row in registers (VPT float4 per lane, H <=
-// 128 * VPT), so a row costs one trip to memory with all its loads in flight and no block-wide
-// barrier.
+// Without slices of a split product, for H % 4 == 0 and H <= 512 * VPT: a CTA of 128 threads per
+// row, the row in registers (VPT 16-byte loads per thread, all in flight at once, the norm's
+// weight among them since it does not wait for the sum), one reduction over four warps.  Small
+// CTAs with few registers: sixteen rows are on an SM at a time, which is what keeps the memory
+// pipe full when there are thousands of rows (2,048 rows of 4,096: 6.4 us; a row per warp, with
+// its row in 128 registers, took 21 us, a row per CTA of 1,024 threads 22 us), and it is no
+// slower than those on a handful of rows.  The reduction tree depends on H alone.
 template <typename T, int VPT>
-__global__ void __launch_bounds__(128) add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+__global__ void __launch_bounds__(128) add_rmsnorm_rows_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                                                const float* __restrict__ weight, T* __restrict__ out,
-                                                               const int* __restrict__ rows, int n_rows, int H, float eps) {
+                                                               const int* __restrict__ rows, int H, float eps) {
   pdl_launch();
-  pdl_wait();
-  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= n_rows) return;
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  float4 w[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {  // the weight comes from no kernel ahead: fetched before the wait
+    const int i = (k * 128 + threadIdx.x) * 4;
+    w[k] = i < H ? *reinterpret_cast<const float4*>(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const int src = rows ? rows[r] : r;
+  pdl_wait();
   float* h = resid + (size_t)src * H;
   const T* dl = delta ? delta + (size_t)src * H : nullptr;
   float4 v[VPT];
-  float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = (k * 32 + lane) * 4;
-    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (i < H) {
-      v[k] = *reinterpret_cast<const float4*>(h + i);
-      if (dl) {
+    const int i = (k * 128 + threadIdx.x) * 4;
+    v[k] = i < H ? *reinterpret_cast<const float4*>(h + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (dl) {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = (k * 128 + threadIdx.x) * 4;
+      if (i < H) {
         const float4 d = Vec4<T>::load(dl + i);
         v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
       }
     }
   }
+  float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
-  ss = warp_sum(ss);
+  ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)H + eps);
   const bool write_back = dl != nullptr && rows == nullptr;
   T* o = out + (size_t)r * H;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int i = (k * 32 + lane) * 4;
+    const int i = (k * 128 + threadIdx.x) * 4;
     if (i < H) {
       if (write_back) *reinterpret_cast<float4*>(h + i) = v[k];
-      const float4 w = *reinterpret_cast<const float4*>(weight + i);
-      Vec4<T>::store(o + i, make_float4(v[k].x * inv * w.x, v[k].y * inv * w.y, v[k].z * inv * w.z, v[k].w * inv * w.w));
+      Vec4<T>::store(o + i, make_float4(v[k].x * inv * w[k].x, v[k].y * inv * w[k].y, v[k].z * inv * w[k].z, v[k].w * inv * w[k].w));
     }
   }
 }
@@ -555,13 +567,19 @@ static inline int norm_threads(int H) {
                                     long long split_stride, const float* weight, void* out,              \
                                     const int* rows, int n_rows, int H, float eps, cudaStream_t st) {    \
     if (n_rows <= 0) return 0;                                                                           \
-    if ((H & 3) == 0 && H <= 4096 && !partials && n_rows >= 1024) {                                       \
-      const unsigned blocks = (unsigned)((n_rows + 3) / 4);                                              \
+    if ((H & 3) == 0 && H <= 4096 && !partials) {                                                        \
+      const dim3 g(n_rows), b(128);                                                                      \
+      if (H <= 512)                                                                                      \
+        return launch(add_rmsnorm_rows_kernel<T, 1>, g, b, 0, st, resid, (const T*)delta, weight,        \
+                      (T*)out, rows, H, eps);                                                            \
+      if (H <= 1024)                                                                                     \
+        return launch(add_rmsnorm_rows_kernel<T, 2>, g, b, 0, st, resid, (const T*)delta, weight,        \
+                      (T*)out, rows, H, eps);                                                            \
       if (H <= 2048)                                                                                     \
-        return launch(add_rmsnorm_warp_kernel<T, 16>, dim3(blocks), dim3(128), 0, st, resid,              \
-                      (const T*)delta, weight, (T*)out, rows, n_rows, H, eps);                           \
-      return launch(add_rmsnorm_warp_kernel<T, 32>, dim3(blocks), dim3(128), 0, st, resid,                \
-                    (const T*)delta, weight, (T*)out, rows, n_rows, H, eps);                             \
+        return launch(add_rmsnorm_rows_kernel<T, 4>, g, b, 0, st, resid, (const T*)delta, weight,        \
+                      (T*)out, rows, H, eps);                                                            \
+      return launch(add_rmsnorm_rows_kernel<T, 8>, g, b, 0, st, resid, (const T*)delta, weight,          \
+                    (T*)out, rows, H, eps);                                                              \
     }                                                                                                    \
     if ((H & 3) == 0 && H <= 32768 && (split_stride & 3) == 0) {                                         \
       int t = 32;                                                                                        \
