@@ -437,37 +437,40 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restri
   }
   const size_t cache_row = slot >= 0 ? ((size_t)(slot / block_size) * nkv) * block_size + (slot % block_size) : 0;
   T* qdst = q_out ? q_out + (size_t)n * nh * d : row;
-  // rotated heads (q then k): one item = 8 pairs of one head
+  // One pass over two kinds of items, so that a token's values are on their way while its heads
+  // turn: rotated heads (q then k), one item = 8 pairs of one head; then values, plain copies of
+  // 8 dims per item.  (Two items in flight per thread of a CTA half the size were no faster.)
   const int rot_items = (nh + nkv) * cph;
-  for (int w = threadIdx.x; w < rot_items; w += blockDim.x) {
-    const int head = w / cph, j0 = (w - head * cph) << 3;
-    float x1[8], x2[8], y1[8], y2[8];
-    load8(head * d + j0, x1);
-    load8(head * d + half + j0, x2);
+  const int v_chunks = d >> 3;
+  const int v_items = slot >= 0 ? nkv * v_chunks : 0;
+  for (int w = threadIdx.x; w < rot_items + v_items; w += blockDim.x) {
+    if (w < rot_items) {
+      const int head = w / cph, j0 = (w - head * cph) << 3;
+      float x1[8], x2[8], y1[8], y2[8];
+      load8(head * d + j0, x1);
+      load8(head * d + half + j0, x2);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float cs = cs_sn[j0 + e], sn = cs_sn[half + j0 + e];
-      rotate_pair(x1[e], x2[e], cs, sn, y1[e], y2[e]);
+      for (int e = 0; e < 8; ++e) {
+        const float cs = cs_sn[j0 + e], sn = cs_sn[half + j0 + e];
+        rotate_pair(x1[e], x2[e], cs, sn, y1[e], y2[e]);
+      }
+      T* dst = nullptr;
+      if (head < nh) {
+        dst = qdst + (size_t)head * d;
+      } else if (slot >= 0) {
+        dst = kcache + (cache_row + (size_t)(head - nh) * block_size) * d;
+      }
+      if (dst) {
+        Ld8<T>::store(dst + j0, y1);
+        Ld8<T>::store(dst + half + j0, y2);
+      }
+    } else {
+      const int v = w - rot_items;
+      const int kvh = v / v_chunks, j0 = (v - kvh * v_chunks) << 3;
+      float f[8];
+      load8((nh + nkv + kvh) * d + j0, f);
+      Ld8<T>::store(vcache + (cache_row + (size_t)kvh * block_size) * d + j0, f);
     }
-    T* dst = nullptr;
-    if (head < nh) {
-      dst = qdst + (size_t)head * d;
-    } else if (slot >= 0) {
-      dst = kcache + (cache_row + (size_t)(head - nh) * block_size) * d;
-    }
-    if (dst) {
-      Ld8<T>::store(dst + j0, y1);
-      Ld8<T>::store(dst + half + j0, y2);
-    }
-  }
-  if (slot < 0) return;
-  // values: plain copies, 8 dims per item
-  const int v_items = nkv * (d >> 3);
-  for (int w = threadIdx.x; w < v_items; w += blockDim.x) {
-    const int kvh = w / (d >> 3), j0 = (w - kvh * (d >> 3)) << 3;
-    float f[8];
-    load8((nh + nkv + kvh) * d + j0, f);
-    Ld8<T>::store(vcache + (cache_row + (size_t)kvh * block_size) * d + j0, f);
   }
 }
 
