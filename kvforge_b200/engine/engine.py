@@ -79,7 +79,7 @@ class InferenceEngine:
         self.block_manager = self.core.block_manager
         self.kv_cache = self.core.pool
         self.runner = self.core.runner
-        self.sampler = Sampler(self.core.device, sc.max_num_seqs)
+        self.sampler = Sampler(self.core.device, sc.max_num_seqs, tokens=self.core.rt.sampled_tokens)
         self.runner.token_feedback = self.sampler._tokens  # a sampled token can feed the next step on the device
         self._host_tokens = [torch.zeros(sc.max_num_seqs + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._events = [torch.cuda.Event(), torch.cuda.Event()]
@@ -220,12 +220,10 @@ class InferenceEngine:
             return None
         keys = [r.stream_base + r.num_output_tokens for r in sampled]
         tokens = self.sampler.sample(logits, [r.sampling_params for r in sampled], keys)
-        # tokens and the device's error flag go to pinned host memory behind the kernels
+        # tokens and the device's error flag (one buffer) go to pinned host memory behind the kernels, in one copy
         host = self._host_tokens[self._flip]
         self._flip ^= 1
-        n = len(sampled)
-        host[:n].copy_(tokens, non_blocking=True)
-        host[n : n + 1].copy_(self.core.rt.err, non_blocking=True)
+        host.copy_(self.core.rt.status, non_blocking=True)
         event = self._events[self._flip]
         event.record()
         max_len = self.config.scheduler.max_model_len
@@ -242,9 +240,8 @@ class InferenceEngine:
         if pending is None:
             return []
         pending.event.synchronize()
-        n = len(pending.sampled)
-        values = pending.host[: n + 1].tolist()  # the step's one device-to-host read
-        if values[n]:
+        values = pending.host.tolist()  # the step's one device-to-host read: tokens in row order, then the error flag
+        if values[-1]:
             self.core.rt.check_error_flag()
         outputs: list[RequestOutput] = []
         now = time.perf_counter()

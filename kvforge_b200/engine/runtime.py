@@ -25,7 +25,11 @@ class Runtime:
         # lazy: a buffer is made for the rows asked for (rounded up), not for the whole token budget
         self.lazy = bool(lazy)
         self._buffers: dict[tuple, torch.Tensor] = {}
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # One int32 per sequence for tokens sampled on the device, then the device error flag: a step's
+        # tokens and the flag reach the host in one copy.
+        self.status = torch.zeros(self.max_seqs + 1, dtype=torch.int32, device=self.device)
+        self.sampled_tokens = self.status[: self.max_seqs]
+        self.err = self.status[self.max_seqs :]
         # Tile sizes (queries of one sequence per CTA) of kernels that want a list of query tiles with
         # every step; parts add theirs in ``bind``, the step function fills ``StepContext.query_tiles``.
         self.query_tile_sizes: set[int] = set()

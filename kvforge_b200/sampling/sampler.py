@@ -33,13 +33,17 @@ def request_stream_base(engine_seed: int, request_id: str, params: SamplingParam
 class Sampler:
     """``sample(logits, params, keys)`` -> int32 token ids on the device."""
 
-    def __init__(self, device: torch.device | str, max_rows: int) -> None:
+    def __init__(self, device: torch.device | str, max_rows: int, tokens: torch.Tensor | None = None) -> None:
+        """``tokens``: an int32 device buffer of ``max_rows`` entries to sample into (default: one of
+        the sampler's own)."""
         self.device = torch.device(device)
         self.max_rows = m = max(1, int(max_rows))
         # int32 words: temperatures [0, m), top-k [m, 2m), top-p [2m, 3m), keys (int64) [4m, 6m)
         self._host = torch.empty(6 * m, dtype=torch.int32, pin_memory=True)
         self._dev = torch.empty(6 * m, dtype=torch.int32, device=self.device)
-        self._tokens = torch.empty(m, dtype=torch.int32, device=self.device)
+        if tokens is not None and (tokens.dtype != torch.int32 or tokens.numel() < m or not tokens.is_cuda):
+            raise ValueError("the token buffer must be int32 on the device with a place per row")
+        self._tokens = tokens if tokens is not None else torch.empty(m, dtype=torch.int32, device=self.device)
         self._argmax_scratch = torch.empty(m * ops.ARGMAX_CHUNKS, dtype=torch.int64, device=self.device)
         self._copied: torch.cuda.Event | None = None
 
