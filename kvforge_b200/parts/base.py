@@ -26,6 +26,13 @@ Kinds of part and the call each must answer:
   ``LayerCache`` (pages of this call, or of the call it reads) or ``None``.  ``y`` is a
   tensor in the storage type, ``ops.Partials`` or ``ops.ADDED``; only a norm ever reads it.
 * feed-forward — ``forward(ctx, x) -> y`` per token (``y`` as for a mixer).
+* embedding — ``forward(ctx, resid)`` fills the float residual stream ``[N, hidden]`` from the
+  step's token ids (``ctx.token_ids``, or where ``ctx.feedback_rows[n] >= 0`` the token the
+  device sampled a step before: ``ctx.token_feedback[ctx.feedback_rows[n]]``); ``table()``
+  returns its ``[vocab, hidden]`` tensor for a head that shares it.
+* head — ``forward(ctx, x) -> logits``: float logits ``[R, vocab]`` of the ``R`` normed rows it is
+  given; ``tie(table)`` hands it the embedding's tensor when the model ties the two or the
+  checkpoint has no tensor for it.
 * block — the arrangement of the above in one layer:
   ``forward(ctx, resid, delta, cache) -> delta`` (the sum not yet added to ``resid``).  An
   arrangement in which a part's result must not go straight into the residual stream (a norm
@@ -137,6 +144,22 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    def table(self) -> torch.Tensor:  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def forward(self, ctx, resid: torch.Tensor) -> None:  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Head(Part):
+    def tie(self, table: torch.Tensor) -> None:  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:  # pragma: no cover - interface
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of parts in a layer.  Sub-parts are built from ``params`` by ``build_part``."""
 
@@ -157,6 +180,8 @@ NORMS: dict[str, type[Norm]] = {}
 MIXERS: dict[str, type[Mixer]] = {}
 FEED_FORWARDS: dict[str, type[FeedForward]] = {}
 BLOCKS: dict[str, type[Block]] = {}
+EMBEDDINGS: dict[str, type[Embedding]] = {}
+HEADS: dict[str, type[Head]] = {}
 
 _FAMILIES = {
     "position": POSITION_ENCODINGS,
@@ -164,6 +189,8 @@ _FAMILIES = {
     "mixer": MIXERS,
     "ffn": FEED_FORWARDS,
     "block": BLOCKS,
+    "embedding": EMBEDDINGS,
+    "head": HEADS,
 }
 
 
@@ -197,6 +224,14 @@ def register_feed_forward(name: str):
 
 def register_block(name: str):
     return _register("block", name)
+
+
+def register_embedding(name: str):
+    return _register("embedding", name)
+
+
+def register_head(name: str):
+    return _register("head", name)
 
 
 def build_part(family: str, spec: PartSpec, prefix: str = "") -> Part:

@@ -16,6 +16,7 @@ from dataclasses import dataclass, field
 import torch
 
 from .. import ops
+from . import embedding as _embedding, head as _head  # noqa: F401  (register the default parts)
 from .base import Block, CacheNeed, LayerCache, PartSpec, WeightDecl, build_part
 
 
@@ -46,6 +47,11 @@ class ModelSpec:
     # names that may be in a checkpoint and are not weights
     ignore_suffixes: tuple[str, ...] = ("rotary_emb.inv_freq",)
     max_position_embeddings: int = 0
+    # what turns token ids into the residual stream and normed rows into logits (defaults: the token
+    # embedding and the linear head of the model's sizes); their tensors are ``embedding_name`` and
+    # ``lm_head_name``
+    embedding: PartSpec | None = None
+    head: PartSpec | None = None
     # a position encoding that acts on the residual stream after the embedding lookup (``embed``);
     # its tensors, if it has any, carry ``input_position_prefix``
     input_position: PartSpec | None = None
@@ -82,6 +88,12 @@ class DecoderModel:
         self.spec = spec
         self.blocks: list[Block] = [build_part("block", ls.block, ls.prefix) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
+        sizes = {"vocab_size": spec.vocab_size, "hidden_size": spec.hidden_size}
+        for name in (spec.embedding_name, spec.lm_head_name):
+            if not name.endswith("weight"):
+                raise ValueError(f"tensor name {name!r} must end in 'weight'")
+        self.embedding = build_part("embedding", spec.embedding or PartSpec("token_embedding", sizes), spec.embedding_name[: -len("weight")])
+        self.head = build_part("head", spec.head or PartSpec("linear_head", sizes), spec.lm_head_name[: -len("weight")])
         self.input_position = build_part("position", spec.input_position, spec.input_position_prefix) if spec.input_position else None
         # cache groups from what the mixers declare
         self.groups: list[CacheGroup] = []
@@ -116,17 +128,15 @@ class DecoderModel:
     # ------------------------------------------------------------------ weights
     def expected_weights(self) -> dict[str, WeightDecl]:
         """Checkpoint tensor name -> declaration, for everything the model needs."""
-        s = self.spec
-        out: dict[str, WeightDecl] = {
-            s.embedding_name: WeightDecl((s.vocab_size, s.hidden_size)),
-            s.lm_head_name: WeightDecl((s.vocab_size, s.hidden_size), optional=True),
-        }
+        out: dict[str, WeightDecl] = {}
         for part in self._all_parts():
             for local, decl in type(part).weight_decls(part.params).items():
                 out[part.prefix + local] = decl
         return out
 
     def _all_parts(self):
+        yield self.embedding
+        yield self.head
         for block in self.blocks:
             yield from block.sub_parts()
         yield self.final_norm
@@ -136,11 +146,6 @@ class DecoderModel:
     def bind(self, weights: dict[str, torch.Tensor], rt) -> None:
         s = self.spec
         self.rt = rt
-        self.embed_table = weights[s.embedding_name]
-        head = weights.get(s.lm_head_name)
-        # kvforge: one tensor when tied, and the embedding stands in when the head is absent
-        # (src/tokenvault/model.py:157-158, src/tokenvault/model_loader.py:105-106)
-        self.lm_head = self.embed_table if (s.tie_word_embeddings or head is None) else head
         shared_positions: dict[str, object] = {}
         for part in self._all_parts():
             pos_spec = getattr(part, "position_spec", None)
@@ -153,6 +158,10 @@ class DecoderModel:
                 part.position = shared_positions[key]
             local = {name: weights[part.prefix + name] for name in type(part).weight_decls(part.params) if part.prefix + name in weights}
             part.bind(local, rt)
+        # kvforge: one tensor when tied, and the embedding stands in when the head is absent
+        # (src/tokenvault/model.py:157-158, src/tokenvault/model_loader.py:105-106)
+        if s.tie_word_embeddings or s.lm_head_name not in weights:
+            self.head.tie(self.embedding.table())
 
     def attach_cache(self, caches: list[LayerCache | None]) -> None:
         """``caches[i]`` is what call ``i`` of the execution list reads and writes."""
@@ -165,7 +174,7 @@ class DecoderModel:
         """Runs the blocks.  Returns the float residual stream and the sum still pending."""
         rt = self.rt
         resid = rt.buf("model.resid", ctx.num_tokens, self.spec.hidden_size, torch.float32)
-        ops.embed(self.embed_table, ctx.token_ids, resid, rt.err, ctx.feedback_rows, ctx.token_feedback)
+        self.embedding.forward(ctx, resid)
         ctx.residual = resid
         if self.input_position is not None:
             self.input_position.embed(ctx, resid)
@@ -179,12 +188,7 @@ class DecoderModel:
         rt = self.rt
         resid, delta = self.forward_hidden(ctx)
         r = ctx.num_logit_rows
-        logits = rt.buf("model.logits", r, self.spec.vocab_size, torch.float32, cap=rt.max_seqs)
         if r == 0:
-            return logits
+            return rt.buf("model.logits", 0, self.spec.vocab_size, torch.float32, cap=rt.max_seqs)
         x = self.final_norm.forward(ctx, resid, delta, rows=ctx.logit_rows, num_rows=r)
-        if ops.skinny_ok(x, self.lm_head):
-            ops.gemm_skinny(x, self.lm_head, logits)
-        else:
-            ops.linear(x, self.lm_head, logits)
-        return logits
+        return self.head.forward(ctx, x)

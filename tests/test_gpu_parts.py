@@ -592,3 +592,74 @@ def test_a_toy_position_encoding_added_at_the_embedding_and_attention_without_ro
                     check(steps, outs, ref, TOL[dtype])
     finally:
         unregister_architecture("ToyLearnedPositionsForCausalLM")
+
+
+def test_a_toy_embedding_and_a_toy_head_are_registered_built_and_stepped(tmp_path):
+    """An embedding that scales its rows by the square root of the width and a head that caps its
+    logits softly (``cap * tanh(logits / cap)``), both written here on top of the built-in parts and
+    named in ``ModelSpec.embedding`` / ``ModelSpec.head``: what turns tokens into the residual
+    stream and rows into logits is a part like any other."""
+    from kvforge_b200 import ModelConfig
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.base import EMBEDDINGS, HEADS, PartSpec, register_embedding, register_head
+    from kvforge_b200.parts.embedding import TokenEmbedding
+    from kvforge_b200.parts.head import LinearHead
+    from kvforge_b200.parts.model import DecoderModel
+    from kvforge_b200.weights.random_init import write_model_dir
+    from test_gpu_replay import TOL, check, run_trace
+
+    cap = 3.0
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, ctx, resid):
+            super().forward(ctx, resid)
+            resid.mul_(math.sqrt(self.hidden))
+
+    class SoftCappedHead(LinearHead):
+        def forward(self, ctx, x):
+            logits = super().forward(ctx, x)
+            return logits.copy_(cap * torch.tanh(logits / cap))
+
+    if "toy_scaled_embedding" not in EMBEDDINGS:
+        register_embedding("toy_scaled_embedding")(ScaledEmbedding)
+    if "toy_soft_capped_head" not in HEADS:
+        register_head("toy_soft_capped_head")(SoftCappedHead)
+
+    def build(cfg):
+        spec = llama_spec(cfg)
+        sizes = {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size}
+        spec.embedding = PartSpec("toy_scaled_embedding", sizes)
+        spec.head = PartSpec("toy_soft_capped_head", sizes)
+        return spec
+
+    register_architecture("ToyEndsForCausalLM", ModelConfig.from_hf_dict, build)
+    try:
+        for name in ("tiny-a", "tiny-b"):  # a tied head and one with a tensor of its own
+            cfg = TINY[name]["cfg"]
+            cj = cfg.to_hf_dict()
+            cj["architectures"] = ["ToyEndsForCausalLM"]
+            model = DecoderModel(build(cfg))
+            skip = ("lm_head.weight",) if cfg.tie_word_embeddings else ()
+            folder = write_model_dir(tmp_path / name, cj, model.expected_weights(), seed=12, store_dtype=torch.bfloat16, init_std=0.05, norm_std=0.1, skip=skip)
+
+            class ToyPlain(PlainLlama):
+                def embed(self, ids):
+                    return super().embed(ids) * math.sqrt(self.hidden)
+
+                def logits(self, ids):
+                    return cap * torch.tanh(super().logits(ids) / cap)
+
+            plain = ToyPlain(folder)
+            reqs = {f"r{i}": random_tokens(cfg.vocab_size, n, seed=30 + i) for i, n in enumerate([40, 5, 70])}
+            ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+            assert float(ref["r0"].abs().max()) > 0.5 * cap  # the cap bites
+            cuts = (traces.whole(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: max(1, len(t) - 6) for r, t in reqs.items()}, max_live=3, seed=2))
+            for dtype in ("float32", "bfloat16"):
+                for graphs in (False, True):
+                    for steps in cuts:
+                        steps = traces.last_only(steps) if graphs else steps
+                        outs, _ = run_trace(folder, dtype, steps, max_live=3, block_size=TINY[name]["block_size"], cuda_graphs=graphs)
+                        check(steps, outs, ref, TOL[dtype])
+    finally:
+        unregister_architecture("ToyEndsForCausalLM")
