@@ -225,6 +225,35 @@ def test_layers_with_a_window_have_pages_of_their_own(tmp_path, variant_architec
             assert most_saved >= 5, cut  # 150 tokens are 10 pages of 16; a window of 21 needs 3
 
 
+@pytest.mark.parametrize("name,window", [("tiny-d", 40), ("tiny-e", 70)])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_window_through_the_tensor_core_kernels(tmp_path, variant_architecture, name, window, graphs):
+    """The same arrangement (layer 0 sees every key, the others a window) with head sizes 64 and
+    128 in bfloat16, where prompts and portions run on the tcgen05 kernel and single tokens on the
+    TMA kernel, at the model's own page size, eager and as captured graphs: a window that ends
+    inside a key tile, inside a page, and behind pages that were given back."""
+    from test_gpu_replay import TOL, check, run_trace
+
+    folder = _variant_folder(tmp_path, name, {"architectures": [variant_architecture], "test_window": window})
+    vocab = TINY[name]["cfg"].vocab_size
+    reqs = {f"r{i}": random_tokens(vocab, n, seed=40 + i) for i, n in enumerate([190, 33, 121])}
+
+    class WindowedPlain(PlainLlama):
+        def attention(self, layer, x, positions, kv=None):
+            self.window = None if layer == 0 else window
+            return super().attention(layer, x, positions, kv)
+
+    plain = WindowedPlain(folder)
+    ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+    assert rel_err(ref["r0"], PlainLlama(folder).logits(reqs["r0"])) > 1e-3
+    cuts = (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 32), traces.mixed(reqs, {r: len(t) - 12 for r, t in reqs.items()}, seed=3))
+    for steps in cuts:
+        steps = traces.last_only(steps) if graphs else steps
+        outs, runner = run_trace(folder, "bfloat16", steps, block_size=TINY[name]["block_size"], cuda_graphs=graphs)
+        check(steps, outs, ref, TOL["bfloat16"])
+        runner.core.rt.check_error_flag()
+
+
 DECAY = 0.9
 TOY_STATE = 24
 
