@@ -15,7 +15,6 @@ from dataclasses import dataclass, field
 
 import torch
 
-from .. import ops
 from . import embedding as _embedding, head as _head  # noqa: F401  (register the default parts)
 from .base import Block, CacheNeed, LayerCache, PartSpec, WeightDecl, build_part
 
