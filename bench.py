@@ -199,7 +199,8 @@ def time_prefill(core, tokens: int, reps: int = 3):
     from kvforge_b200.engine.step import BatchItem
 
     gen = torch.Generator().manual_seed(1)
-    prompt = torch.randint(0, core.spec.vocab_size, (tokens,), generator=gen).tolist()
+    # host token ids as an int32 array, which is how the engine hands a portion of a prompt to the step function
+    prompt = torch.randint(0, core.spec.vocab_size, (tokens,), generator=gen).to(torch.int32).numpy()
     times = []
     for _ in range(reps + 1):
         core.block_manager.allocate("p", tokens)

@@ -23,6 +23,8 @@ import time
 from dataclasses import dataclass
 from enum import Enum
 
+import numpy as np
+
 from ..sampling.params import SamplingParams
 
 IN_FLIGHT = -1  # stands in an output list for a token whose value is still on the device
@@ -48,7 +50,7 @@ class Request:
     __slots__ = (
         "request_id", "prompt_token_ids", "sampling_params", "arrival_time", "eos_token_id", "stream_base",
         "status", "finish_reason", "output_token_ids", "num_computed_tokens", "num_preemptions",
-        "first_scheduled_time", "finish_time", "token_times",
+        "first_scheduled_time", "finish_time", "token_times", "_prompt_array",
     )  # fmt: skip
 
     def __init__(
@@ -76,6 +78,7 @@ class Request:
         self.first_scheduled_time: float | None = None
         self.finish_time: float | None = None
         self.token_times: list[float | None] = []  # per output token: when its value reached the host
+        self._prompt_array = None  # the prompt as an int32 array, made when a portion of it is first asked for
 
     def __repr__(self) -> str:
         return f"Request({self.request_id!r}, {self.status.value}, {self.num_computed_tokens}/{self.num_tokens} tokens)"
@@ -107,12 +110,18 @@ class Request:
     def is_finished(self) -> bool:
         return self.status in _FINAL
 
-    def tokens(self, start: int, count: int) -> list[int]:
-        """``count`` known tokens from position ``start`` (prompt, then output)."""
+    def tokens(self, start: int, count: int):
+        """``count`` known tokens from position ``start`` (prompt, then output): a list, or for a
+        portion that lies inside the prompt a slice of an int32 array of it (a step copies
+        thousands of prompt tokens into its arrays; from a list that is a conversion per token)."""
         n_prompt = len(self.prompt_token_ids)
         end = start + count
         if end <= n_prompt:
-            return self.prompt_token_ids[start:end]
+            if count < 64:
+                return self.prompt_token_ids[start:end]
+            if self._prompt_array is None:
+                self._prompt_array = np.asarray(self.prompt_token_ids, dtype=np.int32)
+            return self._prompt_array[start:end]
         if start >= n_prompt:
             return self.output_token_ids[start - n_prompt : end - n_prompt]
         return self.prompt_token_ids[start:] + self.output_token_ids[: end - n_prompt]
