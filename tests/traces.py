@@ -145,3 +145,45 @@ def wanted_places(steps: list[dict]) -> list[list[tuple[str, int]]]:
             pos.pop(rid, None)
         out.append(rows)
     return out
+
+
+def staggered(requests: dict[str, list[int]], prompt_lens: dict[str, int], sizes=(2048, 1024, 3000, 4096)) -> list[dict]:
+    """Requests join one after the other: the newcomer's prompt comes in portions of changing
+    size while the earlier ones decode one token a step beside it; when every prompt is in, all
+    decode together until their tokens are used up.  Logits are wanted for the last token of
+    every entry.  Made for long prompts: few steps, each with a long reach into the cache."""
+    steps: list[dict] = []
+    pos: dict[str, int] = {}
+    turn = 0
+
+    def decoders(end):
+        entries = []
+        for rid in list(pos):
+            toks, p = requests[rid], pos[rid]
+            if p >= prompt_lens[rid] and p < len(toks):
+                entries.append({"id": rid, "tokens": [toks[p]], "want": [0]})
+                pos[rid] = p + 1
+                if pos[rid] == len(toks):
+                    end.append(rid)
+        return entries
+
+    for rid, toks in requests.items():
+        p = 0
+        while p < prompt_lens[rid]:
+            end: list[str] = []
+            entries = decoders(end)
+            n = min(sizes[turn % len(sizes)], prompt_lens[rid] - p)
+            turn += 1
+            entries.append({"id": rid, "tokens": toks[p : p + n], "want": [n - 1]})
+            p += n
+            pos[rid] = p
+            steps.append({"step": len(steps), "entries": entries, "end": end})
+            for r in end:
+                del pos[r]
+    while pos:
+        end = []
+        entries = decoders(end)
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+        for r in end:
+            del pos[r]
+    return steps
