@@ -692,3 +692,129 @@ def test_a_toy_embedding_and_a_toy_head_are_registered_built_and_stepped(tmp_pat
                         check(steps, outs, ref, TOL[dtype])
     finally:
         unregister_architecture("ToyEndsForCausalLM")
+
+
+def test_a_toy_norm_and_a_toy_block_arrangement_are_registered_built_and_stepped(tmp_path):
+    """A norm that centres its rows and has a bias, and an arrangement in which the mixer and the
+    feed-forward read the same normed rows and both add to the stream
+    (``h = h + mixer(n(h)) + ffn(n(h))``, one norm a layer), both written here and plugged in
+    through the public registries only; the final norm is the toy one too.  The arrangement asks
+    its parts for their results as tensors (``ctx.residual = None`` around their calls) and takes
+    whatever form they come in.  In 32-bit and bfloat16, eager and as captured graphs."""
+    from kvforge_b200 import ModelConfig, ops
+    from kvforge_b200.config.registry import register_architecture, unregister_architecture
+    from kvforge_b200.models.llama import llama_spec
+    from kvforge_b200.parts.base import BLOCKS, NORMS, Block, Norm, PartSpec, WeightDecl, build_part, register_block, register_norm
+    from kvforge_b200.parts.model import DecoderModel
+    from kvforge_b200.weights.random_init import write_model_dir
+    from test_gpu_replay import TOL, check, run_trace
+
+    def centred(v, w, b, eps):
+        v = v.float()
+        v = v - v.mean(-1, keepdim=True)
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float() + b.float()
+
+    def as_float(y, n):
+        """A part's result as float rows, whichever form it came in."""
+        if isinstance(y, ops.Partials):
+            return y.t[:, :n].sum(0)
+        assert y is not ops.ADDED and y is not None
+        return y[:n].float()
+
+    class CentredNorm(Norm):
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.dim, self.eps = int(params["dim"]), float(params["eps"])
+
+        @classmethod
+        def weight_decls(cls, params):
+            d = int(params["dim"])
+            return {"weight": WeightDecl((d,), kind="vector", init="ones"), "bias": WeightDecl((d,), kind="vector")}
+
+        def bind(self, weights, rt):
+            super().bind(weights, rt)
+            self.weight, self.bias = weights["weight"], weights["bias"]
+
+        def forward(self, ctx, resid, delta, rows=None, num_rows=None):
+            if delta is not None and delta is not ops.ADDED:
+                assert rows is None
+                resid += as_float(delta, resid.shape[0])
+            v = resid if rows is None else resid[rows[:num_rows].long()]
+            return centred(v, self.weight, self.bias, self.eps).to(self.rt.dtype)
+
+    class ParallelBlock(Block):
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.norm = build_part("norm", params["norm"], f"{prefix}input_layernorm.")
+            self.mixer = build_part("mixer", params["mixer"], f"{prefix}self_attn.")
+            self.ffn = build_part("ffn", params["ffn"], f"{prefix}mlp.")
+
+        def sub_parts(self):
+            return [self.norm, self.mixer, self.ffn]
+
+        def mixer_part(self):
+            return self.mixer
+
+        def forward(self, ctx, resid, delta, cache):
+            n = resid.shape[0]
+            x = self.norm.forward(ctx, resid, delta)
+            stream, ctx.residual = ctx.residual, None  # both parts read x: neither may add into the stream yet
+            a = as_float(self.mixer.forward(ctx, x, cache), n)
+            f = as_float(self.ffn.forward(ctx, x), n)
+            ctx.residual = stream
+            resid += a + f
+            return None
+
+    if "toy_centred_norm" not in NORMS:
+        register_norm("toy_centred_norm")(CentredNorm)
+    if "toy_parallel" not in BLOCKS:
+        register_block("toy_parallel")(ParallelBlock)
+
+    def build(cfg):
+        spec = llama_spec(cfg)
+        norm = PartSpec("toy_centred_norm", {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps})
+        for ls in spec.layers:
+            ls.block = PartSpec("toy_parallel", {"norm": norm, "mixer": ls.block.params["mixer"], "ffn": ls.block.params["ffn"]})
+        spec.final_norm = norm
+        return spec
+
+    register_architecture("ToyParallelForCausalLM", ModelConfig.from_hf_dict, build)
+    try:
+        cfg = TINY["tiny-d"]["cfg"]
+        cj = cfg.to_hf_dict()
+        cj["architectures"] = ["ToyParallelForCausalLM"]
+        model = DecoderModel(build(cfg))
+        names = model.expected_weights()
+        assert "model.layers.0.input_layernorm.bias" in names and "model.norm.bias" in names
+        assert not any("post_attention_layernorm" in k for k in names)
+        folder = write_model_dir(tmp_path / "toy", cj, names, seed=12, store_dtype=torch.bfloat16, init_std=0.1, norm_std=0.1, skip=("lm_head.weight",))
+
+        class ToyPlain(PlainLlama):
+            def hidden_states(self, ids):
+                ids = torch.as_tensor(ids, dtype=torch.long)
+                positions = torch.arange(ids.shape[0])
+                h = self.embed(ids).float()
+                for layer, _ in self.execution:
+                    p = f"layers.{layer}.input_layernorm."
+                    x = centred(h, self.w[p + "weight"], self.w[p + "bias"], self.eps)
+                    a, _ = self.attention(layer, x, positions, None)
+                    h = h + a + self.mlp(layer, x)
+                return centred(h, self.w["norm.weight"], self.w["norm.bias"], self.eps)
+
+        plain = ToyPlain(folder)
+        reqs = {f"r{i}": random_tokens(cfg.vocab_size, n, seed=40 + i) for i, n in enumerate([70, 5, 130, 33])}
+        ref = {rid: plain.logits(t) for rid, t in reqs.items()}
+        # the bias matters: without it the same model gives other logits
+        saved = plain.w["norm.bias"].clone()
+        plain.w["norm.bias"].zero_()
+        assert rel_err(plain.logits(reqs["r1"]), ref["r1"]) > 1e-3
+        plain.w["norm.bias"].copy_(saved)
+        cuts = (traces.whole(reqs), traces.portions(reqs), traces.tail_one_by_one(reqs, 12), traces.mixed(reqs, {r: max(1, len(t) - 6) for r, t in reqs.items()}, max_live=3, seed=2))
+        for dtype in ("float32", "bfloat16"):
+            for graphs in (False, True):
+                for steps in cuts:
+                    steps = traces.last_only(steps) if graphs else steps
+                    outs, _ = run_trace(folder, dtype, steps, max_live=3, cuda_graphs=graphs)
+                    check(steps, outs, ref, TOL[dtype])
+    finally:
+        unregister_architecture("ToyParallelForCausalLM")
