@@ -65,7 +65,7 @@ struct Shared {
   unsigned long long hist[NWARPS][256];  // per-warp histograms (count or mass); [0] holds the CTA's fold
   unsigned long long tot[256];           // the row's histogram (all CTAs of the cluster)
   unsigned long long red[NWARPS];
-  unsigned long long bcast[3];
+  unsigned long long bcast[4];
   unsigned long long blk[MAX_BLOCKS];    // mass of each stretch, in index order
   unsigned long long xu;                 // what this CTA offers to the others (a sum or a maximum)
   unsigned n_cand;                       // the first CTA's: how many entries passed top-k
@@ -299,10 +299,11 @@ __device__ __forceinline__ unsigned linear_bucket(float x, float mx) { return 25
 // until the running total reaches what is wanted: `want` itself (counts), or the share `top_p` of
 // the row's whole mass, which the histogram gives (masses).  Returns the bucket where that
 // happens; `upto` says how many entries lie in the buckets down to and including it (by mass: a
-// lower bound worked out from the masses), `all` is the total of the row.
+// lower bound worked out from the masses), `all` is the total of the row, `above` the total of the
+// buckets over the returned one.
 template <bool BY_MASS>
 __device__ int linear_level(Shared& sh, const Slice& sl, float temp, float mx, unsigned long long want, float top_p,
-                            unsigned long long& upto, unsigned long long& all) {
+                            unsigned long long& upto, unsigned long long& all, unsigned long long& above) {
   const int warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < NWARPS * 256; i += THREADS) (&sh.hist[0][0])[i] = 0ull;
   __syncthreads();
@@ -343,6 +344,7 @@ __device__ int linear_level(Shared& sh, const Slice& sl, float temp, float mx, u
       sh.bcast[0] = (unsigned long long)bucket;
       sh.bcast[1] = at >= 0 ? before + sh.tot[bucket] : total;
       sh.bcast[2] = total;
+      sh.bcast[3] = at >= 0 ? before : 0ull;
       if (BY_MASS) {
         // how many entries that is, at least: a bucket's entries weigh at most exp(-(255 - b) / 8) each
         float least = 0.f;
@@ -355,6 +357,7 @@ __device__ int linear_level(Shared& sh, const Slice& sl, float temp, float mx, u
   const int bucket = (int)sh.bcast[0];
   upto = sh.bcast[1];
   all = sh.bcast[2];
+  above = sh.bcast[3];
   __syncthreads();
   return bucket;
 }
@@ -422,10 +425,12 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   // the first CTA's shared memory (over the histograms, which are done with), if they are few, and
   // top-k, top-p and the draw are finished there on the exact values: the same masses, the same
   // cuts and the same draw in index order as the passes over the row further down.
+  bool cut_found = false;  // the top-p cut is known already (lo_key): no radix descent by mass
+  unsigned lo_key = 0u;    // entries with key >= lo_key are kept
   if ((by_count && k <= CAND_MAX) || (!by_count && top_p < 1.f)) {
-    unsigned long long upto = 0, all = 0;
-    const int bucket = by_count ? linear_level<false>(sh, sl, T, mx, (unsigned long long)k, 1.f, upto, all)
-                                : linear_level<true>(sh, sl, T, mx, 0ull, top_p, upto, all);
+    unsigned long long upto = 0, all = 0, above = 0;
+    const int bucket = by_count ? linear_level<false>(sh, sl, T, mx, (unsigned long long)k, 1.f, upto, all, above)
+                                : linear_level<true>(sh, sl, T, mx, 0ull, top_p, upto, all, above);
     unsigned* c_idx = reinterpret_cast<unsigned*>(&sh.hist[0][0]);
     unsigned* c_key = c_idx + CAND_MAX;
     float* c_val = reinterpret_cast<float*>(c_key + CAND_MAX);
@@ -433,17 +438,20 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     unsigned long long* c_kept = c_mass + CAND_MAX;
     have_all = !by_count;
     row_mass = all;
-    if (upto <= (unsigned long long)CAND_MAX) {  // (by mass this is a lower bound: the true number shows when they are gathered)
-      // every CTA first collects what it finds in its own shared memory (it stops collecting when it
-      // has more than fit: a flat row would otherwise queue up on the counter), then the CTAs learn
-      // one another's numbers and, if all fit, put theirs into the first CTA's arrays one after another
+    // Gathers the entries of the buckets from `bucket` up (or of `bucket` alone) in the first CTA's
+    // arrays, if they are at most CAND_MAX; returns how many they are (more than CAND_MAX: nothing was
+    // sent).  Every CTA first collects what it finds in its own shared memory (it stops collecting when
+    // it has more than fit: a flat row would otherwise queue up on the counter), then the CTAs learn one
+    // another's numbers and, if all fit, put theirs into the first CTA's arrays one after another.
+    auto gather = [&](bool only_cut) -> int {
       unsigned* l_idx = reinterpret_cast<unsigned*>(&sh.hist[8][0]);  // 16 KB in: behind the first CTA's arrays (14 KB)
       float* l_val = reinterpret_cast<float*>(l_idx + CAND_MAX);
       if (threadIdx.x == 0) sh.n_cand = 0u;
       __syncthreads();
       for_each(sl, [&](int i, float raw) {
         const float x = raw / T;
-        if (linear_bucket(x, mx) >= (unsigned)bucket && *(volatile unsigned*)&sh.n_cand <= (unsigned)CAND_MAX) {
+        const unsigned b = linear_bucket(x, mx);
+        if ((only_cut ? b == (unsigned)bucket : b >= (unsigned)bucket) && *(volatile unsigned*)&sh.n_cand <= (unsigned)CAND_MAX) {
           const unsigned slot = atomicAdd(&sh.n_cand, 1u);
           if (slot < (unsigned)CAND_MAX) {
             l_idx[slot] = (unsigned)i;
@@ -456,7 +464,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
       for (uint32_t c = 0; c < sl.nranks; ++c) {
         const int theirs = (int)ld_cluster_u32(in_cta(sm32(&sh.n_cand), c));
         if (c < sl.rank) offset += theirs;
-        n = theirs > CAND_MAX ? 2 * CAND_MAX : n + theirs;
+        n = (theirs > CAND_MAX || n > CAND_MAX) ? 2 * CAND_MAX : n + theirs;
       }
       if (n <= CAND_MAX) {
         const int mine = (int)sh.n_cand;
@@ -467,6 +475,10 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
         }
       }
       cluster_barrier();  // all of them are in the first CTA (or nobody sent any)
+      return n;
+    };
+    if (upto <= (unsigned long long)CAND_MAX) {  // (by mass this is a lower bound: the true number shows when they are gathered)
+      const int n = gather(false);
       if (n <= CAND_MAX) {
         if (sl.rank == 0) {
           for (int i = threadIdx.x; i < n; i += THREADS) {
@@ -544,10 +556,43 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
         return;
       }
     }
+    // ---- the middle way (top-p alone, too many entries over the cut to gather): every entry of the
+    // buckets over the cut's bucket stays, so only that bucket's entries decide where the cut lies.  If
+    // they are few, the first CTA finds the cut among them by the same rule (an entry stays if the mass
+    // of the strictly larger ones, `above` included, is below the target), every CTA learns the cut's
+    // key, and the draw goes over the row as after the radix descents.  (Bucket 0 holds everything far
+    // below the maximum: no.)
+    if (!by_count && bucket > 0) {
+      const int n = gather(true);
+      if (n <= CAND_MAX) {
+        if (sl.rank == 0) {
+          for (int i = threadIdx.x; i < n; i += THREADS) {
+            c_key[i] = ordered_key(c_val[i]);
+            c_mass[i] = __float2ull_rz(expf(c_val[i] - mx) * FIX_ONE);
+          }
+          __syncthreads();
+          unsigned long long remaining = (unsigned long long)ceil((double)top_p * (double)all);
+          if (remaining < 1ull) remaining = 1ull;
+          if (remaining > all) remaining = all;
+          unsigned lowest = 0xFFFFFFFFu;
+          for (int i = threadIdx.x; i < n; i += THREADS) {
+            unsigned long long larger = above;
+            const unsigned mine = c_key[i];
+            for (int j = 0; j < n; ++j) larger += c_key[j] > mine ? c_mass[j] : 0ull;
+            if (larger < remaining) lowest = min(lowest, mine);
+          }
+          lowest = ~block_max_u32(sh, ~lowest);
+          if (threadIdx.x == 0) sh.bcast[0] = (unsigned long long)lowest;
+        }
+        cluster_barrier();  // the cut stands in the first CTA
+        lo_key = (unsigned)ld_cluster_u64(in_cta(sm32(&sh.bcast[0]), 0));
+        cluster_barrier();  // read by all
+        cut_found = true;
+      }
+    }
   }
 
   // ---- the long way (a flat row, many equal values, or a large k): exact radix descents over the row
-  unsigned lo_key = 0u;  // entries with key >= lo_key are kept
   if (by_count) {
     unsigned prefix = 0u;
     unsigned long long remaining = (unsigned long long)k;
@@ -558,7 +603,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     }
     lo_key = prefix;  // the k-th largest key
   }
-  if (top_p < 1.f) {
+  if (top_p < 1.f && !cut_found) {
     // mass of what top-k kept (of the whole row without top-k: the histogram by mass has it)
     unsigned long long s = row_mass;
     if (!have_all) {

@@ -785,6 +785,48 @@ def test_sampling_distribution_matches_the_formula(ops, v):
             assert min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (i, tok, want)
 
 
+def test_top_p_on_flat_rows_takes_the_cut_from_one_bucket(ops):
+    """Top-p alone on rows with hundreds or thousands of entries over the cut: too many to gather, so
+    the cut is looked for among the entries of the one coarse bucket it falls into (or, when that
+    bucket is crowded too, or is the catch-all lowest one, by the radix passes).  The distribution
+    and the draw are those of the formula whichever way was taken."""
+    v = 128256
+    g = torch.Generator().manual_seed(17)
+    noise = torch.randn(v, generator=g)
+    rows = [
+        (noise * 3, 0.8, 0.9), (noise * 3, 1.0, 0.5), (noise * 3, 2.0, 0.99), (noise * 3, 0.5, 0.3),
+        (noise * 0.05, 1.0, 0.9),       # all within an eighth of a nat: one crowded bucket
+        (noise * 3, 1.0, 0.9999999),    # nearly everything stays: the cut lies far below the maximum
+        (noise * 12, 1.0, 0.999999),    # ... in the lowest bucket, which holds all that is 32 nats down
+        ((noise * 3).round(), 1.0, 0.9),  # many equal values: ties stay or go together
+    ]  # fmt: skip
+    logits = torch.stack([r[0] for r in rows])
+    temps = torch.tensor([r[1] for r in rows])
+    ps = torch.tensor([r[2] for r in rows])
+    keys = torch.arange(len(rows), dtype=torch.int64) + 4242
+    out = torch.empty(len(rows), dtype=torch.int32, device="cuda")
+    probs = torch.empty(len(rows), v, device="cuda")
+    ops.sample(dev(logits), out, dev(temps), None, dev(ps), dev(keys), probs)
+    probs = probs.cpu().double()
+    for i, (row, t, p) in enumerate(rows):
+        ref = tie_keeping_probs(row, t, 0, p)
+        differ = (probs[i] > 0) != (ref > 0)
+        assert float(ref[differ].sum()) + float(probs[i][differ].sum()) < 1e-5, (i, int(differ.sum()))
+        assert torch.allclose(probs[i][~differ], ref[~differ], atol=2e-6, rtol=1e-4), i
+        u = ops.splitmix64(int(keys[i])) / 2.0**64
+        cdf = ref.cumsum(0)
+        want = int(torch.searchsorted(cdf, torch.tensor(u * float(cdf[-1]), dtype=torch.float64), right=True))
+        tok = int(out[i])
+        assert ref[tok] > 0
+        if tok != want:  # only a draw that lands within rounding of a CDF step may differ
+            lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+            assert min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (i, tok, want)
+    # and without the probabilities written out the same tokens are drawn
+    out2 = torch.empty_like(out)
+    ops.sample(dev(logits), out2, dev(temps), None, dev(ps), dev(keys))
+    assert torch.equal(out, out2)
+
+
 def tie_keeping_probs(logits, t, k, p):
     """What the sampling kernel defines: values tied with the k-th largest all stay, and top-p
     treats equal values as one block (it stays if the mass of the strictly larger values is
