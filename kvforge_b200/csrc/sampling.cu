@@ -19,7 +19,10 @@
 // maximum comes first: when the buckets down to the one with the cut (the k-th largest, or the
 // top-p share of the mass) hold at most 512 entries, those are gathered in the first CTA's
 // shared memory and the cuts and the draw are worked out there, by the same rules, instead of by
-// radix passes over the row (which remain for flat rows, many equal values and large k).
+// radix passes over the row.  Under top-p alone on a flat row (more entries than that over the
+// cut) only the entries of the bucket the cut falls into are gathered, since all of the buckets
+// above it stay; the cut is found among them and the draw goes over the row.  The radix passes
+// remain for crowded buckets, many equal values and large k.
 #include "common.cuh"
 
 using namespace kvf;
