@@ -478,6 +478,8 @@ def run_kernel_only(args, cfg) -> dict:
         out = torch.empty(b, nh * d, device=dev, dtype=torch.bfloat16)
         qsl = torch.arange(b + 1, device=dev, dtype=torch.int32)
         cl = torch.full((b,), ctx, device=dev, dtype=torch.int32)
+        from kvforge_b200.parts.attention import CLUSTER_MERGE_MAX_PAIRS
+
         # --split 0: the engine's choice, the launch's size and the kernel's own lengthening of it
         split = args.split or ops.attention_split_size(b, nkv, ctx)
         wave = 0 if args.split else ops.attention_wave_target(b, nkv)
@@ -485,7 +487,8 @@ def run_kernel_only(args, cfg) -> dict:
         scratch = (torch.empty(sa, device=dev), torch.empty(sm, device=dev), torch.zeros(b * nkv, dtype=torch.int32, device=dev))
         sec = _graph_time(
             lambda i: ops.paged_attention(q, out, kcs[i % copies], vcs[i % copies], tables, qsl, cl, b, 1, nh, nkv, d,
-                                          d**-0.5, scratch=scratch, max_context=ctx, split_size=split, wave_target=wave),
+                                          d**-0.5, scratch=scratch, max_context=ctx, split_size=split, wave_target=wave,
+                                          cluster=b * nkv <= CLUSTER_MERGE_MAX_PAIRS),  # as the attention part chooses
             calls=max(2, args.steps), reps=3,
         )  # fmt: skip
         nbytes = b * ctx * 2 * nkv * d * 2
