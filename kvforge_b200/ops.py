@@ -338,7 +338,8 @@ def cast_from_float(src: torch.Tensor, out: torch.Tensor) -> None:
 MAX_ATTN_SPLITS = 1024  # ranges per (sequence, head) the merge kernel takes
 
 
-ATTN_ONE_WAVE = 640  # CTAs of the decode attention that run as one wave with room to spare (six fit an SM)
+ATTN_ONE_WAVE = 888  # CTAs of the decode attention that run as one wave (six fit an SM, 148 SMs)
+ATTN_ONE_WAVE_FEW_PAIRS = 640  # the same with fewer than 32 (sequence, kv head) pairs, whose merges are long: room to spare
 
 
 def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
@@ -362,12 +363,16 @@ def attention_wave_target(num_seqs: int, nkv: int) -> int:
     """How many live CTAs the TMA decode kernel aims at: it doubles the range size, on the
     device, from the step's longest context, until the ranges of all (sequence, kv head) pairs
     are at most this many: one wave of CTAs for few pairs (8 sequences at 4,096 keys: ranges of
-    256 make 1,024 CTAs, a wave and a small second one, 21.7 us; ranges of 512 one wave, 15.3 us),
-    at most six ranges a pair for many (64 sequences at 8,192 keys: ranges of 512 take 196 us,
-    ranges of 2,048 take 162 us; four a pair made ranges so long that their CTAs no longer ran
-    as even waves).  The launch's grid is made for the smallest size; CTAs of ranges that a
-    larger size leaves without keys exit at once."""
-    return max(ATTN_ONE_WAVE, 6 * num_seqs * nkv)
+    256 make 1,024 CTAs, a wave and a small second one, 21.7 us; ranges of 512 one wave, 15.3 us;
+    at 3,026 keys 768 CTAs of 256 keys are still one wave and beat 384 of 512: the batch-8 step
+    takes 0.846 instead of 0.871 ms; with 2 sequences at 12,000 keys it is the other way round,
+    0.911 against 0.890 ms, since the last CTA of a pair then merges 47 ranges: hence the lower
+    number for few pairs), at most six ranges a pair for many (64 sequences at 8,192 keys: ranges
+    of 512 take 196 us, ranges of 2,048 take 162 us; four a pair made ranges so long that their
+    CTAs no longer ran as even waves).  The launch's grid is made for the smallest size; CTAs of
+    ranges that a larger size leaves without keys exit at once."""
+    pairs = num_seqs * nkv
+    return max(ATTN_ONE_WAVE if pairs >= 32 else ATTN_ONE_WAVE_FEW_PAIRS, 6 * pairs)
 
 
 def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, split_size: int = 256) -> tuple[tuple[int, ...], tuple[int, ...]]:
