@@ -541,7 +541,7 @@ def run_kernel_only(args, cfg) -> dict:
     copies = max(2, min(12, int(1.2e9 // (n * k * 2))))
     ws = [(torch.randn(n, k, device=dev) * 0.02).bfloat16() for _ in range(copies)]
     x = torch.randn(m, k, device=dev).bfloat16()
-    splits = ops.skinny_splits(n, k)
+    splits = ops.skinny_splits(n, k, m)
     out = ops.Partials(torch.empty(splits, m, n, device=dev)) if splits > 1 else torch.empty(m, n, device=dev, dtype=torch.bfloat16)
     sec = _graph_time(lambda i: ops.gemm_skinny(x, ws[i % copies], out), calls=max(2, args.steps), reps=3)
     nbytes = n * k * 2

@@ -606,12 +606,23 @@ def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     )  # fmt: skip
 
 
-def skinny_splits(n_out: int, k: int) -> int:
-    """Slices of K so that a product with few output rows still fills the SMs (about 256 CTAs
-    of 64 rows), each slice at least 256 wide."""
+def skinny_splits(n_out: int, k: int, m: int = 8) -> int:
+    """Slices of K so that a product with few output rows still fills the SMs, each slice at least
+    256 wide.  Up to 8 tokens three CTAs of 64 rows fit an SM, and about 384 CTAs (2.6 an SM) were
+    best in whole decode steps of all three shapes, with at most 10 slices: the kernel that sums the
+    slices is the longer for each one.  (1B shape, 8 sequences: qkv / output / down with 5 / 8 / 8
+    slices 0.812 ms a step, with 8 / 8 / 10 slices 0.802 ms, with 8 / 8 / 16 slices 0.845 ms; one
+    sequence 0.730 -> 0.703 ms; the 3B shape 2.018 -> 1.974 ms.)  From 9 tokens on a CTA's tiles are
+    larger and two fit an SM: about 256 CTAs (with 384 the 16-sequence step took 1.036 instead of
+    0.925 ms)."""
     ctas = -(-n_out // 64)
-    want = round(256 / ctas)
-    return max(1, min(want, k // 256, SKINNY_MAX_SPLIT))
+    few = m <= 8
+    want = round((384 if few else 256) / ctas)
+    s = max(1, min(want, k // 256, 10 if few else SKINNY_MAX_SPLIT))
+    k_iters = -(-k // 64)
+    while s > 1 and (s - 1) * -(-k_iters // s) * 64 >= k:  # the last slice would be empty
+        s -= 1
+    return s
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | Partials, mode: str = "plain") -> None:

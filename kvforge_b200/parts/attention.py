@@ -112,7 +112,7 @@ class PagedAttention(Mixer):
         skinny = ops.skinny_ok(x, self.w_qkv)
         if cache.writable:
             slots = ctx.slot_mappings[cache.group]
-            splits = ops.skinny_splits(self.qkv_dim, self.hidden) if skinny else 1
+            splits = ops.skinny_splits(self.qkv_dim, self.hidden, n) if skinny else 1
             if splits > 1:
                 # decode: slices of K in parallel; the rotation kernel sums them
                 part = ops.Partials(rt.buf("attn.qkv_part", splits * n, self.qkv_dim, torch.float32, cap=PART_ROWS).view(splits, n, self.qkv_dim))

@@ -19,7 +19,7 @@ def project(rt, name: str, x: torch.Tensor, w: torch.Tensor, ctx=None):
     stream (``ctx.residual``) and ``ops.ADDED`` is returned."""
     n, width = x.shape[0], w.shape[0]
     if ops.skinny_ok(x, w):
-        splits = ops.skinny_splits(width, w.shape[1])
+        splits = ops.skinny_splits(width, w.shape[1], n)
         if splits > 1:
             part = ops.Partials(rt.buf(name + "_part", splits * n, width, torch.float32, cap=PART_ROWS).view(splits, n, width))
             ops.gemm_skinny(x, w, part)
