@@ -342,18 +342,34 @@ ATTN_ONE_WAVE = 888  # CTAs of the decode attention that run as one wave (six fi
 ATTN_ONE_WAVE_FEW_PAIRS = 640  # the same with fewer than 32 (sequence, kv head) pairs, whose merges are long: room to spare
 
 
+ATTN_MIN_SPLIT = 128  # the shortest range any batch gets: scratch is made for it
+# With this many (sequence, kv head) pairs (4 to 8 sequences of 8 kv heads) ranges of 128 keys: the
+# ranges of 256 keys are too few CTAs to pull the bandwidth, and the last CTA of a pair still merges
+# few (decode steps of the 1B shape at 2,088 keys: 4 sequences 0.796 -> 0.773 ms, 6 0.797 -> 0.785,
+# 8 0.803 -> 0.789 ms; at 3,040 to 5,040 keys 1.5 to 3 %).  With up to 16 pairs the ranges of a pair
+# are a thread-block cluster of at most 16 CTAs, which ranges of 256 keys keep to longer contexts
+# (one sequence 0.704 against 0.738 ms); from 96 pairs on shorter ranges lose (12 sequences 0.876
+# against 0.928 ms).
+ATTN_SHORT_RANGE_PAIRS = (17, 64)
+
+
 def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
     """Keys per range of the decode form, as the launch fixes it.  A range is a CTA, and a CTA has
     a fixed cost of a few microseconds (its chain of dependent reads, its share of the merge), so
-    ranges are not short: 256 keys, 512 with many (sequence, kv head) pairs (measured inside the
-    decode step at 1, 8 and 64 sequences), and more when the context is so long that there would
+    ranges are not short: 256 keys, 128 with 17 to 64 (sequence, kv head) pairs, 512 with 256 or more
+    (measured inside the decode step at 1 to 64 sequences), and more when the context is so long that there would
     be more than ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of the size.  (The TMA
     kernel may double the size further at run time, see ``attention_wave_target``.)  Since the
     size follows the number of sequences, so does the order in which a context's keys are merged:
     a caller that wants sums that do not depend on the batch at all (the 32-bit path) passes
     ``num_seqs=1``."""
     pairs = num_seqs * nkv
-    split = 512 if pairs >= 256 else 256
+    if pairs >= 256:
+        split = 512
+    elif ATTN_SHORT_RANGE_PAIRS[0] <= pairs <= ATTN_SHORT_RANGE_PAIRS[1]:
+        split = ATTN_MIN_SPLIT
+    else:
+        split = 256
     while -(-max_context // split) > MAX_ATTN_SPLITS:
         split *= 2
     return split

@@ -94,7 +94,7 @@ class PagedAttention(Mixer):
         # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
         split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound)
         # made for the smallest range size, so that one buffer serves every batch size
-        smallest = ops.attention_split_size(1, 1, bound)
+        smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
         sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)
         acc = rt.buf("attn.part_acc", sa[0] * sa[1] * sa[2], sa[3], torch.float32, cap=0).view(sa)
         ml = rt.buf("attn.part_ml", sm[0] * sm[1] * sm[2], sm[3], torch.float32, cap=0).view(sm)
