@@ -634,6 +634,8 @@ def skinny_splits(n_out: int, k: int, m: int = 8) -> int:
     ctas = -(-n_out // 64)
     few = m <= 8
     want = round((384 if few else 256) / ctas)
+    while want > 1 and want * ctas > (444 if few else 296):  # more CTAs than are on the SMs at once
+        want -= 1
     s = max(1, min(want, k // 256, 10 if few else SKINNY_MAX_SPLIT))
     k_iters = -(-k // 64)
     while s > 1 and (s - 1) * -(-k_iters // s) * 64 >= k:  # the last slice would be empty

@@ -82,3 +82,27 @@ def test_when_the_library_product_is_cut_into_slices_of_k():
     assert ops.library_splits(16, 2048, 2048) == 1 and ops.library_splits(129, 2048, 8192) == 1
     assert ops.library_splits(32, 16384, 2048) == 1 and ops.library_splits(32, 96, 160) == 1
     assert ops.library_splits(32, 2048, 2048 + 64) == 1  # K that does not cut into 4 slices of whole 64s
+
+
+def test_slices_of_the_decode_product_and_ranges_of_the_decode_attention():
+    import random
+
+    from kvforge_b200 import ops
+
+    # the 1B shape: qkv / output / down up to 8 tokens, and from 9 on
+    assert [ops.skinny_splits(n, k, 8) for n, k in ((3072, 2048), (2048, 2048), (2048, 8192))] == [8, 8, 10]
+    assert [ops.skinny_splits(n, k, 16) for n, k in ((3072, 2048), (2048, 2048), (2048, 8192))] == [5, 8, 8]
+    assert ops.skinny_splits(16384, 2048, 8) == 1 and ops.skinny_splits(96, 128, 4) == 1
+    # no slice is ever empty: the kernel cuts K into slices of whole 64s, the same number of them each but the last
+    rng = random.Random(0)
+    for _ in range(2000):
+        n, k, m = rng.randrange(8, 20000), 8 * rng.randrange(1, 2500), rng.choice((1, 8, 9, 16))
+        s = ops.skinny_splits(n, k, m)
+        per = -(-(-(-k // 64)) // s) * 64
+        assert 1 <= s <= ops.SKINNY_MAX_SPLIT and (s - 1) * per < k, (n, k, m, s)
+    # key ranges: 128 with 17 to 64 (sequence, kv head) pairs, 512 from 256 on, else 256; one size for one sequence
+    sizes = {pairs: ops.attention_split_size(pairs, 1, 4096) for pairs in (1, 8, 16, 17, 64, 65, 255, 256, 2048)}
+    assert sizes == {1: 256, 8: 256, 16: 256, 17: 128, 64: 128, 65: 256, 255: 256, 256: 512, 2048: 512}
+    assert ops.ATTN_MIN_SPLIT == min(sizes.values())
+    # and never more ranges than the merge takes
+    assert -(-(1 << 20) // ops.attention_split_size(8, 8, 1 << 20)) <= ops.MAX_ATTN_SPLITS
