@@ -351,12 +351,16 @@ ATTN_MIN_SPLIT = 128  # the shortest range any batch gets: scratch is made for i
 # (one sequence 0.704 against 0.738 ms); from 96 pairs on shorter ranges lose (12 sequences 0.876
 # against 0.928 ms).
 ATTN_SHORT_RANGE_PAIRS = (17, 64)
+# ... and only while the step's reach (the longest context, or what a captured graph was made for) is at most
+# this: a grid made for ranges of 128 keys over a long reach is mostly CTAs that leave at once, and they
+# cost (8 sequences at 8,030 keys 1.100 against 1.042 ms, at 32,798 keys 2.385 against 2.178 ms)
+ATTN_SHORT_RANGE_REACH = 4096
 
 
-def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
+def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0, reach: int = 0) -> int:
     """Keys per range of the decode form, as the launch fixes it.  A range is a CTA, and a CTA has
     a fixed cost of a few microseconds (its chain of dependent reads, its share of the merge), so
-    ranges are not short: 256 keys, 128 with 17 to 64 (sequence, kv head) pairs, 512 with 256 or more
+    ranges are not short: 256 keys, 128 with 17 to 64 (sequence, kv head) pairs and a ``reach`` of at most 4,096 keys, 512 with 256 or more
     (measured inside the decode step at 1 to 64 sequences), and more when the context is so long that there would
     be more than ``MAX_ATTN_SPLITS`` of them.  Ranges start at multiples of the size.  (The TMA
     kernel may double the size further at run time, see ``attention_wave_target``.)  Since the
@@ -366,7 +370,7 @@ def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0) -> int:
     pairs = num_seqs * nkv
     if pairs >= 256:
         split = 512
-    elif ATTN_SHORT_RANGE_PAIRS[0] <= pairs <= ATTN_SHORT_RANGE_PAIRS[1]:
+    elif ATTN_SHORT_RANGE_PAIRS[0] <= pairs <= ATTN_SHORT_RANGE_PAIRS[1] and reach <= ATTN_SHORT_RANGE_REACH:
         split = ATTN_MIN_SPLIT
     else:
         split = 256

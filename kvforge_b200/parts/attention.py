@@ -92,7 +92,7 @@ class PagedAttention(Mixer):
         reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
         # 32-bit: one range size whatever the batch, so a request's sums come in the same order beside
         # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
-        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound)
+        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound, reach)
         # made for the smallest range size, so that one buffer serves every batch size
         smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
         sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)

@@ -104,5 +104,6 @@ def test_slices_of_the_decode_product_and_ranges_of_the_decode_attention():
     sizes = {pairs: ops.attention_split_size(pairs, 1, 4096) for pairs in (1, 8, 16, 17, 64, 65, 255, 256, 2048)}
     assert sizes == {1: 256, 8: 256, 16: 256, 17: 128, 64: 128, 65: 256, 255: 256, 256: 512, 2048: 512}
     assert ops.ATTN_MIN_SPLIT == min(sizes.values())
+    assert ops.attention_split_size(64, 1, 1 << 17, reach=4096) == 128 and ops.attention_split_size(64, 1, 1 << 17, reach=8192) == 256
     # and never more ranges than the merge takes
     assert -(-(1 << 20) // ops.attention_split_size(8, 8, 1 << 20)) <= ops.MAX_ATTN_SPLITS
