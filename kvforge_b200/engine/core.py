@@ -58,6 +58,9 @@ class EngineCore:
     ) -> None:
         if not torch.cuda.is_available():
             raise RuntimeError("kvforge_b200 needs a CUDA device: there is no CPU path")
+        # The library's bfloat16 products sum in 32-bit, also across slices of K of the library's own
+        # choosing (a setting of this process; it costs nothing measurable on the products of this engine).
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self.spec = spec
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
