@@ -101,13 +101,21 @@ def test_gemm_f32_is_true_float32(ops, m, n, k):
     assert float((out.cpu().double() - ref).abs().max()) < 2e-6 * math.sqrt(k) * float(ref.abs().max())
 
 
-def test_gemm_f32_rows_do_not_depend_on_the_batch(ops):
-    a, w = torch.randn(200, 96), torch.randn(150, 96)
-    full = torch.empty(200, 150, device="cuda")
+@pytest.mark.parametrize("n,k", [(150, 96), (2048, 2048), (203, 1000), (64, 8192), (9, 4), (331, 130)])
+def test_gemm_f32_rows_do_not_depend_on_the_batch(ops, n, k):
+    """Up to 16 rows take a kernel of their own (a thread per output, 8 columns a CTA), more rows the
+    tiled one; both add a row's products in the order of k, so a row has the same bits alone, among
+    a handful and among hundreds.  (K = 130 is no multiple of 4: the tiled kernel takes every count.)"""
+    g = torch.Generator().manual_seed(n + k)
+    a, w = torch.randn(200, k, generator=g), torch.randn(n, k, generator=g)
+    full = torch.empty(200, n, device="cuda")
     ops.gemm_nt_f32(dev(a), dev(w), full)
-    one = torch.empty(1, 150, device="cuda")
-    ops.gemm_nt_f32(dev(a[137:138]), dev(w), one)
-    assert torch.equal(one[0], full[137])
+    ref = a.double() @ w.double().t()
+    assert float((full.cpu().double() - ref).abs().max()) < 2e-6 * math.sqrt(k) * float(ref.abs().max())
+    for lo, hi in ((137, 138), (0, 16), (100, 109), (30, 47)):
+        part = torch.full((hi - lo, n), float("nan"), device="cuda")
+        ops.gemm_nt_f32(dev(a[lo:hi]), dev(w), part)
+        assert torch.equal(part, full[lo:hi]), (lo, hi)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
