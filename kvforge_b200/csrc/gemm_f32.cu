@@ -81,32 +81,32 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
 }
 
 // The same sums for a handful of rows (decoding): with M <= 16 the tiles above are nearly empty and
-// a product with a narrow output (N = 2,048: 32 CTAs) leaves most SMs idle.  Here a CTA of 128
-// threads takes MR rows of A (8 or 16) and 256 / MR rows of W, two outputs of one row of A per
-// thread; W and A come in through a cp.async pipeline, k contiguous in shared memory, and each
-// output is one accumulator that walks k = 0..K-1 in order, exactly as above: the bits are the same
-// whichever of the two kernels runs.  (Entries past K are filled with zeros and add nothing.)  What
-// bounds a CTA is its chains of dependent FMAs, four cycles a step of k, so few CTAs of many
-// columns do as well as many of few and fetch A less often.  Needs K % 4 == 0 and 16-byte aligned rows.
-constexpr int SBK = 64, SSTAGES = 6, SLD = SBK + 4;
+// a product with a narrow output (N = 2,048: 32 CTAs) leaves most SMs idle.  Here a CTA of 64
+// threads takes MR rows of A (8 or 16) and 256 / MR rows of W, four outputs per thread (two rows of
+// A by two rows of W); W and A come in through a cp.async pipeline, k contiguous in shared memory,
+// and each output is one accumulator that walks k = 0..K-1 in order, exactly as above: the bits are
+// the same whichever of the two kernels runs.  (Entries past K are filled with zeros and add
+// nothing.)  What bounds a warp is its chains of dependent FMAs, so a thread has four of them.
+// Needs K % 4 == 0 and 16-byte aligned rows.
+constexpr int SBK = 64, SSTAGES = 6, SLD = SBK + 4, STHREADS = 64;
 
 template <int MR>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(STHREADS)
 sgemm_nt_small_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M,
                       int N, int K, int lda, int ldw, int ldc) {
-  constexpr int SBN = 256 / MR, HALF = SBN / 2;
+  constexpr int SBN = 256 / MR, HN = SBN / 2, HM = MR / 2;
   constexpr int STAGE = (SBN + MR) * SLD;  // floats: the rows of W, then the rows of A
   extern __shared__ __align__(16) float small_smem[];
   const int t = threadIdx.x;
   const int n0 = blockIdx.x * SBN;
-  const int nl = t % HALF, mr = t / HALF;  // this thread's outputs: row mr, columns n0 + nl and n0 + nl + HALF
+  const int nl = t % HN, mr = t / HN;  // outputs: rows mr and mr + HM, columns n0 + nl and n0 + nl + HN
   const int n_tiles = (K + SBK - 1) / SBK;
   auto load = [&](int stage, int tile) {
     const int k0 = tile * SBK;
     float* ws = small_smem + stage * STAGE;
     float* as = ws + SBN * SLD;
 #pragma unroll
-    for (int i = t; i < SBN * 16; i += 128) {  // rows of W x 16 chunks of 4 floats
+    for (int i = t; i < SBN * 16; i += STHREADS) {  // rows of W x 16 chunks of 4 floats
       const int row = i >> 4, c = (i & 15) * 4;
       const bool ok = n0 + row < N && k0 + c < K;
       const float* src = ok ? W + (size_t)(n0 + row) * ldw + k0 + c : W;
@@ -114,7 +114,7 @@ sgemm_nt_small_kernel(const float* __restrict__ A, const float* __restrict__ W, 
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0));
     }
 #pragma unroll
-    for (int i = t; i < MR * 16; i += 128) {
+    for (int i = t; i < MR * 16; i += STHREADS) {
       const int row = i >> 4, c = (i & 15) * 4;
       const bool ok = row < M && k0 + c < K;
       const float* src = ok ? A + (size_t)row * lda + k0 + c : A;
@@ -127,35 +127,38 @@ sgemm_nt_small_kernel(const float* __restrict__ A, const float* __restrict__ W, 
     if (s < n_tiles) load(s, s);
     asm volatile("cp.async.commit_group;" ::);
   }
-  float acc0 = 0.f, acc1 = 0.f;
+  float c00 = 0.f, c01 = 0.f, c10 = 0.f, c11 = 0.f;  // c[row][column]
   for (int tile = 0; tile < n_tiles; ++tile) {
     asm volatile("cp.async.wait_group %0;" ::"n"(SSTAGES - 2));
     __syncthreads();  // tile `tile` has landed for every thread; tile - 1 has been consumed
     if (tile + SSTAGES - 1 < n_tiles) load((tile + SSTAGES - 1) % SSTAGES, tile + SSTAGES - 1);
     asm volatile("cp.async.commit_group;" ::);
     const float* ws = small_smem + (tile % SSTAGES) * STAGE;
-    const float* ap = ws + SBN * SLD + mr * SLD;
+    const float* a0 = ws + SBN * SLD + mr * SLD;
+    const float* a1 = a0 + HM * SLD;
     const float* w0 = ws + nl * SLD;
-    const float* w1 = ws + (nl + HALF) * SLD;
+    const float* w1 = w0 + HN * SLD;
 #pragma unroll
     for (int k = 0; k < SBK; k += 4) {
-      const float4 a = *reinterpret_cast<const float4*>(ap + k);
+      const float4 p = *reinterpret_cast<const float4*>(a0 + k);
+      const float4 q = *reinterpret_cast<const float4*>(a1 + k);
       const float4 u = *reinterpret_cast<const float4*>(w0 + k);
       const float4 v = *reinterpret_cast<const float4*>(w1 + k);
-      acc0 = fmaf(a.x, u.x, acc0);
-      acc1 = fmaf(a.x, v.x, acc1);
-      acc0 = fmaf(a.y, u.y, acc0);
-      acc1 = fmaf(a.y, v.y, acc1);
-      acc0 = fmaf(a.z, u.z, acc0);
-      acc1 = fmaf(a.z, v.z, acc1);
-      acc0 = fmaf(a.w, u.w, acc0);
-      acc1 = fmaf(a.w, v.w, acc1);
+      c00 = fmaf(p.x, u.x, c00); c01 = fmaf(p.x, v.x, c01); c10 = fmaf(q.x, u.x, c10); c11 = fmaf(q.x, v.x, c11);
+      c00 = fmaf(p.y, u.y, c00); c01 = fmaf(p.y, v.y, c01); c10 = fmaf(q.y, u.y, c10); c11 = fmaf(q.y, v.y, c11);
+      c00 = fmaf(p.z, u.z, c00); c01 = fmaf(p.z, v.z, c01); c10 = fmaf(q.z, u.z, c10); c11 = fmaf(q.z, v.z, c11);
+      c00 = fmaf(p.w, u.w, c00); c01 = fmaf(p.w, v.w, c01); c10 = fmaf(q.w, u.w, c10); c11 = fmaf(q.w, v.w, c11);
     }
   }
   asm volatile("cp.async.wait_group 0;" ::);
+  const int col0 = n0 + nl, col1 = n0 + nl + HN;
   if (mr < M) {
-    if (n0 + nl < N) C[(size_t)mr * ldc + n0 + nl] = acc0;
-    if (n0 + nl + HALF < N) C[(size_t)mr * ldc + n0 + nl + HALF] = acc1;
+    if (col0 < N) C[(size_t)mr * ldc + col0] = c00;
+    if (col1 < N) C[(size_t)mr * ldc + col1] = c01;
+  }
+  if (mr + HM < M) {
+    if (col0 < N) C[(size_t)(mr + HM) * ldc + col0] = c10;
+    if (col1 < N) C[(size_t)(mr + HM) * ldc + col1] = c11;
   }
 }
 
@@ -165,7 +168,7 @@ int launch_small(const float* A, const float* W, float* C, int M, int N, int K, 
   const size_t smem = (size_t)SSTAGES * (SBN + MR) * SLD * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sgemm_nt_small_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  sgemm_nt_small_kernel<MR><<<dim3((N + SBN - 1) / SBN), 128, smem, st>>>(A, W, C, M, N, K, lda, ldw, ldc);
+  sgemm_nt_small_kernel<MR><<<dim3((N + SBN - 1) / SBN), STHREADS, smem, st>>>(A, W, C, M, N, K, lda, ldw, ldc);
   return KVF_LAUNCH_STATUS();
 }
 
