@@ -847,7 +847,9 @@ def sample(
     )  # fmt: skip
 
 
-ARGMAX_CHUNKS = 32
+# stretches of a row of logits that a CTA each looks through (8 rows of 128,256 in the decode step: 32 stretches
+# 0.789 ms a step, 128 stretches 0.782 ms; 64 rows the same either way)
+ARGMAX_CHUNKS = 128
 
 
 def argmax(logits: torch.Tensor, out_tokens: torch.Tensor, partial: torch.Tensor) -> None:

@@ -227,9 +227,11 @@ def test_gemm_tcgen05_with_the_gate(ops, m, i, h):
     assert float((out.float().cpu() - ref).abs().max()) < 1e-2 * float(ref.abs().max())
 
 
+# (width, slices): one group of threads; two and four groups that share the slices; a width past a CTA's threads
+@pytest.mark.parametrize("h,splits", [(100, 3), (2048, 10), (2048, 8), (1024, 9), (512, 16), (3072, 8), (4096, 6), (2048, 5)])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_norm_and_rope_sum_the_slices_of_a_split_product(ops, dtype):
-    n, h, splits = 6, 100, 3
+def test_norm_and_rope_sum_the_slices_of_a_split_product(ops, dtype, h, splits):
+    n = 6
     resid = torch.randn(n, h)
     parts = torch.randn(splits, n, h)
     w = torch.rand(h) + 0.5
