@@ -481,8 +481,8 @@ def run_kernel_only(args, cfg) -> dict:
         from kvforge_b200.parts.attention import CLUSTER_MERGE_MAX_PAIRS
 
         # --split 0: the engine's choice, the launch's size and the kernel's own lengthening of it
-        split = args.split or ops.attention_split_size(b, nkv, ctx, reach=ctx)
-        wave = 0 if args.split else ops.attention_wave_target(b, nkv)
+        split = args.split or ops.attention_split_size(b, nkv, ctx, reach=ctx, head_dim=d)
+        wave = 0 if args.split else ops.attention_wave_target(b, nkv, d)
         sa, sm = ops.attention_scratch_shapes(b, nh, d, ctx, split)
         scratch = (torch.empty(sa, device=dev), torch.empty(sm, device=dev), torch.zeros(b * nkv, dtype=torch.int32, device=dev))
         sec = _graph_time(

@@ -351,13 +351,16 @@ ATTN_MIN_SPLIT = 128  # the shortest range any batch gets: scratch is made for i
 # (one sequence 0.704 against 0.738 ms); from 96 pairs on shorter ranges lose (12 sequences 0.876
 # against 0.928 ms).
 ATTN_SHORT_RANGE_PAIRS = (17, 64)
+# with heads wider than 64 only up to this many pairs (8 sequences of the 3B shape at 2,074 keys: 1.925 ms a step
+# with a grid for ranges of 128 keys, 1.847 ms with one for 256; 4 sequences 1.695 against 1.730 ms)
+ATTN_SHORT_RANGE_PAIRS_WIDE_HEADS = 32
 # ... and only while the step's reach (the longest context, or what a captured graph was made for) is at most
 # this: a grid made for ranges of 128 keys over a long reach is mostly CTAs that leave at once, and they
 # cost (8 sequences at 8,030 keys 1.100 against 1.042 ms, at 32,798 keys 2.385 against 2.178 ms)
 ATTN_SHORT_RANGE_REACH = 4096
 
 
-def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0, reach: int = 0) -> int:
+def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0, reach: int = 0, head_dim: int = 64) -> int:
     """Keys per range of the decode form, as the launch fixes it.  A range is a CTA, and a CTA has
     a fixed cost of a few microseconds (its chain of dependent reads, its share of the merge), so
     ranges are not short: 256 keys, 128 with 17 to 64 (sequence, kv head) pairs and a ``reach`` of at most 4,096 keys, 512 with 256 or more
@@ -370,7 +373,7 @@ def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0, reach: i
     pairs = num_seqs * nkv
     if pairs >= 256:
         split = 512
-    elif ATTN_SHORT_RANGE_PAIRS[0] <= pairs <= ATTN_SHORT_RANGE_PAIRS[1] and reach <= ATTN_SHORT_RANGE_REACH:
+    elif ATTN_SHORT_RANGE_PAIRS[0] <= pairs <= (ATTN_SHORT_RANGE_PAIRS[1] if head_dim <= 64 else ATTN_SHORT_RANGE_PAIRS_WIDE_HEADS) and reach <= ATTN_SHORT_RANGE_REACH:
         split = ATTN_MIN_SPLIT
     else:
         split = 256
@@ -379,7 +382,7 @@ def attention_split_size(num_seqs: int, nkv: int, max_context: int = 0, reach: i
     return split
 
 
-def attention_wave_target(num_seqs: int, nkv: int) -> int:
+def attention_wave_target(num_seqs: int, nkv: int, head_dim: int = 64) -> int:
     """How many live CTAs the TMA decode kernel aims at: it doubles the range size, on the
     device, from the step's longest context, until the ranges of all (sequence, kv head) pairs
     are at most this many: one wave of CTAs for few pairs (8 sequences at 4,096 keys: ranges of
@@ -392,7 +395,12 @@ def attention_wave_target(num_seqs: int, nkv: int) -> int:
     CTAs no longer ran as even waves).  The launch's grid is made for the smallest size; CTAs of
     ranges that a larger size leaves without keys exit at once."""
     pairs = num_seqs * nkv
-    return max(ATTN_ONE_WAVE if pairs >= 32 else ATTN_ONE_WAVE_FEW_PAIRS, 6 * pairs)
+    one_wave = ATTN_ONE_WAVE if pairs >= 32 else ATTN_ONE_WAVE_FEW_PAIRS
+    if head_dim > 64:
+        # a CTA's ring is twice the size and three fit an SM: half the CTAs are a wave (8 sequences of the
+        # 3B shape at 4,026 keys: 2.255 -> 2.188 ms a step, of the 8B shape 4.113 -> 4.035 ms)
+        one_wave //= 2
+    return max(one_wave, 6 * pairs)
 
 
 def attention_scratch_shapes(max_seqs: int, nh: int, d: int, max_context: int, split_size: int = 256) -> tuple[tuple[int, ...], tuple[int, ...]]:

@@ -92,7 +92,7 @@ class PagedAttention(Mixer):
         reach = max(ctx.context_bound if ctx.context_bound > 0 else ctx.max_context_len, 1)
         # 32-bit: one range size whatever the batch, so a request's sums come in the same order beside
         # any number of others; bfloat16: longer ranges for many sequences (fewer CTAs, same bytes)
-        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound, reach)
+        split = ops.attention_split_size(ctx.num_seqs if rt.dtype == torch.bfloat16 else 1, self.nkv, bound, reach, self.d)
         # made for the smallest range size, so that one buffer serves every batch size
         smallest = min(ops.attention_split_size(1, 1, bound), ops.attention_split_size(ops.ATTN_SHORT_RANGE_PAIRS[0], 1, bound))
         sa, sm = ops.attention_scratch_shapes(max(rt.max_seqs, ctx.num_seqs), self.nh, self.d, bound, smallest)
@@ -145,7 +145,7 @@ class PagedAttention(Mixer):
         shape = (self.nh, self.nkv, self.d, self.scale)
         # bfloat16: the decode kernel may lengthen its key ranges from the step's longest context (the merge
         # order then follows the batch, within rounding); 32-bit keeps one order whatever the batch
-        wave = ops.attention_wave_target(ctx.num_seqs, self.nkv) if q.dtype == torch.bfloat16 else 0
+        wave = ops.attention_wave_target(ctx.num_seqs, self.nkv, self.d) if q.dtype == torch.bfloat16 else 0
         if ctx.all_single_query:
             scratch, bound, split = self._scratch(ctx)
         tiles = ctx.query_tiles.get(self._query_tile)

@@ -105,5 +105,8 @@ def test_slices_of_the_decode_product_and_ranges_of_the_decode_attention():
     assert sizes == {1: 256, 8: 256, 16: 256, 17: 128, 64: 128, 65: 256, 255: 256, 256: 512, 2048: 512}
     assert ops.ATTN_MIN_SPLIT == min(sizes.values())
     assert ops.attention_split_size(64, 1, 1 << 17, reach=4096) == 128 and ops.attention_split_size(64, 1, 1 << 17, reach=8192) == 256
+    # heads wider than 64: a CTA holds twice the bytes, so short ranges only up to 32 pairs and half the CTAs a wave
+    assert ops.attention_split_size(8, 8, 4096, 4096, head_dim=128) == 256 and ops.attention_split_size(4, 8, 4096, 4096, head_dim=128) == 128
+    assert ops.attention_wave_target(8, 8, 64) == 888 and ops.attention_wave_target(8, 8, 128) == 444 and ops.attention_wave_target(64, 8, 128) == 3072
     # and never more ranges than the merge takes
     assert -(-(1 << 20) // ops.attention_split_size(8, 8, 1 << 20)) <= ops.MAX_ATTN_SPLITS
