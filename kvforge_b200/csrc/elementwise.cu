@@ -439,7 +439,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restri
   T* qdst = q_out ? q_out + (size_t)n * nh * d : row;
   // One pass over two kinds of items, so that a token's values are on their way while its heads
   // turn: rotated heads (q then k), one item = 8 pairs of one head; then values, plain copies of
-  // 8 dims per item.  (CTAs of 128 threads: with 256 the 2,048-token prompt step of the 1B shape takes 4.09 instead of
+  // 8 dims per item.  (CTAs of 128 threads from 512 tokens on: with 256 the 2,048-token prompt step of the 1B shape takes 4.09 instead of
   // 4.05 ms, the 8B shape's 24.1 instead of 23.7 ms.  Two items in flight per thread were no faster.)
   const int rot_items = (nh + nkv) * cph;
   const int v_chunks = d >> 3;
@@ -615,7 +615,8 @@ static inline int norm_threads(int H) {
     if (rot < 0 || rot > d || (rot & 1)) return (int)cudaErrorInvalidValue;                              \
     if (!qkv && !(partials && q_out)) return (int)cudaErrorInvalidValue;                                 \
     if (rot == d && (d & 15) == 0 && N > 16 && (split_stride & 3) == 0) {                                \
-      return launch(rope_cache_vec_kernel<T>, dim3(N), dim3(128), (size_t)d * sizeof(float), st, (T*)qkv, partials, nsplit, \
+      /* a CTA per token: small CTAs when the tokens fill the SMs several times over, larger ones for a few dozen */ \
+      return launch(rope_cache_vec_kernel<T>, dim3(N), dim3(N >= 512 ? 128 : 256), (size_t)d * sizeof(float), st, (T*)qkv, partials, nsplit, \
                     (size_t)split_stride, (T*)q_out, positions, inv_freq, slots, (T*)kcache, (T*)vcache, \
                     nh, nkv, d, block_size, num_slots, err);                                             \
     }                                                                                                    \
