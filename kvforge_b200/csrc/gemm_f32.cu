@@ -80,6 +80,105 @@ sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
   }
 }
 
+// The same sums for many rows (prompts): tiles of 128 x 128 outputs, 8 x 8 per thread (as four blocks
+// of 4 x 4, so that a thread's reads of shared memory are whole float4s), the next tile's operands
+// fetched into registers while this one is multiplied, two buffers in shared memory.  An output is
+// still one accumulator that walks k = 0..K-1 in order: the same bits as from the kernels above and below.
+constexpr int LM = 128, LN = 128, LK = 16, LPAD = 4;
+
+__global__ void __launch_bounds__(256, 2)
+sgemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M,
+                      int N, int K, int lda, int ldw, int ldc, int vec_ok) {
+  __shared__ __align__(16) float As[2][LK][LM + LPAD];
+  __shared__ __align__(16) float Ws[2][LK][LN + LPAD];
+  const int t = threadIdx.x;
+  const int m0 = blockIdx.y * LM, n0 = blockIdx.x * LN;
+  const int ty = t >> 4, tx = t & 15;  // 16 x 16 threads; rows ty*4.. and 64 + ty*4.., columns likewise
+  // loader: 128 rows x 4 quads of k, two rows per thread (row, row + 64)
+  const int lrow = t >> 2, lk = (t & 3) * 4;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  float ra[2][4], rw[2][4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int gm = m0 + lrow + 64 * h, gn = n0 + lrow + 64 * h, gk = k0 + lk;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ra[h][i] = rw[h][i] = 0.f;
+      if (gm < M) {
+        const float* p = A + (size_t)gm * lda + gk;
+        if (vec_ok && gk + 3 < K) {
+          const float4 v = *reinterpret_cast<const float4*>(p);
+          ra[h][0] = v.x; ra[h][1] = v.y; ra[h][2] = v.z; ra[h][3] = v.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (gk + i < K) ra[h][i] = p[i];
+        }
+      }
+      if (gn < N) {
+        const float* p = W + (size_t)gn * ldw + gk;
+        if (vec_ok && gk + 3 < K) {
+          const float4 v = *reinterpret_cast<const float4*>(p);
+          rw[h][0] = v.x; rw[h][1] = v.y; rw[h][2] = v.z; rw[h][3] = v.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (gk + i < K) rw[h][i] = p[i];
+        }
+      }
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        As[buf][lk + i][lrow + 64 * h] = ra[h][i];
+        Ws[buf][lk + i][lrow + 64 * h] = rw[h][i];
+      }
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += LK) {
+    const bool more = k0 + LK < K;
+    if (more) fetch(k0 + LK);  // on its way while this tile is multiplied
+#pragma unroll
+    for (int k = 0; k < LK; ++k) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+      const float4 w0 = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * 4]);
+      const float4 w1 = *reinterpret_cast<const float4*>(&Ws[buf][k][64 + tx * 4]);
+      const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float wr[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+    }
+    if (more) {
+      stash(buf ^ 1);  // the other buffer: its last readers passed the barrier below one tile ago
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (gn < N) C[(size_t)gm * ldc + gn] = acc[i][j];
+    }
+  }
+}
+
 // The same sums for a handful of rows (decoding): with M <= 16 the tiles above are nearly empty and
 // a product with a narrow output (N = 2,048: 32 CTAs) leaves most SMs idle.  Here a CTA of 64
 // threads takes MR rows of A (8 or 16) and 256 / MR rows of W, four outputs per thread (two rows of
@@ -184,6 +283,12 @@ KVF_API int kvf_gemm_nt_f32(const float* A, const float* W, float* C, int M, int
   if (M <= 16 && vec_ok && (K & 3) == 0) {
     if (M <= 8) return launch_small<8>(A, W, C, M, N, K, lda, ldw, ldc, st);
     return launch_small<16>(A, W, C, M, N, K, lda, ldw, ldc, st);
+  }
+  if (M > 64 && N > 64) {
+    dim3 large((N + LN - 1) / LN, (M + LM - 1) / LM);
+    if (large.y > 65535) return (int)cudaErrorInvalidValue;
+    sgemm_nt_large_kernel<<<large, 256, 0, st>>>(A, W, C, M, N, K, lda, ldw, ldc, vec_ok);
+    return KVF_LAUNCH_STATUS();
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return (int)cudaErrorInvalidValue;

@@ -103,16 +103,17 @@ def test_gemm_f32_is_true_float32(ops, m, n, k):
 
 @pytest.mark.parametrize("n,k", [(150, 96), (2048, 2048), (203, 1000), (64, 8192), (9, 4), (331, 130)])
 def test_gemm_f32_rows_do_not_depend_on_the_batch(ops, n, k):
-    """Up to 16 rows take a kernel of their own (a thread per output, 8 columns a CTA), more rows the
-    tiled one; both add a row's products in the order of k, so a row has the same bits alone, among
-    a handful and among hundreds.  (K = 130 is no multiple of 4: the tiled kernel takes every count.)"""
+    """Up to 16 rows take a kernel of their own, up to 64 tiles of 64 x 64, more rows tiles of
+    128 x 128; all add a row's products in the order of k, so a row has the same bits alone, among
+    a handful and among hundreds.  (K = 130 is no multiple of 4: the tiled kernels take every count.)"""
     g = torch.Generator().manual_seed(n + k)
     a, w = torch.randn(200, k, generator=g), torch.randn(n, k, generator=g)
     full = torch.empty(200, n, device="cuda")
     ops.gemm_nt_f32(dev(a), dev(w), full)
     ref = a.double() @ w.double().t()
     assert float((full.cpu().double() - ref).abs().max()) < 2e-6 * math.sqrt(k) * float(ref.abs().max())
-    for lo, hi in ((137, 138), (0, 16), (100, 109), (30, 47)):
+    # 1, 16 and 9 rows: the kernel of few rows; 17 and 64 rows: tiles of 64 x 64; all 200 (with more than 64 columns): tiles of 128 x 128
+    for lo, hi in ((137, 138), (0, 16), (100, 109), (30, 47), (120, 184)):
         part = torch.full((hi - lo, n), float("nan"), device="cuda")
         ops.gemm_nt_f32(dev(a[lo:hi]), dev(w), part)
         assert torch.equal(part, full[lo:hi]), (lo, hi)
