@@ -35,6 +35,14 @@ class Runtime:
         self.query_tile_sizes: set[int] = set()
         self.capturing = False
         self.graphs_captured = False  # captured graphs hold buffer addresses: no buffer may move afterwards
+        self._side: torch.cuda.Stream | None = None
+
+    def side_stream(self) -> torch.cuda.Stream:
+        """A second stream for a kernel that may run beside the step's chain while a step is captured
+        (a branch of the graph); whoever uses it makes the step's stream wait for it again."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
     def buf(self, name: str, rows: int, cols: int, dtype: torch.dtype | None = None, cap: int | None = None) -> torch.Tensor:
         """A ``[rows, cols]`` view of the persistent buffer ``name`` (contents undefined).
