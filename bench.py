@@ -634,7 +634,8 @@ def _reference_package() -> str | None:
     what ``baseline/_ref/tokenvault`` holds (its build backend, hatchling, is not installed
     offline, so pip cannot make the wheel).  Returns why it is not there, or ``None``."""
     if not (REF_DIR / "tokenvault" / "__init__.py").is_file():
-        src = Path(os.environ.get("KVFORGE_REFERENCE_SRC", "/root/reference/src")) / "tokenvault"
+        # the checkout beside this repository (``../reference``), or wherever KVFORGE_REFERENCE_SRC points
+        src = Path(os.environ.get("KVFORGE_REFERENCE_SRC", str(ROOT.parent / "reference" / "src"))) / "tokenvault"
         if not src.is_dir():
             return f"no copy of the reference package under {REF_DIR.relative_to(ROOT)} and no checkout at {src.parent} to copy it from"
         import shutil
